@@ -1,0 +1,181 @@
+// L1 dispatch (fblt_attn_forward), the mask inspection entry points and the
+// host-side patch boundary helpers.
+#include "common.cuh"
+
+namespace fblt {
+
+int launch_row_kernel(const fblt_attn_desc &d, cudaStream_t stream);
+int launch_tile_kernel(const fblt_attn_desc &d, cudaStream_t stream);
+bool tile_kernel_supports(const fblt_attn_desc &d, const char **why);
+
+static int validate_desc(const fblt_attn_desc *d) {
+    if (!d) return fail(FBLT_ERR_ARG, "attn: NULL descriptor");
+    if (d->batch < 0 || d->num_heads <= 0 || d->head_dim <= 0) return fail(FBLT_ERR_ARG, "attn: bad batch/heads/head_dim");
+    if (d->batch == 0) return FBLT_OK;
+    if (!d->cu_q || !d->cu_k) return fail(FBLT_ERR_ARG, "attn: cu_q / cu_k required");
+    if (!d->q || !d->k || !d->v || !d->out) return fail(FBLT_ERR_ARG, "attn: NULL tensor");
+    const int64_t E = (int64_t)d->num_heads * d->head_dim;
+    if (d->q_stride < E || d->k_stride < E || d->v_stride < E || d->out_stride < E)
+        return fail(FBLT_ERR_ARG, "attn: row stride smaller than num_heads*head_dim");
+    const fblt_mask_desc &m = d->mask;
+    if (m.sliding_window < 0) return fail(FBLT_ERR_ARG, "attn: negative window");
+    switch (m.group_rule) {
+    case FBLT_GROUP_NONE: break;
+    case FBLT_GROUP_PATCH_ENC:
+    case FBLT_GROUP_PATCH_DEC:
+    case FBLT_GROUP_PATCH_LEQ:
+        if (!m.cu_patch || !m.patch_bounds) return fail(FBLT_ERR_ARG, "attn: patch rule needs cu_patch / patch_bounds");
+        if (m.subtokens < 1) return fail(FBLT_ERR_ARG, "attn: subtokens must be >= 1");
+        break;
+    case FBLT_GROUP_IDS:
+        if (!m.q_group_ids || !m.k_group_ids) return fail(FBLT_ERR_ARG, "attn: GROUP_IDS needs q_group_ids / k_group_ids");
+        break;
+    default: return fail(FBLT_ERR_ARG, "attn: unknown group rule %d", m.group_rule);
+    }
+    if ((m.cu_doc == nullptr) != (m.doc_bounds == nullptr)) return fail(FBLT_ERR_ARG, "attn: cu_doc and doc_bounds go together");
+    return FBLT_OK;
+}
+
+// ---- mask inspection ---------------------------------------------------------
+
+__global__ void mask_bitmap_kernel(fblt_attn_desc d, uint8_t *bitmap, int use_range) {
+    const int b = blockIdx.y;
+    const int q0 = d.cu_q[b], nq = d.cu_q[b + 1] - q0;
+    const int k0 = d.cu_k[b], nk = d.cu_k[b + 1] - k0;
+    const int64_t cell = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t cells = (int64_t)d.max_q * d.max_k;
+    if (cell >= cells) return;
+    const int i = (int)(cell / d.max_k), j = (int)(cell % d.max_k);
+    uint8_t bit = 0;
+    if (i < nq && j < nk) {
+        const SeqMask s = resolve_mask(d.mask, b, q0, k0, nq, nk);
+        if (use_range) {
+            int lo, hi;
+            row_range(s, i, lo, hi);
+            bit = (j >= lo && j < hi) ? 1 : 0;
+        } else {
+            bit = pair_allowed(s, i, j) ? 1 : 0;
+        }
+    }
+    bitmap[(int64_t)b * cells + cell] = bit;
+}
+
+__device__ int g_empty_rows;
+
+__global__ void mask_materialize_kernel(fblt_attn_desc d, int b, float *out) {
+    const int q0 = d.cu_q[b], nq = d.cu_q[b + 1] - q0;
+    const int k0 = d.cu_k[b], nk = d.cu_k[b + 1] - k0;
+    const int i = blockIdx.x;
+    if (i >= nq) return;
+    const SeqMask s = resolve_mask(d.mask, b, q0, k0, nq, nk);
+    int any = 0;
+    for (int j = threadIdx.x; j < nk; j += blockDim.x) {
+        const bool ok = pair_allowed(s, i, j);
+        out[(int64_t)i * nk + j] = ok ? 0.0f : -INFINITY;
+        any |= ok ? 1 : 0;
+    }
+    any = __syncthreads_or(any);
+    if (threadIdx.x == 0 && !any) atomicAdd(&g_empty_rows, 1);
+}
+
+} // namespace fblt
+
+extern "C" int fblt_attn_forward(const fblt_attn_desc *d, void *stream) {
+    using namespace fblt;
+    int st = validate_desc(d);
+    if (st != FBLT_OK) return st;
+    if (d->batch == 0 || d->max_q <= 0) return FBLT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const char *why = "";
+    switch (d->impl) {
+    case FBLT_IMPL_ROW: return launch_row_kernel(*d, s);
+    case FBLT_IMPL_TILE:
+        if (!tile_kernel_supports(*d, &why)) return fail(FBLT_ERR_UNSUPPORTED, "tile kernel: %s", why);
+        return launch_tile_kernel(*d, s);
+    case FBLT_IMPL_AUTO:
+        // short per-row key ranges (a patch's own bytes, one latent) stay on the row kernel
+        if ((d->mask.group_rule == FBLT_GROUP_NONE || d->mask.group_rule == FBLT_GROUP_PATCH_LEQ) && d->max_k >= 32 &&
+            tile_kernel_supports(*d, &why))
+            return launch_tile_kernel(*d, s);
+        return launch_row_kernel(*d, s);
+    default: return fail(FBLT_ERR_ARG, "attn: unknown impl %d", d->impl);
+    }
+}
+
+extern "C" int fblt_mask_bitmap(const fblt_attn_desc *d, uint8_t *bitmap, int use_range, void *stream) {
+    using namespace fblt;
+    int st = validate_desc(d);
+    if (st != FBLT_OK) return st;
+    if (!bitmap) return fail(FBLT_ERR_ARG, "mask_bitmap: NULL bitmap");
+    if (use_range && d->mask.group_rule == FBLT_GROUP_IDS)
+        return fail(FBLT_ERR_UNSUPPORTED, "mask_bitmap: explicit group ids have no key range");
+    if (d->batch == 0 || d->max_q <= 0 || d->max_k <= 0) return FBLT_OK;
+    const int64_t cells = (int64_t)d->max_q * d->max_k;
+    dim3 grid((unsigned)((cells + 255) / 256), d->batch);
+    mask_bitmap_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(*d, bitmap, use_range);
+    count_launch();
+    return check_launch("mask_bitmap_kernel");
+}
+
+extern "C" int fblt_mask_materialize(const fblt_attn_desc *d, int32_t seq, float *mask_out, int32_t *empty_rows_out,
+                                     void *stream) {
+    using namespace fblt;
+    int st = validate_desc(d);
+    if (st != FBLT_OK) return st;
+    if (!mask_out || seq < 0 || seq >= d->batch) return fail(FBLT_ERR_ARG, "mask_materialize: bad arguments");
+    if (d->max_q <= 0) return FBLT_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int zero = 0;
+    FBLT_CUDA_TRY(cudaMemcpyToSymbolAsync(g_empty_rows, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s));
+    mask_materialize_kernel<<<d->max_q, 128, 0, s>>>(*d, seq, mask_out);
+    count_launch();
+    st = check_launch("mask_materialize_kernel");
+    if (st != FBLT_OK) return st;
+    if (empty_rows_out) {
+        int v = 0;
+        FBLT_CUDA_TRY(cudaMemcpyFromSymbolAsync(&v, g_empty_rows, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
+        FBLT_CUDA_TRY(cudaStreamSynchronize(s));
+        *empty_rows_out = v;
+    }
+    return FBLT_OK;
+}
+
+// ---- host helpers --------------------------------------------------------------
+
+extern "C" int fblt_patch_bounds(const fblt_patch_info *patches, size_t num_patches, size_t seq_len, int32_t *bounds_out) {
+    using namespace fblt;
+    if ((!patches && num_patches) || !bounds_out) return fail(FBLT_ERR_ARG, "patch_bounds: NULL argument");
+    size_t pos = 0;
+    for (size_t p = 0; p < num_patches; ++p) {
+        if (patches[p].start_idx != pos) return fail(FBLT_ERR_ARG, "patch_bounds: patches must tile [0, seq_len) contiguously");
+        if (patches[p].length < 1) return fail(FBLT_ERR_ARG, "patch_bounds: empty patch");
+        bounds_out[p] = (int32_t)pos;
+        pos += patches[p].length;
+    }
+    if (pos != seq_len) return fail(FBLT_ERR_ARG, "patch_bounds: patches do not cover [0, seq_len) exactly");
+    bounds_out[num_patches] = (int32_t)pos;
+    return FBLT_OK;
+}
+
+extern "C" int32_t fblt_patch_latent_at(const int32_t *bounds, int32_t num_patches, int32_t pos) {
+    if (pos < bounds[0]) return 0;
+    if (pos >= bounds[num_patches]) return num_patches - 1;
+    int32_t lo = 0, hi = num_patches; // patch p with bounds[p] <= pos < bounds[p+1]
+    while (hi - lo > 1) {
+        const int32_t mid = (lo + hi) / 2;
+        if (bounds[mid] <= pos) lo = mid;
+        else hi = mid;
+    }
+    const bool closes = (pos + 1 == bounds[lo + 1]) && (lo + 1 < num_patches);
+    if (closes) return lo;
+    return lo == 0 ? 0 : lo - 1;
+}
+
+// sizeof of every ABI struct, for bindings that re-declare them (ctypes, cgo).
+extern "C" size_t fblt_abi_sizes(size_t *out, size_t cap) {
+    const size_t v[] = {sizeof(fblt_head_args), sizeof(fblt_patch_info), sizeof(fblt_mask_desc), sizeof(fblt_attn_desc),
+                        sizeof(fblt_decode_desc)};
+    const size_t n = sizeof(v) / sizeof(v[0]);
+    for (size_t i = 0; i < n && i < cap; ++i) out[i] = v[i];
+    return n;
+}

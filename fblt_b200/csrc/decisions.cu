@@ -1,0 +1,149 @@
+// Decision step of the speculative / block-diffusion loops: integer and
+// comparison logic whose results must equal the reference's host code exactly.
+#include "common.cuh"
+
+namespace fblt {
+
+// Strict-'>' scan from index 0 (infer/self_speculation.c:21-31): the lowest
+// index among equal maxima wins; a NaN never wins a comparison, and a NaN in
+// slot 0 makes every later comparison false, so slot 0 is returned.
+__global__ void __launch_bounds__(128) argmax_rows_kernel(const float *logits, int64_t stride, int rows, int vocab,
+                                                          int32_t *ids) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= rows) return;
+    const float *x = logits + (int64_t)row * stride;
+    const float first = x[0];
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int v = lane; v < vocab; v += 32) {
+        float val = x[v];
+        if (val != val) val = -INFINITY;
+        if (val > best || arg == 0x7fffffff) { // first element of the lane's slice, or strictly greater
+            best = val;
+            arg = v;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) {
+            best = ob;
+            arg = oa;
+        }
+    }
+    if (lane == 0) ids[row] = (first != first) ? 0 : arg;
+}
+
+// Algorithm 2 accept loop (infer/self_speculation.c:158-182), one thread per
+// candidate.
+__global__ void verify_accept_kernel(uint8_t *x, int64_t x_stride, const int32_t *pred, int64_t pred_stride,
+                                     const int32_t *l, const int32_t *r, const int32_t *target_len, int batch,
+                                     int32_t *new_len, int32_t *accepted) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= batch) return;
+    uint8_t *xc = x + (int64_t)c * x_stride;
+    const int32_t *pc = pred + (int64_t)c * pred_stride;
+    const int lc = l[c], cand = lc + r[c];
+    for (int p = lc; p < cand; ++p) {
+        const uint8_t want = (uint8_t)pc[p - 1];
+        if (xc[p] != want) {
+            xc[p] = want;
+            new_len[c] = p + 1;
+            if (accepted) accepted[c] = p - lc;
+            return;
+        }
+    }
+    if (accepted) accepted[c] = r[c];
+    if (cand < target_len[c]) {
+        xc[cand] = (uint8_t)pc[cand - 1];
+        new_len[c] = cand + 1;
+    } else {
+        new_len[c] = cand;
+    }
+}
+
+} // namespace fblt
+
+extern "C" int fblt_argmax_rows(const float *logits, int64_t stride, int32_t rows, int32_t vocab, int32_t *ids_out,
+                                void *stream) {
+    using namespace fblt;
+    if (!logits || !ids_out || vocab < 1 || rows < 0 || stride < vocab) return fail(FBLT_ERR_ARG, "argmax_rows: bad arguments");
+    if (rows == 0) return FBLT_OK;
+    argmax_rows_kernel<<<(rows + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits, stride, rows, vocab, ids_out);
+    count_launch();
+    return check_launch("argmax_rows_kernel");
+}
+
+extern "C" int fblt_verify_accept(uint8_t *x, int64_t x_stride, const int32_t *pred, int64_t pred_stride,
+                                  const int32_t *l, const int32_t *r, const int32_t *target_len, int32_t batch,
+                                  int32_t *new_len, int32_t *accepted, void *stream) {
+    using namespace fblt;
+    if (!x || !pred || !l || !r || !target_len || !new_len || batch < 0) return fail(FBLT_ERR_ARG, "verify_accept: bad arguments");
+    if (batch == 0) return FBLT_OK;
+    verify_accept_kernel<<<(batch + 127) / 128, 128, 0, (cudaStream_t)stream>>>(x, x_stride, pred, pred_stride, l, r,
+                                                                               target_len, batch, new_len, accepted);
+    count_launch();
+    return check_launch("verify_accept_kernel");
+}
+
+// ---- host mirrors of the selection helpers --------------------------------------
+
+extern "C" uint32_t fblt_unmask_select_confidence(const float *scores, const uint8_t *masked, size_t B, float alpha) {
+    uint32_t picked = 0;
+    long lead = -1;
+    for (size_t b = 0; b < B; ++b) {
+        if (!masked[b]) continue;
+        if (lead < 0 || scores[b] > scores[lead]) lead = (long)b;
+        if (scores[b] >= alpha) picked |= 1u << b;
+    }
+    if (!picked && lead >= 0) picked = 1u << lead; // always make progress
+    return picked;
+}
+
+extern "C" uint32_t fblt_unmask_select_eb(const float *scores, const uint8_t *masked, size_t B, float gamma) {
+    size_t rank[32];
+    size_t n = 0;
+    for (size_t b = 0; b < B && b < 32; ++b) { // ascending entropy, stable
+        if (!masked[b]) continue;
+        size_t slot = n++;
+        for (; slot > 0 && scores[rank[slot - 1]] > scores[b]; --slot) rank[slot] = rank[slot - 1];
+        rank[slot] = b;
+    }
+    if (!n) return 0;
+    uint32_t picked = 0;
+    float budget_used = 0.0f;
+    for (size_t t = 0; t < n; ++t) {
+        if (t > 0 && !(budget_used + scores[rank[t]] <= gamma)) break;
+        budget_used += scores[rank[t]];
+        picked |= 1u << rank[t];
+    }
+    return picked;
+}
+
+extern "C" size_t fblt_aligned_commit_select(const fblt_patch_info *patches, size_t num_patches, size_t lo, size_t hi) {
+    size_t chosen = 0;
+    for (size_t p = 0; p < num_patches; ++p) {
+        const size_t end = patches[p].start_idx + patches[p].length;
+        if (end > lo && end <= hi && end > chosen) chosen = end;
+    }
+    return chosen;
+}
+
+extern "C" size_t fblt_block_adapt_b(size_t cur_b, double rolling_acceptance, size_t b_min, size_t b_max, float target) {
+    const float band = 0.10f; // BLT_ADAPT_B_MARGIN (infer/block_generation.h:76)
+    if (b_max == 0 || b_max < b_min) return cur_b;
+    size_t low = b_min ? b_min : 1;
+    if (low > b_max) low = b_max;
+    size_t b = cur_b;
+    if (b < low) b = low;
+    if (b > b_max) b = b_max;
+    if (!(rolling_acceptance >= 0.0)) return b; // no history yet (NaN)
+    if (rolling_acceptance > (double)(target + band)) {
+        if (b < b_max) ++b;
+    } else if (rolling_acceptance < (double)(target - band)) {
+        if (b > low) --b;
+    }
+    return b;
+}

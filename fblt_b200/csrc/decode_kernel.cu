@@ -1,0 +1,444 @@
+// L1 KV-cache decode / block-verify attention: n_new fresh query rows per
+// sequence over that sequence's cache rows, every sequence and head in one
+// launch. Bandwidth-bound by construction (each K/V row is used for at most
+// n_new dot products), so the kernel is a coalesced HBM streamer:
+//
+//   * CTA = (head, key-range split, sequence x query-group), 4 warps;
+//   * a key row of one head (head_dim floats) is covered by head_dim/4 lanes
+//     with one 16-byte load each, so a warp instruction fetches 32/(head_dim/4)
+//     complete rows, and U such loads for K and V are in flight per lane;
+//   * scores are reduced inside the lane group with xor shuffles, softmax is
+//     online per lane group in the log2 domain, groups / warps merge at the end;
+//   * keys every row of the CTA can see take the unmasked path; the few keys at
+//     the window edge and the freshly appended rows take a per-row checked path;
+//   * split-K writes (m, l, acc) partials to caller scratch; a second small
+//     kernel merges them (no inter-CTA waiting anywhere).
+#include "common.cuh"
+
+#include <limits.h>
+
+namespace fblt {
+
+constexpr int kDecWarps = 4;
+constexpr int kDecThreads = kDecWarps * 32;
+
+struct DecodeParams {
+    int batch, H, n_new, block_mode, window, splits, qgroups;
+    const int32_t *base_len;
+    float *kc, *vc;
+    int64_t seq_stride, row_stride;
+    const float *q;
+    int64_t q_stride;
+    const float *kn, *vn;
+    int64_t new_stride;
+    float *out;
+    int64_t out_stride;
+    float *ws;
+    float qscale;
+};
+
+__device__ __forceinline__ float4 ld4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ float dot4(const float4 &a, const float4 &b) {
+    return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+}
+__device__ __forceinline__ void fma4(float4 &acc, float p, const float4 &v) {
+    acc.x += p * v.x;
+    acc.y += p * v.y;
+    acc.z += p * v.z;
+    acc.w += p * v.w;
+}
+__device__ __forceinline__ void scale4(float4 &a, float c) {
+    a.x *= c;
+    a.y *= c;
+    a.z *= c;
+    a.w *= c;
+}
+
+template <int HD>
+__host__ __device__ constexpr int dec_partial_floats() {
+    return HD + 4; // acc[HD], m, l, 2 pad (keeps 16-byte alignment)
+}
+
+template <int HD, int NQ>
+__global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p) {
+    constexpr int LPK = HD / 4;   // lanes per key row
+    constexpr int KPW = 32 / LPK; // key rows per warp load
+    constexpr int U = NQ == 1 ? 8 : (NQ <= 4 ? 4 : 2);
+    constexpr int CH = KPW * U; // keys per warp per chunk
+
+    const int h = blockIdx.x, sp = blockIdx.y;
+    const int b = blockIdx.z / p.qgroups, qg = blockIdx.z - b * p.qgroups;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int grp = lane / LPK, dl = lane % LPK;
+    const int n = p.n_new;
+    const int base = p.base_len[b];
+    const int total = base + n;
+    const int r0 = qg * NQ;
+    const int nv = min(NQ, n - r0); // valid rows in this query group (>= 1)
+
+    int lo_r[NQ], hi_r[NQ];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+        const int r = r0 + q;
+        if (q < nv) {
+            hi_r[q] = p.block_mode ? total : base + r + 1;
+            lo_r[q] = (p.window > 0 && !p.block_mode) ? max(0, base + r + 1 - p.window) : 0;
+        } else {
+            hi_r[q] = 0;
+            lo_r[q] = 0;
+        }
+    }
+    // rows ascend, so do both bounds
+    const int lo_min = lo_r[0], hi_min = hi_r[0];
+    int lo_max = lo_r[0], hi_max = hi_r[0];
+#pragma unroll
+    for (int q = 1; q < NQ; ++q) {
+        if (q < nv) {
+            lo_max = lo_r[q];
+            hi_max = hi_r[q];
+        }
+    }
+
+    // this CTA's share of [lo_min, hi_max)
+    const int span = hi_max - lo_min;
+    const int per = ((span + p.splits - 1) / p.splits + CH - 1) / CH * CH;
+    const int k0 = min(hi_max, lo_min + sp * per);
+    const int k1 = min(hi_max, k0 + per);
+    // keys all valid rows see, served from the cache
+    int F0 = max(k0, lo_max);
+    int F1 = min(k1, hi_min);
+    if (p.kn) F1 = min(F1, base);
+    if (F1 < F0) F1 = F0;
+    const int nchunks = (F1 - F0) / CH;
+    const int Fe = F0 + nchunks * CH;
+    const int head_slow = F0 - k0;
+    const int nslow = head_slow + (k1 - Fe);
+
+    const int64_t hoff = (int64_t)h * HD + dl * 4;
+    const float *kc = p.kc + (int64_t)b * p.seq_stride + hoff;
+    const float *vc = p.vc + (int64_t)b * p.seq_stride + hoff;
+
+    float4 qv[NQ], acc[NQ];
+    float m[NQ], l[NQ];
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+        if (q < nv) {
+            qv[q] = ld4(p.q + (int64_t)(b * n + r0 + q) * p.q_stride + hoff);
+            scale4(qv[q], p.qscale);
+        } else {
+            qv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        m[q] = -INFINITY;
+        l[q] = 0.0f;
+    }
+
+    // ---- unmasked stream -------------------------------------------------
+    for (int c = warp; c < nchunks; c += kDecWarps) {
+        const int jb = F0 + c * CH + grp;
+        float4 kk[U], vv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int64_t off = (int64_t)(jb + u * KPW) * p.row_stride;
+            kk[u] = ld4(kc + off);
+            vv[u] = ld4(vc + off);
+        }
+        float s[U][NQ];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) s[u][q] = dot4(qv[q], kk[u]);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1)
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) s[u][q] += __shfl_xor_sync(0xffffffffu, s[u][q], o);
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            float mn = m[q];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (!finite_f(s[u][q])) s[u][q] = -INFINITY;
+                mn = fmaxf(mn, s[u][q]);
+            }
+            const float mref = mn == -INFINITY ? 0.0f : mn;
+            const float corr = exp2f(m[q] - mref);
+            float ls = l[q] * corr;
+            scale4(acc[q], corr);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const float pe = exp2f(s[u][q] - mref);
+                ls += pe;
+                fma4(acc[q], pe, vv[u]);
+            }
+            l[q] = ls;
+            m[q] = mn;
+        }
+    }
+
+    // ---- checked keys: window edge, chunk remainder, appended rows --------
+    {
+        const int iters = (nslow + kDecWarps * KPW - 1) / (kDecWarps * KPW);
+        for (int it = 0; it < iters; ++it) {
+            const int t = it * (kDecWarps * KPW) + warp * KPW + grp;
+            const bool live = t < nslow;
+            const int j = t < head_slow ? k0 + t : Fe + (t - head_slow);
+            float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+            if (live) {
+                if (p.kn && j >= base) {
+                    const int64_t off = (int64_t)(b * n + (j - base)) * p.new_stride + hoff;
+                    kk = ld4(p.kn + off);
+                    vv = ld4(p.vn + off);
+                } else {
+                    const int64_t off = (int64_t)j * p.row_stride;
+                    kk = ld4(kc + off);
+                    vv = ld4(vc + off);
+                }
+            }
+            float s[NQ];
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) s[q] = dot4(qv[q], kk);
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1)
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) s[q] += __shfl_xor_sync(0xffffffffu, s[q], o);
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                const bool vis = live && j >= lo_r[q] && j < hi_r[q] && finite_f(s[q]);
+                const float sv = vis ? s[q] : -INFINITY;
+                const float mn = fmaxf(m[q], sv);
+                const float mref = mn == -INFINITY ? 0.0f : mn;
+                const float corr = exp2f(m[q] - mref);
+                const float pe = exp2f(sv - mref);
+                l[q] = l[q] * corr + pe;
+                scale4(acc[q], corr);
+                fma4(acc[q], pe, vv);
+                m[q] = mn;
+            }
+        }
+    }
+
+    // ---- merge lane groups of the warp -------------------------------------
+#pragma unroll
+    for (int o = LPK; o < 32; o <<= 1) {
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[q], o);
+            const float lo2 = __shfl_xor_sync(0xffffffffu, l[q], o);
+            float4 ao;
+            ao.x = __shfl_xor_sync(0xffffffffu, acc[q].x, o);
+            ao.y = __shfl_xor_sync(0xffffffffu, acc[q].y, o);
+            ao.z = __shfl_xor_sync(0xffffffffu, acc[q].z, o);
+            ao.w = __shfl_xor_sync(0xffffffffu, acc[q].w, o);
+            const float mn = fmaxf(m[q], mo);
+            const float mref = mn == -INFINITY ? 0.0f : mn;
+            const float ca = exp2f(m[q] - mref), cb = exp2f(mo - mref);
+            l[q] = l[q] * ca + lo2 * cb;
+            acc[q].x = acc[q].x * ca + ao.x * cb;
+            acc[q].y = acc[q].y * ca + ao.y * cb;
+            acc[q].z = acc[q].z * ca + ao.z * cb;
+            acc[q].w = acc[q].w * ca + ao.w * cb;
+            m[q] = mn;
+        }
+    }
+
+    // ---- merge warps through shared memory ---------------------------------
+    __shared__ float4 sm_acc[kDecWarps][NQ][LPK];
+    __shared__ float sm_m[kDecWarps][NQ], sm_l[kDecWarps][NQ];
+    if (grp == 0) {
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            sm_acc[warp][q][dl] = acc[q];
+            if (dl == 0) {
+                sm_m[warp][q] = m[q];
+                sm_l[warp][q] = l[q];
+            }
+        }
+    }
+    __syncthreads();
+    for (int t = tid; t < NQ * LPK; t += kDecThreads) {
+        const int q = t / LPK, c = t - q * LPK;
+        if (q >= nv) continue;
+        float M = sm_m[0][q];
+#pragma unroll
+        for (int w = 1; w < kDecWarps; ++w) M = fmaxf(M, sm_m[w][q]);
+        const float mref = M == -INFINITY ? 0.0f : M;
+        float L = 0.0f;
+        float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) {
+            const float cw = exp2f(sm_m[w][q] - mref);
+            L += sm_l[w][q] * cw;
+            fma4(A, cw, sm_acc[w][q][c]);
+        }
+        const int r = r0 + q;
+        if (p.splits == 1) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (L > 0.0f) o = make_float4(A.x / L, A.y / L, A.z / L, A.w / L);
+            *reinterpret_cast<float4 *>(p.out + (int64_t)(b * n + r) * p.out_stride + (int64_t)h * HD + c * 4) = o;
+        } else {
+            float *w = p.ws + ((((int64_t)b * p.H + h) * n + r) * p.splits + sp) * dec_partial_floats<HD>();
+            *reinterpret_cast<float4 *>(w + c * 4) = A;
+            if (c == 0) {
+                w[HD] = M;
+                w[HD + 1] = L;
+            }
+        }
+    }
+
+    // ---- write-through of the appended rows --------------------------------
+    if (p.kn && sp == p.splits - 1 && qg == 0) {
+        for (int t = tid; t < n * LPK; t += kDecThreads) {
+            const int row = t / LPK, c = t - row * LPK;
+            const int64_t src = (int64_t)(b * n + row) * p.new_stride + (int64_t)h * HD + c * 4;
+            const int64_t dst = (int64_t)b * p.seq_stride + (int64_t)(base + row) * p.row_stride + (int64_t)h * HD + c * 4;
+            *reinterpret_cast<float4 *>(p.kc + dst) = ld4(p.kn + src);
+            *reinterpret_cast<float4 *>(p.vc + dst) = ld4(p.vn + src);
+        }
+    }
+}
+
+// One warp per (sequence, head, query row): merges the split partials.
+template <int HD>
+__global__ void __launch_bounds__(128) decode_combine_kernel(DecodeParams p) {
+    constexpr int LPK = HD / 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t unit = (int64_t)blockIdx.x * 4 + warp;
+    const int64_t units = (int64_t)p.batch * p.H * p.n_new;
+    if (unit >= units) return;
+    const int r = (int)(unit % p.n_new);
+    const int h = (int)((unit / p.n_new) % p.H);
+    const int b = (int)(unit / ((int64_t)p.n_new * p.H));
+    const float *w0 = p.ws + unit * p.splits * dec_partial_floats<HD>();
+    float M = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) M = fmaxf(M, w0[(int64_t)s * dec_partial_floats<HD>() + HD]);
+    const float mref = M == -INFINITY ? 0.0f : M;
+    if (lane < LPK) {
+        float L = 0.0f;
+        float4 A = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s = 0; s < p.splits; ++s) {
+            const float *w = w0 + (int64_t)s * dec_partial_floats<HD>();
+            const float cw = exp2f(w[HD] - mref);
+            L += w[HD + 1] * cw;
+            fma4(A, cw, *reinterpret_cast<const float4 *>(w + lane * 4));
+        }
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (L > 0.0f) o = make_float4(A.x / L, A.y / L, A.z / L, A.w / L);
+        *reinterpret_cast<float4 *>(p.out + (int64_t)(b * p.n_new + r) * p.out_stride + (int64_t)h * HD + lane * 4) = o;
+    }
+}
+
+static int pick_nq(int n_new) { return n_new <= 1 ? 1 : (n_new <= 2 ? 2 : (n_new <= 4 ? 4 : 8)); }
+
+static int resolve_splits(const fblt_decode_desc *d) {
+    if (d->splits > 0) return d->splits > 64 ? 64 : d->splits;
+    const int nq = pick_nq(d->n_new);
+    const int qgroups = (d->n_new + nq - 1) / nq;
+    const int64_t ctas = (int64_t)d->batch * d->num_heads * qgroups;
+    const int64_t target = 148 * 6;
+    if (ctas >= target) return 1;
+    int64_t s = (target + ctas - 1) / ctas;
+    const int64_t cap = d->max_len / 128 > 1 ? d->max_len / 128 : 1;
+    if (s > cap) s = cap;
+    if (s > 64) s = 64;
+    return (int)s;
+}
+
+static size_t partial_floats(int hd) { return (size_t)hd + 4; }
+
+static int validate_decode(const fblt_decode_desc *d) {
+    if (!d) return fail(FBLT_ERR_ARG, "decode: NULL descriptor");
+    if (d->batch < 0 || d->num_heads <= 0) return fail(FBLT_ERR_ARG, "decode: bad batch/heads");
+    if (d->head_dim != 32 && d->head_dim != 64 && d->head_dim != 128)
+        return fail(FBLT_ERR_UNSUPPORTED, "decode: head_dim %d (32, 64 or 128)", d->head_dim);
+    if (d->n_new < 1 || d->n_new > 32) return fail(FBLT_ERR_UNSUPPORTED, "decode: n_new %d outside 1..32", d->n_new);
+    if (!d->base_len || !d->k_cache || !d->v_cache || !d->q || !d->out)
+        return fail(FBLT_ERR_ARG, "decode: NULL buffer");
+    if ((d->k_new == nullptr) != (d->v_new == nullptr)) return fail(FBLT_ERR_ARG, "decode: k_new and v_new go together");
+    const int64_t E = (int64_t)d->num_heads * d->head_dim;
+    if (d->cache_row_stride < E || d->q_stride < E || d->out_stride < E || (d->k_new && d->kv_new_stride < E))
+        return fail(FBLT_ERR_ARG, "decode: row stride smaller than num_heads*head_dim");
+    if ((d->cache_row_stride | d->cache_seq_stride | d->q_stride | d->out_stride | (d->k_new ? d->kv_new_stride : 0)) & 3)
+        return fail(FBLT_ERR_ARG, "decode: strides must be multiples of 4 elements");
+    const uintptr_t ptrs = (uintptr_t)d->k_cache | (uintptr_t)d->v_cache | (uintptr_t)d->q | (uintptr_t)d->out |
+                           (uintptr_t)d->k_new | (uintptr_t)d->v_new;
+    if (ptrs & 15) return fail(FBLT_ERR_ARG, "decode: buffers must be 16-byte aligned");
+    const int nq = pick_nq(d->n_new);
+    if ((int64_t)d->batch * ((d->n_new + nq - 1) / nq) > 65535 || d->num_heads > 65535)
+        return fail(FBLT_ERR_LIMIT, "decode: batch * query groups (or heads) exceed 65535 per launch");
+    return FBLT_OK;
+}
+
+template <int HD>
+static int launch_decode_hd(const DecodeParams &p, int nq, cudaStream_t stream) {
+    dim3 grid(p.H, p.splits, p.batch * p.qgroups);
+    switch (nq) {
+    case 1: decode_attn_kernel<HD, 1><<<grid, kDecThreads, 0, stream>>>(p); break;
+    case 2: decode_attn_kernel<HD, 2><<<grid, kDecThreads, 0, stream>>>(p); break;
+    case 4: decode_attn_kernel<HD, 4><<<grid, kDecThreads, 0, stream>>>(p); break;
+    default: decode_attn_kernel<HD, 8><<<grid, kDecThreads, 0, stream>>>(p); break;
+    }
+    count_launch();
+    int st = check_launch("decode_attn_kernel");
+    if (st != FBLT_OK) return st;
+    if (p.splits > 1) {
+        const int64_t units = (int64_t)p.batch * p.H * p.n_new;
+        decode_combine_kernel<HD><<<(unsigned)((units + 3) / 4), 128, 0, stream>>>(p);
+        count_launch();
+        st = check_launch("decode_combine_kernel");
+    }
+    return st;
+}
+
+} // namespace fblt
+
+extern "C" size_t fblt_attn_decode_workspace(const fblt_decode_desc *d) {
+    if (!d || d->batch <= 0) return 0;
+    const int splits = fblt::resolve_splits(d);
+    if (splits <= 1) return 0;
+    return (size_t)d->batch * d->num_heads * d->n_new * splits * fblt::partial_floats(d->head_dim) * sizeof(float);
+}
+
+extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size_t workspace_bytes, void *stream) {
+    using namespace fblt;
+    int st = validate_decode(d);
+    if (st != FBLT_OK) return st;
+    if (d->batch == 0) return FBLT_OK;
+    DecodeParams p;
+    p.batch = d->batch;
+    p.H = d->num_heads;
+    p.n_new = d->n_new;
+    p.block_mode = d->block_mode ? 1 : 0;
+    p.window = d->window > 0 ? d->window : 0;
+    p.splits = resolve_splits(d);
+    const int nq = pick_nq(d->n_new);
+    p.qgroups = (d->n_new + nq - 1) / nq;
+    p.base_len = d->base_len;
+    p.kc = d->k_cache;
+    p.vc = d->v_cache;
+    p.seq_stride = d->cache_seq_stride;
+    p.row_stride = d->cache_row_stride;
+    p.q = d->q;
+    p.q_stride = d->q_stride;
+    p.kn = d->k_new;
+    p.vn = d->v_new;
+    p.new_stride = d->kv_new_stride;
+    p.out = d->out;
+    p.out_stride = d->out_stride;
+    p.ws = (float *)workspace;
+    p.qscale = d->scale * kLog2e;
+    if (p.splits > 1) {
+        const size_t need = fblt_attn_decode_workspace(d);
+        if (!workspace || workspace_bytes < need)
+            return fail(FBLT_ERR_WORKSPACE, "decode: %d splits need %zu bytes of workspace, got %zu", p.splits, need,
+                        workspace_bytes);
+        if ((uintptr_t)workspace & 15) return fail(FBLT_ERR_ARG, "decode: workspace must be 16-byte aligned");
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (d->head_dim) {
+    case 32: return launch_decode_hd<32>(p, nq, s);
+    case 64: return launch_decode_hd<64>(p, nq, s);
+    default: return launch_decode_hd<128>(p, nq, s);
+    }
+}

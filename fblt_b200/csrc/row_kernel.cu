@@ -1,0 +1,88 @@
+// L1 per-row kernel: one warp per (sequence, query row, head), plain fp32 FMA,
+// online softmax, key loop restricted to the row's allowed range. Handles every
+// mask rule (explicit group ids included) and any head_dim up to 256; it is the
+// path for short key ranges (encoder cross-attention: a patch's own bytes;
+// decoder cross-attention reference rule: one latent) and the fallback for
+// shapes the tile kernel does not take.
+#include "common.cuh"
+
+namespace fblt {
+
+constexpr int kRowWarps = 4;
+
+template <int NT>
+__global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc d) {
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q0 = d.cu_q[b], nq = d.cu_q[b + 1] - q0;
+    const int k0 = d.cu_k[b], nk = d.cu_k[b + 1] - k0;
+    const int i = blockIdx.x * kRowWarps + warp;
+    if (i >= nq) return;
+    const int hd = d.head_dim;
+
+    const SeqMask s = resolve_mask(d.mask, b, q0, k0, nq, nk);
+    int lo, hi;
+    row_range(s, i, lo, hi);
+    const bool by_ids = s.group_rule == FBLT_GROUP_IDS;
+    const int my_group = by_ids ? s.qg[i] : 0;
+
+    const float qscale = d.scale * kLog2e; // scores live in the log2 domain
+    const float *qrow = d.q + (int64_t)(q0 + i) * d.q_stride + (int64_t)h * hd;
+    float qv[NT], acc[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const int dd = lane + 32 * t;
+        qv[t] = dd < hd ? qrow[dd] * qscale : 0.0f;
+        acc[t] = 0.0f;
+    }
+    float m = -INFINITY, l = 0.0f;
+    const float *kb = d.k + (int64_t)k0 * d.k_stride + (int64_t)h * hd;
+    const float *vb = d.v + (int64_t)k0 * d.v_stride + (int64_t)h * hd;
+
+    for (int j = lo; j < hi; ++j) {
+        if (by_ids && s.kg[j] != my_group) continue;
+        const float *kj = kb + (int64_t)j * d.k_stride;
+        float part = 0.0f;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const int dd = lane + 32 * t;
+            if (dd < hd) part += qv[t] * kj[dd];
+        }
+        part = warp_sum(part);
+        if (!finite_f(part)) continue; // non-finite score: weight 0
+        const float mn = fmaxf(m, part);
+        const float corr = exp2f(m - mn);
+        const float p = exp2f(part - mn);
+        l = l * corr + p;
+        const float *vj = vb + (int64_t)j * d.v_stride;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            const int dd = lane + 32 * t;
+            if (dd < hd) acc[t] = acc[t] * corr + p * vj[dd];
+        }
+        m = mn;
+    }
+
+    float *orow = d.out + (int64_t)(q0 + i) * d.out_stride + (int64_t)h * hd;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const int dd = lane + 32 * t;
+        if (dd < hd) orow[dd] = l > 0.0f ? acc[t] / l : 0.0f;
+    }
+}
+
+int launch_row_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
+    if (d.head_dim > 256) return fail(FBLT_ERR_UNSUPPORTED, "row kernel: head_dim %d > 256", d.head_dim);
+    if (d.max_q <= 0 || d.batch <= 0) return FBLT_OK;
+    if (d.num_heads > 65535 || d.batch > 65535) return fail(FBLT_ERR_LIMIT, "row kernel: batch/heads exceed 65535");
+    dim3 grid((d.max_q + kRowWarps - 1) / kRowWarps, d.num_heads, d.batch);
+    const int nt = (d.head_dim + 31) / 32;
+    if (nt <= 1) row_attn_kernel<1><<<grid, kRowWarps * 32, 0, stream>>>(d);
+    else if (nt <= 2) row_attn_kernel<2><<<grid, kRowWarps * 32, 0, stream>>>(d);
+    else if (nt <= 4) row_attn_kernel<4><<<grid, kRowWarps * 32, 0, stream>>>(d);
+    else row_attn_kernel<8><<<grid, kRowWarps * 32, 0, stream>>>(d);
+    count_launch();
+    return check_launch("row_attn_kernel");
+}
+
+} // namespace fblt

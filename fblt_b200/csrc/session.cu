@@ -1,0 +1,280 @@
+// Host-buffer sessions: the call path of a host program that owns no device
+// memory. A session allocates once (stream, staging for one batch, a batched
+// KV cache [batch, cache_rows, E] and its length table); every per-step call
+// copies its inputs host->device, runs the batched kernels, copies the result
+// back and returns with the stream idle.
+#include "common.cuh"
+
+#include <stdlib.h>
+#include <string.h>
+#include <vector>
+
+struct fblt_session {
+    cudaStream_t stream = nullptr;
+    int max_batch = 0, H = 0, hd = 0, cache_rows = 0, max_new = 0;
+    int64_t E = 0, max_q_rows = 0, max_k_rows = 0;
+    float *d_q = nullptr, *d_k = nullptr, *d_v = nullptr, *d_out = nullptr;
+    int32_t *d_tab = nullptr;
+    size_t tab_cap = 0; // int32 entries
+    float *kc = nullptr, *vc = nullptr;
+    int32_t *d_lens = nullptr, *h_lens = nullptr;
+    float *d_qn = nullptr, *d_kn = nullptr, *d_vn = nullptr, *d_on = nullptr;
+    void *ws = nullptr;
+    size_t ws_bytes = 0;
+};
+
+namespace fblt {
+
+static void session_free(fblt_session *s) {
+    if (!s) return;
+    cudaFree(s->d_q);
+    cudaFree(s->d_k);
+    cudaFree(s->d_v);
+    cudaFree(s->d_out);
+    cudaFree(s->d_tab);
+    cudaFree(s->kc);
+    cudaFree(s->vc);
+    cudaFree(s->d_lens);
+    cudaFree(s->d_qn);
+    cudaFree(s->d_kn);
+    cudaFree(s->d_vn);
+    cudaFree(s->d_on);
+    cudaFree(s->ws);
+    if (s->h_lens) cudaFreeHost(s->h_lens);
+    if (s->stream) cudaStreamDestroy(s->stream);
+    delete s;
+}
+
+// Bump placement of int32 tables in the session's device table arena.
+struct TableArena {
+    fblt_session *s;
+    size_t used = 0;
+    int status = FBLT_OK;
+    const int32_t *put(const int32_t *host, size_t n) {
+        if (!host || status != FBLT_OK) return nullptr;
+        const size_t padded = (n + 3) & ~(size_t)3;
+        if (used + padded > s->tab_cap) {
+            status = fail(FBLT_ERR_CAPACITY, "session: mask tables exceed session capacity");
+            return nullptr;
+        }
+        int32_t *dst = s->d_tab + used;
+        cudaError_t e = cudaMemcpyAsync(dst, host, n * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream);
+        if (e != cudaSuccess) {
+            status = fail(FBLT_ERR_CUDA, "session: table upload: %s", cudaGetErrorString(e));
+            return nullptr;
+        }
+        used += padded;
+        return dst;
+    }
+};
+
+} // namespace fblt
+
+extern "C" int fblt_session_create(fblt_session **out, int32_t max_batch, int32_t num_heads, int32_t head_dim,
+                                   int64_t max_q_rows, int64_t max_k_rows, int32_t cache_rows, int32_t max_new) {
+    using namespace fblt;
+    if (!out || max_batch < 1 || num_heads < 1 || head_dim < 1 || max_q_rows < 0 || max_k_rows < 0 || cache_rows < 0 ||
+        max_new < 0)
+        return fail(FBLT_ERR_ARG, "session_create: bad arguments");
+    fblt_session *s = new fblt_session();
+    s->max_batch = max_batch;
+    s->H = num_heads;
+    s->hd = head_dim;
+    s->E = (int64_t)num_heads * head_dim;
+    s->max_q_rows = max_q_rows;
+    s->max_k_rows = max_k_rows;
+    s->cache_rows = cache_rows;
+    s->max_new = max_new;
+#define S_TRY(expr)                                                                          \
+    do {                                                                                     \
+        cudaError_t e__ = (expr);                                                            \
+        if (e__ != cudaSuccess) {                                                            \
+            session_free(s);                                                                 \
+            return fail(FBLT_ERR_CUDA, "session_create: %s: %s", #expr, cudaGetErrorString(e__)); \
+        }                                                                                    \
+    } while (0)
+    S_TRY(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    const size_t fE = (size_t)s->E * sizeof(float);
+    if (max_q_rows > 0) {
+        S_TRY(cudaMalloc(&s->d_q, (size_t)max_q_rows * fE));
+        S_TRY(cudaMalloc(&s->d_out, (size_t)max_q_rows * fE));
+    }
+    if (max_k_rows > 0) {
+        S_TRY(cudaMalloc(&s->d_k, (size_t)max_k_rows * fE));
+        S_TRY(cudaMalloc(&s->d_v, (size_t)max_k_rows * fE));
+    }
+    // tables: 8 per-sequence arrays plus doc / patch boundary lists
+    s->tab_cap = (size_t)(max_batch + 4) * 10 + (size_t)max_k_rows + (size_t)max_q_rows + 2 * (size_t)max_batch + 64;
+    S_TRY(cudaMalloc(&s->d_tab, s->tab_cap * sizeof(int32_t)));
+    S_TRY(cudaMalloc(&s->d_lens, (size_t)max_batch * sizeof(int32_t)));
+    S_TRY(cudaMallocHost(&s->h_lens, (size_t)max_batch * sizeof(int32_t)));
+    memset(s->h_lens, 0, (size_t)max_batch * sizeof(int32_t));
+    if (cache_rows > 0) {
+        const size_t cache_bytes = (size_t)max_batch * cache_rows * fE;
+        S_TRY(cudaMalloc(&s->kc, cache_bytes));
+        S_TRY(cudaMalloc(&s->vc, cache_bytes));
+    }
+    if (max_new > 0) {
+        const size_t nb = (size_t)max_batch * max_new * fE;
+        S_TRY(cudaMalloc(&s->d_qn, nb));
+        S_TRY(cudaMalloc(&s->d_kn, nb));
+        S_TRY(cudaMalloc(&s->d_vn, nb));
+        S_TRY(cudaMalloc(&s->d_on, nb));
+        // split-K partials exist only while (sequences x heads) is below the
+        // launch-width target, which bounds units x splits
+        s->ws_bytes = (size_t)2048 * max_new * ((size_t)head_dim + 4) * sizeof(float);
+        S_TRY(cudaMalloc(&s->ws, s->ws_bytes));
+    }
+#undef S_TRY
+    *out = s;
+    return FBLT_OK;
+}
+
+extern "C" void fblt_session_destroy(fblt_session *s) { fblt::session_free(s); }
+
+extern "C" int fblt_session_forward(fblt_session *s, const fblt_attn_desc *hd) {
+    using namespace fblt;
+    if (!s || !hd) return fail(FBLT_ERR_ARG, "session_forward: NULL argument");
+    if (hd->batch < 0 || hd->batch > s->max_batch) return fail(FBLT_ERR_CAPACITY, "session_forward: batch %d > %d", hd->batch, s->max_batch);
+    if (hd->num_heads != s->H || hd->head_dim != s->hd) return fail(FBLT_ERR_ARG, "session_forward: heads/head_dim differ from the session");
+    if (hd->batch == 0) return FBLT_OK;
+    if (!hd->cu_q || !hd->cu_k || !hd->q || !hd->k || !hd->v || !hd->out) return fail(FBLT_ERR_ARG, "session_forward: NULL buffer");
+    if (hd->mask.q_group_ids || hd->mask.k_group_ids) return fail(FBLT_ERR_UNSUPPORTED, "session_forward: explicit group ids are device-only");
+    const int B = hd->batch;
+    const int64_t tq = hd->cu_q[B], tk = hd->cu_k[B];
+    if (tq > s->max_q_rows || tk > s->max_k_rows) return fail(FBLT_ERR_CAPACITY, "session_forward: %lld/%lld rows exceed session staging", (long long)tq, (long long)tk);
+    const int64_t E = s->E;
+    if (hd->q_stride < E || hd->k_stride < E || hd->v_stride < E || hd->out_stride < E) return fail(FBLT_ERR_ARG, "session_forward: row stride smaller than num_heads*head_dim");
+
+    const size_t wb = (size_t)E * sizeof(float);
+    FBLT_CUDA_TRY(cudaMemcpy2DAsync(s->d_q, wb, hd->q, (size_t)hd->q_stride * 4, wb, (size_t)tq, cudaMemcpyHostToDevice, s->stream));
+    FBLT_CUDA_TRY(cudaMemcpy2DAsync(s->d_k, wb, hd->k, (size_t)hd->k_stride * 4, wb, (size_t)tk, cudaMemcpyHostToDevice, s->stream));
+    FBLT_CUDA_TRY(cudaMemcpy2DAsync(s->d_v, wb, hd->v, (size_t)hd->v_stride * 4, wb, (size_t)tk, cudaMemcpyHostToDevice, s->stream));
+
+    fblt_attn_desc d = *hd;
+    TableArena ta{s};
+    d.cu_q = ta.put(hd->cu_q, (size_t)B + 1);
+    d.cu_k = ta.put(hd->cu_k, (size_t)B + 1);
+    const fblt_mask_desc &hm = hd->mask;
+    d.mask.causal_offset = ta.put(hm.causal_offset, (size_t)B);
+    if (hm.cu_doc && hm.doc_bounds) {
+        d.mask.cu_doc = ta.put(hm.cu_doc, (size_t)B + 1);
+        d.mask.doc_bounds = ta.put(hm.doc_bounds, (size_t)hm.cu_doc[B] > 0 ? (size_t)hm.cu_doc[B] : 1);
+    }
+    if (hm.cu_patch && hm.patch_bounds) {
+        d.mask.cu_patch = ta.put(hm.cu_patch, (size_t)B + 1);
+        d.mask.patch_bounds = ta.put(hm.patch_bounds, (size_t)hm.cu_patch[B]);
+    }
+    d.mask.q_pos_offset = ta.put(hm.q_pos_offset, (size_t)B);
+    d.mask.num_clean = ta.put(hm.num_clean, (size_t)B);
+    if (hm.trailing_closed) {
+        std::vector<int32_t> packed(((size_t)B + 3) / 4, 0);
+        memcpy(packed.data(), hm.trailing_closed, (size_t)B);
+        // bytes keep their order inside the int32 words on a little-endian host
+        d.mask.trailing_closed = reinterpret_cast<const uint8_t *>(ta.put(packed.data(), packed.size()));
+        // `packed` is pageable: the copy above has completed staging on return
+    }
+    if (ta.status != FBLT_OK) return ta.status;
+    d.q = s->d_q;
+    d.k = s->d_k;
+    d.v = s->d_v;
+    d.out = s->d_out;
+    d.q_stride = d.k_stride = d.v_stride = d.out_stride = E;
+    int st = fblt_attn_forward(&d, s->stream);
+    if (st != FBLT_OK) return st;
+    FBLT_CUDA_TRY(cudaMemcpy2DAsync(hd->out, (size_t)hd->out_stride * 4, s->d_out, wb, wb, (size_t)tq, cudaMemcpyDeviceToHost, s->stream));
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    return FBLT_OK;
+}
+
+extern "C" int fblt_session_cache_load(fblt_session *s, int32_t batch, const int32_t *lens, const float *k_host,
+                                       const float *v_host, int64_t host_seq_stride_rows) {
+    using namespace fblt;
+    if (!s || !lens || batch < 0) return fail(FBLT_ERR_ARG, "cache_load: bad arguments");
+    if (batch > s->max_batch || !s->kc) return fail(FBLT_ERR_CAPACITY, "cache_load: batch %d exceeds the session cache", batch);
+    const size_t rowb = (size_t)s->E * sizeof(float);
+    int32_t max_len = 0;
+    bool uniform = batch > 0;
+    for (int b = 0; b < batch; ++b) {
+        if (lens[b] < 0 || lens[b] > s->cache_rows) return fail(FBLT_ERR_CAPACITY, "cache_load: length %d exceeds cache_rows %d", lens[b], s->cache_rows);
+        if (lens[b] > host_seq_stride_rows) return fail(FBLT_ERR_ARG, "cache_load: length exceeds the host stride");
+        max_len = lens[b] > max_len ? lens[b] : max_len;
+        uniform = uniform && lens[b] == lens[0];
+        s->h_lens[b] = lens[b];
+    }
+    if (batch > 0 && max_len > 0) {
+        if (!k_host || !v_host) return fail(FBLT_ERR_ARG, "cache_load: NULL host rows");
+        if (uniform) {
+            // one strided copy per array: `max_len` rows of every sequence
+            const size_t width = (size_t)max_len * rowb;
+            FBLT_CUDA_TRY(cudaMemcpy2DAsync(s->kc, (size_t)s->cache_rows * rowb, k_host, (size_t)host_seq_stride_rows * rowb, width, (size_t)batch, cudaMemcpyHostToDevice, s->stream));
+            FBLT_CUDA_TRY(cudaMemcpy2DAsync(s->vc, (size_t)s->cache_rows * rowb, v_host, (size_t)host_seq_stride_rows * rowb, width, (size_t)batch, cudaMemcpyHostToDevice, s->stream));
+        } else {
+            for (int b = 0; b < batch; ++b) {
+                if (!lens[b]) continue;
+                const size_t bytes = (size_t)lens[b] * rowb;
+                FBLT_CUDA_TRY(cudaMemcpyAsync(s->kc + (size_t)b * s->cache_rows * s->E, k_host + (size_t)b * host_seq_stride_rows * s->E, bytes, cudaMemcpyHostToDevice, s->stream));
+                FBLT_CUDA_TRY(cudaMemcpyAsync(s->vc + (size_t)b * s->cache_rows * s->E, v_host + (size_t)b * host_seq_stride_rows * s->E, bytes, cudaMemcpyHostToDevice, s->stream));
+            }
+        }
+    }
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    return FBLT_OK;
+}
+
+extern "C" int fblt_session_decode(fblt_session *s, int32_t batch, int32_t n_new, int32_t block_mode, int32_t window,
+                                   float scale, const float *q_new, const float *k_new, const float *v_new, float *out,
+                                   int32_t advance) {
+    using namespace fblt;
+    if (!s || !q_new || !k_new || !v_new || !out) return fail(FBLT_ERR_ARG, "session_decode: NULL argument");
+    if (batch < 0 || batch > s->max_batch || !s->kc) return fail(FBLT_ERR_CAPACITY, "session_decode: batch %d exceeds the session", batch);
+    if (n_new < 1 || n_new > s->max_new) return fail(FBLT_ERR_CAPACITY, "session_decode: n_new %d outside 1..%d", n_new, s->max_new);
+    if (advance < 0 || advance > n_new) return fail(FBLT_ERR_ARG, "session_decode: advance must be in 0..n_new");
+    if (batch == 0) return FBLT_OK;
+    int32_t max_len = 0;
+    for (int b = 0; b < batch; ++b) {
+        if (s->h_lens[b] + n_new > s->cache_rows) return fail(FBLT_ERR_CAPACITY, "session_decode: sequence %d would exceed cache_rows %d", b, s->cache_rows);
+        max_len = s->h_lens[b] + n_new > max_len ? s->h_lens[b] + n_new : max_len;
+    }
+    const size_t nb = (size_t)batch * n_new * s->E * sizeof(float);
+    FBLT_CUDA_TRY(cudaMemcpyAsync(s->d_lens, s->h_lens, (size_t)batch * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    FBLT_CUDA_TRY(cudaMemcpyAsync(s->d_qn, q_new, nb, cudaMemcpyHostToDevice, s->stream));
+    FBLT_CUDA_TRY(cudaMemcpyAsync(s->d_kn, k_new, nb, cudaMemcpyHostToDevice, s->stream));
+    FBLT_CUDA_TRY(cudaMemcpyAsync(s->d_vn, v_new, nb, cudaMemcpyHostToDevice, s->stream));
+    fblt_decode_desc d;
+    memset(&d, 0, sizeof(d));
+    d.batch = batch;
+    d.num_heads = s->H;
+    d.head_dim = s->hd;
+    d.n_new = n_new;
+    d.block_mode = block_mode;
+    d.window = window;
+    d.max_len = max_len;
+    d.base_len = s->d_lens;
+    d.k_cache = s->kc;
+    d.v_cache = s->vc;
+    d.cache_seq_stride = (int64_t)s->cache_rows * s->E;
+    d.cache_row_stride = s->E;
+    d.q = s->d_qn;
+    d.q_stride = s->E;
+    d.k_new = s->d_kn;
+    d.v_new = s->d_vn;
+    d.kv_new_stride = s->E;
+    d.out = s->d_on;
+    d.out_stride = s->E;
+    d.scale = scale;
+    if (fblt_attn_decode_workspace(&d) > s->ws_bytes) d.splits = 1;
+    int st = fblt_attn_decode(&d, s->ws, s->ws_bytes, s->stream);
+    if (st != FBLT_OK) return st;
+    FBLT_CUDA_TRY(cudaMemcpyAsync(out, s->d_on, nb, cudaMemcpyDeviceToHost, s->stream));
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    for (int b = 0; b < batch; ++b) s->h_lens[b] += advance;
+    return FBLT_OK;
+}
+
+extern "C" int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch) {
+    using namespace fblt;
+    if (!s || !lens_out || batch < 0 || batch > s->max_batch) return fail(FBLT_ERR_ARG, "cache_lens: bad arguments");
+    memcpy(lens_out, s->h_lens, (size_t)batch * sizeof(int32_t));
+    return FBLT_OK;
+}

@@ -1,0 +1,418 @@
+/*
+ * fblt_attn.h -- C ABI of the B200 (sm_100a) attention path for fBLT.
+ *
+ * Two levels:
+ *
+ *   L0  strict drop-in for the reference backend symbols that core/backend.c
+ *       links against (core/backend.c:66-67, 484-487): one sequence, one head,
+ *       dense additive mask, reference struct layout, reference error
+ *       convention (print + exit(1)).
+ *
+ *   L1  batched entry points (all sequences and all heads per launch, varlen,
+ *       mask given as a descriptor derived from the patcher's boundary array,
+ *       never a dense matrix). These return an int status and never exit.
+ *
+ * All tensors are fp32. Pointers named "device" must be CUDA device pointers
+ * of the current device; everything else is host memory. No entry point
+ * requires the caller to synchronise; work is ordered on the stream passed in
+ * (NULL = the legacy default stream, which is what the reference uses,
+ * ops/memory.cu:54-77).
+ *
+ * There is no CPU fallback anywhere in this library.
+ */
+#ifndef FBLT_ATTN_H
+#define FBLT_ATTN_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------ */
+/* status                                                                    */
+/* ------------------------------------------------------------------------ */
+
+typedef enum {
+    FBLT_OK = 0,
+    FBLT_ERR_ARG = 1,         /* NULL pointer, bad stride, bad size          */
+    FBLT_ERR_UNSUPPORTED = 2, /* shape the requested kernel cannot run       */
+    FBLT_ERR_WORKSPACE = 3,   /* workspace missing or too small              */
+    FBLT_ERR_CUDA = 4,        /* a CUDA runtime call failed                  */
+    FBLT_ERR_CAPACITY = 5,    /* KV cache / session capacity exceeded        */
+    FBLT_ERR_LIMIT = 6        /* size beyond a documented fixed maximum      */
+} fblt_status;
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char *fblt_last_error(void);
+const char *fblt_status_string(int status);
+/* Library build identification: "fblt_attn sm_100a <n>". */
+const char *fblt_version(void);
+
+/* ------------------------------------------------------------------------ */
+/* L0: single-head operator, reference layout                                */
+/* ------------------------------------------------------------------------ */
+
+/* Values of the reference's blt_backend enum (core/tensor.h:15). */
+enum { FBLT_BACKEND_CPU = 0, FBLT_BACKEND_CUDA = 1 };
+
+/*
+ * Field-for-field layout of blt_attention_head_args (ops/attn_core.h:25-44);
+ * a pointer to either type may be passed to the L0 symbols.
+ *
+ *   scores_ij = dot(q_i, k_j); w = softmax(scale*scores + mask); out = w @ v
+ *   `mask` (additive, [nq*nk]) wins over is_causal; with mask == NULL and
+ *   is_causal, keys j > i are masked. The row maximum is taken over finite
+ *   entries only; non-finite entries get weight 0; a row with no finite entry
+ *   produces zeros (ops/vecmath_cpu.c:16-53). Only head_dim columns at
+ *   combined_col_offset are written (ops/attn_core_cpu.c:39-55).
+ */
+typedef struct {
+    const float *q;
+    size_t q_stride;
+    const float *k;
+    size_t k_stride;
+    const float *v;
+    size_t v_stride;
+    float *combined;
+    size_t combined_stride;
+    size_t combined_col_offset;
+    float *weights_out;    /* optional [nq*nk]: post-softmax weights          */
+    float *lse_out;        /* optional [nq*2]: (row max m, row sum l)          */
+    float *scores_scratch; /* optional; unused here (no global score buffer)   */
+    const float *mask;     /* optional [nq*nk] additive mask                   */
+    size_t nq;
+    size_t nk;
+    size_t head_dim;
+    bool is_causal;
+    float scale;
+} fblt_head_args;
+
+/*
+ * Replaces blt_attention_head_core_cuda (ops/attn_core.cu:288-312; declared
+ * for the dispatcher at core/backend.c:66). Same preconditions and the same
+ * failure mode: a violated requirement prints "BLT Fatal Error ..." to stderr
+ * and exits (core/backend.h:13-31). Launches on the default stream.
+ */
+void blt_attention_head_core_cuda(int backend, const fblt_head_args *args);
+
+/*
+ * Link stub for blt_attention_head_core_backward_cuda (ops/attn_core.cu:505,
+ * core/backend.c:67). Training is outside this library: calling it is fatal,
+ * which is the reference's own convention for an unavailable backend op
+ * (core/backend.c:102).
+ */
+void blt_attention_head_core_backward_cuda(int backend, const void *bwd_args);
+
+/* Status-returning form of the same operator on an explicit stream. */
+int fblt_attention_head(const fblt_head_args *args, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* patch boundary helpers (host, integer logic)                              */
+/* ------------------------------------------------------------------------ */
+
+/* Layout of blt_patch_info (models/patcher.h:16-20). */
+typedef struct {
+    size_t start_idx;
+    size_t length;
+    float peak_entropy;
+} fblt_patch_info;
+
+/*
+ * Boundary array of one sequence: bounds[p] = first byte of patch p,
+ * bounds[num_patches] = one past the last byte. Requires the patches to tile
+ * [0, seq_len) contiguously with no empty patch, like
+ * blt_patch_build_group_ids (ops/patch_pool_cpu.c:98-112). Returns FBLT_OK or
+ * FBLT_ERR_ARG.
+ */
+int fblt_patch_bounds(const fblt_patch_info *patches, size_t num_patches, size_t seq_len, int32_t *bounds_out);
+
+/*
+ * Decoder latent index of byte `pos` (Fast-BLT 3.1.1), as
+ * blt_patch_decoder_latent_at (ops/patch_pool_cpu.c:114-131) computes it, from
+ * a boundary array: final byte of a non-last patch j -> j; any other byte of
+ * patch j -> max(j-1, 0); pos before bounds[0] -> 0; pos at or past the end ->
+ * num_patches-1.
+ */
+int32_t fblt_patch_latent_at(const int32_t *bounds, int32_t num_patches, int32_t pos);
+
+/* ------------------------------------------------------------------------ */
+/* L1: mask descriptor                                                       */
+/* ------------------------------------------------------------------------ */
+
+typedef enum {
+    FBLT_GROUP_NONE = 0,
+    /* Encoder cross-attention (models/local_encoder.c:70-74): query row i is
+     * sub-token i of patch i / subtokens; key row j is byte j; allowed iff
+     * byte j lies in that patch. */
+    FBLT_GROUP_PATCH_ENC = 1,
+    /* Decoder cross-attention, reference rule (models/local_decoder.c:82-94,
+     * infer/kv_cache.c:206-218): query row i is byte q_pos_offset + i; key row
+     * j is sub-token j; allowed iff j / subtokens == latent_at(byte); with
+     * trailing_closed the last query row of the sequence reads latent P-1. */
+    FBLT_GROUP_PATCH_DEC = 2,
+    /* Decoder cross-attention, "patches <= its patch" rule: allowed iff
+     * j / subtokens <= patch containing the byte (bytes past the end -> P-1). */
+    FBLT_GROUP_PATCH_LEQ = 3,
+    /* Explicit ids per packed row: q_group_ids[i] == k_group_ids[j]
+     * (ops/mask_builder_cpu.c:82-88). Runs on the per-row kernel only. */
+    FBLT_GROUP_IDS = 4
+} fblt_group_rule;
+
+/*
+ * Batched counterpart of blt_mask_config (ops/mask_builder.h:12-32) plus the
+ * INFER rule of blt_block_diffusion_config (ops/mask_builder.h:55-68).
+ * Within one sequence, with i/j the row indices local to that sequence:
+ *
+ *   allowed(i,j) =  (!is_causal  || j <= i + causal_offset)
+ *                && (window == 0 || dist < window)     dist = |i + causal_offset - j| if causal else |i - j|
+ *                && (no docs     || doc(i) == doc(j))
+ *                && group rule
+ *                && (group rule == NONE || bidirectional_within_group || j <= i)
+ *
+ * and, when num_clean is given (block-diffusion INFER), the first two lines are
+ * replaced by: i < N ? (j < N && j <= i) : true   (ops/mask_builder_cpu.c:127-135).
+ *
+ * All array members are device pointers to int32 (uint8 for trailing_closed);
+ * NULL means "absent".
+ */
+typedef struct {
+    int32_t is_causal;
+    int32_t sliding_window;
+    int32_t group_rule; /* fblt_group_rule */
+    int32_t subtokens;  /* k >= 1 sub-tokens per patch (PATCH_* rules) */
+    int32_t bidirectional_within_group;
+    int32_t reserved;
+    const int32_t *causal_offset;   /* [batch] */
+    const int32_t *cu_doc;          /* [batch+1] offsets into doc_bounds */
+    const int32_t *doc_bounds;      /* per sequence: first position of document d+1, ascending */
+    const int32_t *cu_patch;        /* [batch+1] offsets into patch_bounds; sequence b owns P_b + 1 entries */
+    const int32_t *patch_bounds;    /* per sequence: fblt_patch_bounds() output */
+    const int32_t *q_pos_offset;    /* [batch] byte position of the first query row (PATCH_DEC / PATCH_LEQ) */
+    const uint8_t *trailing_closed; /* [batch] (PATCH_DEC) */
+    const int32_t *q_group_ids;     /* [total q rows] (GROUP_IDS) */
+    const int32_t *k_group_ids;     /* [total k rows] (GROUP_IDS) */
+    const int32_t *num_clean;       /* [batch] N: switches on the block-diffusion INFER rule */
+} fblt_mask_desc;
+
+/* ------------------------------------------------------------------------ */
+/* L1: batched prefill / cross attention                                     */
+/* ------------------------------------------------------------------------ */
+
+typedef enum {
+    FBLT_IMPL_AUTO = 0,   /* pick per shape */
+    FBLT_IMPL_ROW = 1,    /* one warp per (query row, head), fp32 FMA; any head_dim % 4 == 0 up to 256, any mask */
+    FBLT_IMPL_TILE = 2    /* tensor-core tiles (head_dim 32/64/128, range masks) */
+} fblt_impl;
+
+typedef enum {
+    FBLT_PREC_FP32 = 0, /* fp32-equivalent: error-compensated 3xTF32 on tensor cores, plain fp32 on the row kernel */
+    FBLT_PREC_TF32 = 1  /* single-pass TF32 tensor cores (tile kernel only) */
+} fblt_precision;
+
+/*
+ * One call = every (sequence, head) of a batch. Sequence b owns query rows
+ * [cu_q[b], cu_q[b+1]) of q/out and key rows [cu_k[b], cu_k[b+1]) of k/v (for
+ * self-attention pass the same table twice). Head h lives at columns
+ * [h*head_dim, (h+1)*head_dim) of every row, which covers the packed
+ * [T, 3E] layout of models/attention.c:95-107 (q = base, k = base + E,
+ * v = base + 2E, strides 3E) as well as the [rows, E] layout of
+ * models/cross_attention.c:78-86.
+ *
+ * Replaces the per-head loops at models/attention.c:199-202,
+ * models/cross_attention.c:147-150, models/block_diffusion.c:293-319.
+ * A query row with no allowed key yields zeros.
+ */
+typedef struct {
+    int32_t batch;
+    int32_t num_heads;
+    int32_t head_dim;
+    int32_t max_q; /* host-known upper bound of rows per sequence (grid sizing) */
+    int32_t max_k;
+    int32_t impl;      /* fblt_impl */
+    int32_t precision; /* fblt_precision */
+    int32_t reserved;
+    const int32_t *cu_q; /* device [batch+1] */
+    const int32_t *cu_k; /* device [batch+1] */
+    const float *q;      /* device */
+    int64_t q_stride;    /* elements per row */
+    const float *k;
+    int64_t k_stride;
+    const float *v;
+    int64_t v_stride;
+    float *out;
+    int64_t out_stride;
+    float scale;
+    int32_t reserved2;
+    fblt_mask_desc mask;
+} fblt_attn_desc;
+
+int fblt_attn_forward(const fblt_attn_desc *desc, void *stream);
+
+/*
+ * Debug / parity: writes allowed(i,j) as bytes (1/0) for sequence-local
+ * (i,j) into bitmap[b * max_q * max_k + i * max_k + j] (device). `use_range`
+ * != 0 evaluates the [lo,hi) key range the tile and streaming kernels use
+ * instead of the per-pair predicate; both must equal the reference's dense
+ * mask (ops/mask_builder_cpu.c:49-94) wherever the rule is a range.
+ * FBLT_ERR_UNSUPPORTED if use_range is asked for GROUP_IDS.
+ */
+int fblt_mask_bitmap(const fblt_attn_desc *desc, uint8_t *bitmap, int use_range, void *stream);
+
+/*
+ * Dense additive fp32 mask (0 / -inf) for one sequence of the descriptor,
+ * [nq, nk] row-major into device memory: what a kept
+ * blt_build_attention_mask_cuda / blt_build_block_diffusion_mask_cuda
+ * (core/backend.c:190-192) would hand back to callers that still want a
+ * tensor. *empty_rows_out (host, optional) receives the number of query rows
+ * with no allowed key, the condition the reference treats as fatal
+ * (ops/mask_builder_cpu.c:93).
+ */
+int fblt_mask_materialize(const fblt_attn_desc *desc, int32_t seq, float *mask_out, int32_t *empty_rows_out,
+                          void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* L1: KV-cache decode / block verify                                        */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Attention of n_new fresh query rows per sequence over that sequence's KV
+ * cache: the two per-head loops of blt_kv_decode_step
+ * (infer/kv_cache.c:369-390) for every sequence and head at once, with the
+ * visibility rule of infer/kv_cache.c:229-236 evaluated in the kernel:
+ *
+ *   block_mode == 0: row r (position p = base + r) sees key j iff
+ *                    j <= p && (window == 0 || p - j < window)
+ *   block_mode == 1: every row sees all base + n_new keys (the block rows of
+ *                    the INFER mask, ops/mask_builder_cpu.c:130-135).
+ *
+ * Cache row = absolute byte position (infer/kv_cache.h:45-65); sequence b's
+ * rows start at cache + b * cache_seq_stride. When k_new/v_new are given, the
+ * kernel attends to them as rows [base, base + n_new) and also writes them
+ * into the cache (the write-through of infer/kv_cache.c:352-365); otherwise
+ * the cache must already hold those rows. base_len is not modified.
+ */
+typedef struct {
+    int32_t batch;
+    int32_t num_heads;
+    int32_t head_dim; /* 32, 64 or 128 */
+    int32_t n_new;    /* 1..16 */
+    int32_t block_mode;
+    int32_t window;
+    int32_t max_len;  /* host-known upper bound of base_len[b] + n_new */
+    int32_t splits;   /* key-range splits per (sequence, head); 0 = choose */
+    const int32_t *base_len; /* device [batch] */
+    float *k_cache;          /* device */
+    float *v_cache;
+    int64_t cache_seq_stride; /* elements */
+    int64_t cache_row_stride; /* elements, >= num_heads*head_dim */
+    const float *q;           /* device [batch*n_new rows] */
+    int64_t q_stride;
+    const float *k_new; /* optional device [batch*n_new rows] */
+    const float *v_new;
+    int64_t kv_new_stride;
+    float *out; /* device [batch*n_new rows] */
+    int64_t out_stride;
+    float scale;
+    int32_t reserved;
+} fblt_decode_desc;
+
+/* Bytes of device scratch fblt_attn_decode needs for this descriptor (0 when
+ * the key range is not split). */
+size_t fblt_attn_decode_workspace(const fblt_decode_desc *desc);
+int fblt_attn_decode(const fblt_decode_desc *desc, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* L1: decision step (bit-exact integer / compare logic)                     */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Row argmax with the reference tie rule: strict '>' scan from index 0, so
+ * the lowest index wins (infer/self_speculation.c:21-31,
+ * ops/row_stats.cu:46-83). logits: device [rows, vocab] with row stride
+ * `stride`; ids_out: device [rows].
+ */
+int fblt_argmax_rows(const float *logits, int64_t stride, int32_t rows, int32_t vocab, int32_t *ids_out,
+                     void *stream);
+
+/*
+ * Accept-until-first-mismatch of Algorithm 2 as blt_verify_draft runs it on
+ * the host (infer/self_speculation.c:160-182), for a batch of candidates.
+ * Candidate c has committed length l[c] and draft length r[c]; x is
+ * [batch, x_stride] bytes; pred is the argmax byte of every candidate
+ * position ([batch, pred_stride], pred[p] = argmax of logits row p). For each
+ * candidate writes new_len[c] and fixes x in place exactly as the reference:
+ * first p in [l, l+r) with x[p] != pred[p-1] -> x[p] = pred[p-1], new_len =
+ * p+1; none -> if l+r < target_len: x[l+r] = pred[l+r-1], new_len = l+r+1,
+ * else new_len = l+r. accepted[c] receives the number of accepted draft
+ * bytes. All pointers device.
+ */
+int fblt_verify_accept(uint8_t *x, int64_t x_stride, const int32_t *pred, int64_t pred_stride, const int32_t *l,
+                       const int32_t *r, const int32_t *target_len, int32_t batch, int32_t *new_len,
+                       int32_t *accepted, void *stream);
+
+/* Host mirrors of the selection helpers (same names minus the prefix, same
+ * results): blt_unmask_select_confidence / _eb (infer/block_generation.c:20-58),
+ * blt_aligned_commit_select (infer/self_speculation.c:73-80),
+ * blt_block_adapt_b (infer/block_generation.c:139-152). */
+uint32_t fblt_unmask_select_confidence(const float *scores, const uint8_t *masked, size_t B, float alpha);
+uint32_t fblt_unmask_select_eb(const float *scores, const uint8_t *masked, size_t B, float gamma);
+size_t fblt_aligned_commit_select(const fblt_patch_info *patches, size_t num_patches, size_t lo, size_t hi);
+size_t fblt_block_adapt_b(size_t cur_b, double rolling_acceptance, size_t b_min, size_t b_max, float target);
+
+/* ------------------------------------------------------------------------ */
+/* host-buffer sessions (what a host-side caller with no device memory uses) */
+/* ------------------------------------------------------------------------ */
+
+typedef struct fblt_session fblt_session;
+
+/*
+ * A session owns a stream, device staging for one batch and, optionally, a
+ * batched two-array KV cache [batch, cache_rows, E] (the layout
+ * blt_kv_cache_create_batched reserves, infer/kv_cache.h:71-75). All
+ * allocation happens here; the per-step calls below allocate nothing.
+ * max_q_rows / max_k_rows bound the packed row counts of one forward call.
+ */
+int fblt_session_create(fblt_session **out, int32_t max_batch, int32_t num_heads, int32_t head_dim,
+                        int64_t max_q_rows, int64_t max_k_rows, int32_t cache_rows, int32_t max_new);
+void fblt_session_destroy(fblt_session *s);
+
+/*
+ * Host-memory form of fblt_attn_forward: every pointer in `desc` (tensors and
+ * the int32 tables of desc->mask) is HOST memory; rows are copied to the
+ * device, the batch runs, `out` rows are copied back and the call returns
+ * after the stream is idle. q/k/v may alias one packed buffer.
+ * mask.q_group_ids / k_group_ids are not supported here.
+ */
+int fblt_session_forward(fblt_session *s, const fblt_attn_desc *host_desc);
+
+/* Loads `lens[b]` rows of host K/V ([batch, rows_stride_rows, E] with the
+ * given per-sequence stride in rows) into the session cache and sets the
+ * cache lengths. */
+int fblt_session_cache_load(fblt_session *s, int32_t batch, const int32_t *lens, const float *k_host,
+                            const float *v_host, int64_t host_seq_stride_rows);
+/*
+ * One decode / block-verify step from host rows: q_new, k_new, v_new are
+ * [batch*n_new, E] host arrays; rows are written through to the cache, the
+ * attention runs, out ([batch*n_new, E] host) is filled, and every cache
+ * length grows by `advance` (<= n_new; the rows past base + advance are
+ * overwritten by the next step, the rollback of infer/kv_cache.c:252-336).
+ */
+int fblt_session_decode(fblt_session *s, int32_t batch, int32_t n_new, int32_t block_mode, int32_t window,
+                        float scale, const float *q_new, const float *k_new, const float *v_new, float *out,
+                        int32_t advance);
+/* Current cache lengths (host copy), for checks. */
+int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch);
+
+/* Number of kernels this library has launched in this process (all threads). */
+uint64_t fblt_launch_count(void);
+/* sizeof of {fblt_head_args, fblt_patch_info, fblt_mask_desc, fblt_attn_desc,
+ * fblt_decode_desc}, for bindings that re-declare the structs. Returns the count. */
+size_t fblt_abi_sizes(size_t *out, size_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FBLT_ATTN_H */

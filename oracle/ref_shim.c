@@ -1,0 +1,185 @@
+/*
+ * TEST INFRASTRUCTURE -- not part of the product.
+ *
+ * Flat-argument entry points over the reference's own CPU object code, so
+ * that ctypes can call it without re-declaring blt_tensor / blt_arena. This
+ * file is compiled together with the reference's C sources (from where they
+ * are mounted) into oracle/_ref/libblt_ref.so; it contains no arithmetic of
+ * its own -- every result comes from a reference function.
+ *
+ * The reference aborts the process on a violated requirement (for example a
+ * mask row with no allowed key); callers check such inputs with the
+ * restatement first.
+ */
+#include <math.h>
+#include <pthread.h>
+#include <stddef.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+
+#include "core/allocator.h"
+#include "core/backend.h"
+#include "infer/block_generation.h"
+#include "infer/self_speculation.h"
+#include "models/patcher.h"
+#include "ops/attn_core.h"
+#include "ops/mask_builder.h"
+#include "ops/patch_pool.h"
+
+void ref_attention_head(const blt_attention_head_args *a) { blt_attention_head_core(BLT_BACKEND_CPU, a); }
+
+typedef struct {
+    const blt_attention_head_args *jobs;
+    size_t n;
+    size_t *next;
+    pthread_mutex_t *lock;
+} ref_pool;
+
+static void *ref_worker(void *p) {
+    ref_pool *c = (ref_pool *)p;
+    float *scratch = NULL;
+    size_t cap = 0;
+    for (;;) {
+        pthread_mutex_lock(c->lock);
+        size_t idx = (*c->next)++;
+        pthread_mutex_unlock(c->lock);
+        if (idx >= c->n) break;
+        blt_attention_head_args a = c->jobs[idx];
+        if (!a.weights_out && !a.scores_scratch) {
+            size_t need = a.nq * a.nk;
+            if (need > cap) {
+                free(scratch);
+                scratch = (float *)malloc(need * sizeof(float) + 16);
+                cap = need;
+            }
+            a.scores_scratch = scratch;
+        }
+        blt_attention_head_core(BLT_BACKEND_CPU, &a);
+    }
+    free(scratch);
+    return NULL;
+}
+
+/* Independent head jobs over a thread pool; the reference operator itself is
+ * untouched and single-threaded per job. Returns wall seconds. */
+double ref_run_heads(const blt_attention_head_args *jobs, size_t n, int nthreads) {
+    if (nthreads < 1) nthreads = 1;
+    size_t next = 0;
+    pthread_mutex_t lock = PTHREAD_MUTEX_INITIALIZER;
+    ref_pool ctx = {jobs, n, &next, &lock};
+    struct timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    if (nthreads == 1) {
+        ref_worker(&ctx);
+    } else {
+        pthread_t *th = (pthread_t *)malloc(sizeof(pthread_t) * (size_t)nthreads);
+        for (int t = 0; t < nthreads; ++t) pthread_create(&th[t], NULL, ref_worker, &ctx);
+        for (int t = 0; t < nthreads; ++t) pthread_join(th[t], NULL);
+        free(th);
+    }
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    return (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
+}
+
+void ref_build_mask(size_t nq, size_t nk, size_t window, const size_t *doc_boundaries, size_t num_docs,
+                    const size_t *q_groups, const size_t *k_groups, int bidirectional, int is_causal,
+                    size_t causal_offset, float *out) {
+    blt_arena *arena = blt_arena_create(nq * nk * sizeof(float) + (nq + nk) * 2 * sizeof(size_t) + 4096,
+                                        BLT_BACKEND_CPU);
+    blt_mask_config cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.seq_len_q = nq;
+    cfg.seq_len_kv = nk;
+    cfg.sliding_window = window;
+    cfg.doc_boundaries = doc_boundaries;
+    cfg.num_docs = num_docs;
+    cfg.query_group_ids = q_groups;
+    cfg.kv_group_ids = k_groups;
+    cfg.bidirectional_within_group = bidirectional != 0;
+    cfg.is_causal = is_causal != 0;
+    cfg.causal_offset = causal_offset;
+    blt_tensor m;
+    memset(&m, 0, sizeof(m));
+    blt_build_attention_mask(&cfg, &m, arena);
+    memcpy(out, m.data, nq * nk * sizeof(float));
+    blt_arena_destroy(arena);
+}
+
+void ref_block_diffusion_mask(int mode, size_t S, size_t N, size_t B, const size_t *block_starts,
+                              size_t num_blocks, float *out) {
+    blt_arena *arena = blt_arena_create(S * S * sizeof(float) + 4096, BLT_BACKEND_CPU);
+    blt_block_diffusion_config cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.mode = mode == 1 ? BLT_BDM_INFER : BLT_BDM_TRAIN;
+    cfg.seq_len = S;
+    cfg.num_clean = N;
+    cfg.block_size = B;
+    cfg.block_starts = block_starts;
+    cfg.num_blocks = num_blocks;
+    blt_tensor m;
+    memset(&m, 0, sizeof(m));
+    blt_build_block_diffusion_mask(&cfg, &m, arena);
+    memcpy(out, m.data, S * S * sizeof(float));
+    blt_arena_destroy(arena);
+}
+
+void ref_patch_group_ids(const blt_patch_info *patches, size_t num_patches, size_t seq_len, size_t *q_groups,
+                         size_t *k_groups) {
+    blt_patch_build_group_ids(patches, num_patches, seq_len, q_groups, k_groups);
+}
+
+size_t ref_decoder_latent_at(const blt_patch_info *patches, size_t num_patches, size_t pos) {
+    return blt_patch_decoder_latent_at(patches, num_patches, pos);
+}
+
+void ref_expand_group_ids(const size_t *in, size_t n, size_t k, size_t *out) {
+    blt_patch_expand_group_ids(in, n, k, out);
+}
+
+uint32_t ref_unmask_select_confidence(const float *s, const uint8_t *m, size_t B, float alpha) {
+    return blt_unmask_select_confidence(s, m, B, alpha);
+}
+uint32_t ref_unmask_select_eb(const float *s, const uint8_t *m, size_t B, float gamma) {
+    return blt_unmask_select_eb(s, m, B, gamma);
+}
+size_t ref_block_adapt_b(size_t cur, double acc, size_t lo, size_t hi, float target) {
+    return blt_block_adapt_b(cur, acc, lo, hi, target);
+}
+size_t ref_aligned_commit_select(const blt_patch_info *p, size_t n, size_t lo, size_t hi) {
+    return blt_aligned_commit_select(p, n, lo, hi);
+}
+
+/* sizeof / offsetof of the ABI structs, for the layout check of include/fblt_attn.h. */
+size_t ref_struct_layout(size_t *out, size_t cap) {
+    const size_t v[] = {
+        sizeof(blt_attention_head_args),
+        offsetof(blt_attention_head_args, q),
+        offsetof(blt_attention_head_args, q_stride),
+        offsetof(blt_attention_head_args, k),
+        offsetof(blt_attention_head_args, k_stride),
+        offsetof(blt_attention_head_args, v),
+        offsetof(blt_attention_head_args, v_stride),
+        offsetof(blt_attention_head_args, combined),
+        offsetof(blt_attention_head_args, combined_stride),
+        offsetof(blt_attention_head_args, combined_col_offset),
+        offsetof(blt_attention_head_args, weights_out),
+        offsetof(blt_attention_head_args, lse_out),
+        offsetof(blt_attention_head_args, scores_scratch),
+        offsetof(blt_attention_head_args, mask),
+        offsetof(blt_attention_head_args, nq),
+        offsetof(blt_attention_head_args, nk),
+        offsetof(blt_attention_head_args, head_dim),
+        offsetof(blt_attention_head_args, is_causal),
+        offsetof(blt_attention_head_args, scale),
+        sizeof(blt_patch_info),
+        offsetof(blt_patch_info, start_idx),
+        offsetof(blt_patch_info, length),
+        offsetof(blt_patch_info, peak_entropy),
+        (size_t)BLT_BACKEND_CPU,
+        (size_t)BLT_BACKEND_CUDA,
+    };
+    const size_t n = sizeof(v) / sizeof(v[0]);
+    for (size_t i = 0; i < n && i < cap; ++i) out[i] = v[i];
+    return n;
+}

@@ -1,0 +1,21 @@
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+
+
+@pytest.fixture(scope="session")
+def cuda_lib():
+    """The CUDA library, loaded for real: GPU tests never run on a substitute."""
+    import torch
+    assert torch.cuda.is_available(), "gpu-marked test collected without a GPU"
+    from fblt_b200 import lib
+    return lib.load()
