@@ -1,0 +1,438 @@
+"""Benchmark of the attention path on the scaled batch-sharded workload.
+
+One step = one pass of the hot path over the whole batch: block-causal patch-transformer
+prefill attention (16 heads x 64, patch structure from the seeded generator) followed by 64
+KV-cache decode steps with a block of 4 verify rows (cache 512 -> 768 rows), for 2048
+independent sequences sharded by batch over the ranks; outputs are gathered over NCCL when
+the batch is partitioned.
+
+    python bench.py [--gpus N --steps K --warmup W]            # this library
+    python bench.py --impl reference [...]                     # reference CPU operator, host cores
+    torchrun --nproc-per-node N bench.py --gpus N ...           # one rank per GPU
+
+Prints ONE JSON line (rank 0). `value` is algorithmic attention bytes per second with inputs
+resident in HBM; `e2e` is the same metric through the host-buffer C ABI (sessions) with all
+host<->device copies inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "attn_algorithmic_bytes_per_s"
+UNIT = "GB/s"
+H, HD, E = 16, 64, 1024
+N_NEW, BASE_LEN = 4, 512
+SCALE = 0.125
+
+
+# ----------------------------------------------------------------------------- workload arithmetic
+
+def prefill_bytes(rows: int) -> int:
+    """Q, K, V rows read once and O rows written once (fp32)."""
+    return 4 * E * 4 * rows
+
+
+def decode_bytes(batch: int, base: int) -> int:
+    """One block-verify step: K and V of base + 4 rows per sequence read once, q read, out written."""
+    return 4 * E * (2 * batch * (base + N_NEW) + 2 * batch * N_NEW)
+
+
+def job_bytes(rows: int, batch: int, decode_steps: int) -> int:
+    return prefill_bytes(rows) + sum(decode_bytes(batch, BASE_LEN + N_NEW * t) for t in range(decode_steps))
+
+
+# ----------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------- CPU reference legs
+
+def cpu_sample(qkv: np.ndarray, cu: np.ndarray, kc: np.ndarray, vc: np.ndarray, qn: np.ndarray, kn: np.ndarray,
+               vn: np.ndarray, step_ids, total_batch: int, total_rows: int, decode_steps: int, threads: int,
+               use_ref: bool):
+    """Times the reference CPU operator on a bounded sample of the workload and scales it to
+    the whole job: `qkv`/`cu` are a sample of prefill sequences, kc/vc/qn/kn/vn a sample of
+    decode sequences evaluated at the decode steps in `step_ids`. Returns
+    (estimated job seconds, outputs for checking, description)."""
+    from oracle import binding as ob
+    nb = len(cu) - 1
+    t_mask0 = time.perf_counter()
+    masks = [ob.build_mask(int(cu[b + 1] - cu[b]), int(cu[b + 1] - cu[b]), is_causal=True, use_ref=use_ref)[0]
+             for b in range(nb)]
+    t_mask = time.perf_counter() - t_mask0
+    out_p, t_pre = ob.batched_attention(qkv, qkv, qkv, cu, cu, H, HD, SCALE, masks, k_col0=E, v_col0=2 * E,
+                                        use_ref=use_ref, nthreads=threads)
+    db = kc.shape[0]
+    outs_d, t_dec = [], 0.0
+    for t in step_ids:
+        base = BASE_LEN + N_NEW * t
+        jobs = ob.HeadJobs()
+        out_d = np.zeros((db * N_NEW, E), np.float32)
+        mask = np.zeros((N_NEW, base + N_NEW), np.float32)   # block rows see every key
+        kk = np.ascontiguousarray(np.concatenate([kc[:, :base], kn.reshape(db, N_NEW, E)], axis=1))
+        vv = np.ascontiguousarray(np.concatenate([vc[:, :base], vn.reshape(db, N_NEW, E)], axis=1))
+        for b in range(db):
+            for h in range(H):
+                c = h * HD
+                jobs.add(qn, kk[b], vv[b], out_d, col=c, head_dim=HD, q_col=c, k_col=c, v_col=c, scale=SCALE,
+                         mask=mask, nq=N_NEW, nk=base + N_NEW, q_row=b * N_NEW)
+        t_dec += jobs.run(threads, use_ref)
+        outs_d.append(out_d)
+    prefill_rows = int(cu[-1])
+    est = t_pre * (total_rows / max(prefill_rows, 1)) + \
+        (t_dec / max(len(step_ids), 1)) * decode_steps * (total_batch / max(db, 1))
+    desc = (f"{nb} of {total_batch} sequences prefill ({prefill_rows} rows, {t_pre:.2f}s) + {db} sequences x "
+            f"{len(step_ids)} of {decode_steps} decode steps ({t_dec:.2f}s), scaled linearly; dense mask build "
+            f"{t_mask:.2f}s not included")
+    return est, out_p, outs_d, desc
+
+
+def run_reference_arm(args):
+    """The reference's own CPU attention operator on the box's host cores, bounded sample per step."""
+    from fblt_b200 import workloads
+    from oracle import binding as ob
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    use_ref = ob.have_ref()
+    threads = ob.host_cores()
+    case = workloads.c5_prefill(batch=args.batch, with_tensors=False)
+    total_rows = int(case.cu_q[-1])
+    nb, db = min(args.cpu_prefill_seqs, args.batch), min(args.cpu_decode_seqs, args.batch)
+    cu = (case.cu_q[: nb + 1] - case.cu_q[0]).astype(np.int32)
+    rng = np.random.default_rng(4)
+    qkv = rng.standard_normal((int(cu[-1]), 3 * E), dtype=np.float32) * 0.125
+    rows = BASE_LEN + N_NEW * args.decode_steps
+    kc = rng.standard_normal((db, rows, E), dtype=np.float32)
+    vc = rng.standard_normal((db, rows, E), dtype=np.float32)
+    qn, kn, vn = (rng.standard_normal((db * N_NEW, E), dtype=np.float32) for _ in range(3))
+    step_ids = list(range(0, args.decode_steps, max(1, args.decode_steps // args.cpu_decode_steps)))[: args.cpu_decode_steps]
+    ests, desc = [], ""
+    for it in range(args.warmup + args.steps):
+        est, _, _, desc = cpu_sample(qkv, cu, kc, vc, qn, kn, vn, step_ids, args.batch, total_rows, args.decode_steps,
+                                     threads, use_ref)
+        if it >= args.warmup:
+            ests.append(est)
+    sec = statistics.mean(ests)
+    value = job_bytes(total_rows, args.batch, args.decode_steps) / sec / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, total_rows),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "reference" if use_ref else "port",
+                         "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, total_rows: int) -> dict:
+    return {"workload": "scaled batch-sharded prefill+decode (config 5): block-causal patch attention + "
+                        f"{args.decode_steps} block-verify decode steps (B=4) over the KV cache",
+            "sequences": args.batch, "patch_rows": total_rows, "heads": H, "head_dim": HD, "cache_rows_start": BASE_LEN,
+            "block": N_NEW, "decode_steps": args.decode_steps, "parallelism": f"batch-sharded x{args.gpus}",
+            "l2": "inputs larger than L2 (>= 8 GB streamed per decode launch set)"}
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=2048, help="total sequences over all ranks")
+    ap.add_argument("--decode-steps", type=int, default=64)
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--cpu-prefill-seqs", type=int, default=128)
+    ap.add_argument("--cpu-decode-seqs", type=int, default=32)
+    ap.add_argument("--cpu-decode-steps", type=int, default=4)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from fblt_b200 import lib as L
+    from fblt_b200 import ops, shard, workloads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the attention path has no CPU fallback")
+    lib = L.load()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
+
+    # ---- this rank's shard ---------------------------------------------------
+    case = workloads.c5_prefill(batch=args.batch, with_tensors=False)
+    total_rows = int(case.cu_q[-1])
+    ranges = shard.partition(args.batch, world)
+    s0, s1 = ranges[rank]
+    B = s1 - s0
+    cu = (case.cu_q[s0: s1 + 1] - case.cu_q[s0]).astype(np.int32)
+    rows = int(cu[-1])
+    rows_per_rank = [int(case.cu_q[e] - case.cu_q[b]) for b, e in ranges]
+    cache_rows = BASE_LEN + N_NEW * args.decode_steps
+    gen = torch.Generator(device=dev).manual_seed(4 + 1000 * rank)
+    qkv = torch.randn((rows, 3 * E), generator=gen, device=dev) * 0.125
+    out_p = torch.empty((rows, E), device=dev)
+    kc = torch.randn((B, cache_rows, E), generator=gen, device=dev)
+    vc = torch.randn((B, cache_rows, E), generator=gen, device=dev)
+    qn = torch.randn((B * N_NEW, E), generator=gen, device=dev)
+    kn = torch.randn((B * N_NEW, E), generator=gen, device=dev)
+    vn = torch.randn((B * N_NEW, E), generator=gen, device=dev)
+    out_d = torch.empty((args.decode_steps, B * N_NEW, E), device=dev)
+    lens_all = (BASE_LEN + N_NEW * torch.arange(args.decode_steps, device=dev, dtype=torch.int32))[:, None] \
+        .expand(args.decode_steps, B).contiguous()
+    pre = ops.make_batch(qkv[:, 0:E], qkv[:, E:2 * E], qkv[:, 2 * E:], out_p, cu, cu, H, HD, SCALE,
+                         ops.MaskConfig(is_causal=True))
+    dec = [ops.make_decode(kc, vc, lens_all[t], qn, out_d[t], H, HD, N_NEW, SCALE, block_mode=True, k_new=kn,
+                           v_new=vn, max_len=BASE_LEN + N_NEW * (t + 1)) for t in range(args.decode_steps)]
+    ws = ops.decode_workspace(dec[-1])
+
+    main_stream = torch.cuda.Stream(device=dev)
+    comm_stream = torch.cuda.Stream(device=dev)
+    if world > 1:
+        max_rows = max(rows_per_rank)
+        pad_p = torch.zeros((max_rows, E), device=dev)
+        gath_p = torch.empty((world, max_rows, E), device=dev)
+        gath_d = torch.empty((world, args.decode_steps * B * N_NEW, E), device=dev)
+        equal = len({e - b for b, e in ranges}) == 1
+        assert equal, "decode gather assumes equal sequence counts per rank"
+
+    ev_pre_done = torch.cuda.Event()
+    dec_t0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.warmup + args.steps)]
+    dec_t1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.warmup + args.steps)]
+
+    def one_step(it: int):
+        with torch.cuda.stream(main_stream):
+            ops.attn_forward(pre, main_stream)
+            if world > 1:
+                ev_pre_done.record(main_stream)
+                comm_stream.wait_event(ev_pre_done)
+                with torch.cuda.stream(comm_stream):   # prefill rows travel while decode runs
+                    shard.gather_rows(out_p, rows_per_rank, padded=pad_p, gathered=gath_p)
+            dec_t0[it].record(main_stream)
+            for t in range(args.decode_steps):
+                ops.attn_decode(dec[t], ws, main_stream)
+            dec_t1[it].record(main_stream)
+            if world > 1:
+                dist.all_gather_into_tensor(gath_d.view(-1, E), out_d.view(-1, E))
+                main_stream.wait_stream(comm_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for it in range(args.warmup):
+        one_step(it)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = lib.fblt_launch_count()
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_begin.record(main_stream)
+    for it in range(args.steps):
+        one_step(args.warmup + it)
+    t_end.record(main_stream)
+    barrier()
+    launches = lib.fblt_launch_count() - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    ms = t_begin.elapsed_time(t_end)
+    dec_ms = sum(dec_t0[args.warmup + i].elapsed_time(dec_t1[args.warmup + i]) for i in range(args.steps))
+    if world > 1:
+        tt = torch.tensor([ms, dec_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, dec_ms = float(tt[0]), float(tt[1])
+        lt = torch.tensor([launches], device=dev, dtype=torch.int64)
+        dist.all_reduce(lt)
+        launches = int(lt[0])
+    ms_per_step = ms / args.steps
+    total_bytes = job_bytes(total_rows, args.batch, args.decode_steps)
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- roofline of the dominant kernel (block-verify decode) ------------------
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    launch_ms = dec_ms / (args.steps * args.decode_steps)
+    launch_bytes = sum(decode_bytes(B, BASE_LEN + N_NEW * t) for t in range(args.decode_steps)) / args.decode_steps
+    achieved = launch_bytes / (launch_ms * 1e-3) / 1e9
+    roofline = {"kernel": "decode_attn_kernel<64,4>", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_source": peak_src, "launch_ms": launch_ms,
+                "algorithmic_bytes_per_launch": launch_bytes, "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE and
+                NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * launch_bytes}
+
+    # ---- host-buffer leg (sessions): copies inside the timed region -------------
+    e2e = None
+    if not args.no_e2e:
+        e2e = run_e2e(args, torch, ops, dev, qkv, cu, rows, B, cache_rows, kc, vc, qn, kn, vn, world, total_bytes, barrier)
+
+    # ---- CPU baseline on a bounded sample of the same tensors (rank 0, one GPU) ----
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = run_cpu_baseline(args, torch, qkv, cu, kc, vc, qn, kn, vn, out_p, out_d, total_rows)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": workload_config(args, total_rows),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "job_bytes": total_bytes,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in
+# profiles/ (None until captured).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+
+
+def run_e2e(args, torch, ops, dev, qkv, cu, rows, B, cache_rows, kc, vc, qn, kn, vn, world, total_bytes, barrier):
+    import torch.distributed as dist
+    sess = ops.Session(B, H, HD, max_q_rows=rows, max_k_rows=rows, cache_rows=cache_rows, max_new=N_NEW)
+    h_qkv = torch.empty((rows, 3 * E), dtype=torch.float32, pin_memory=True)
+    h_qkv.copy_(qkv)
+    h_out = torch.empty((rows, E), dtype=torch.float32, pin_memory=True)
+    h_kc = torch.empty((B, BASE_LEN, E), dtype=torch.float32, pin_memory=True)
+    h_vc = torch.empty((B, BASE_LEN, E), dtype=torch.float32, pin_memory=True)
+    h_kc.copy_(kc[:, :BASE_LEN])
+    h_vc.copy_(vc[:, :BASE_LEN])
+    h_new = [torch.empty((B * N_NEW, E), dtype=torch.float32, pin_memory=True) for _ in range(3)]
+    for h, d in zip(h_new, (qn, kn, vn)):
+        h.copy_(d)
+    h_od = torch.empty((B * N_NEW, E), dtype=torch.float32, pin_memory=True)
+    torch.cuda.synchronize()
+    lens0 = np.full(B, BASE_LEN, dtype=np.int32)
+    q_h, k_h, v_h = h_qkv[:, 0:E], h_qkv[:, E:2 * E], h_qkv[:, 2 * E:]
+
+    def step():
+        sess.forward(q_h, k_h, v_h, h_out, cu, cu, SCALE, ops.MaskConfig(is_causal=True), q_stride=3 * E,
+                     k_stride=3 * E, v_stride=3 * E, out_stride=E)
+        sess.cache_load(lens0, h_kc, h_vc, BASE_LEN)
+        for _ in range(args.decode_steps):
+            sess.decode(B, N_NEW, h_new[0], h_new[1], h_new[2], h_od, SCALE, block_mode=True)
+
+    step()  # warm-up
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        step()
+    barrier()
+    sec = (time.perf_counter() - t0) / args.e2e_steps
+    if world > 1:
+        tt = torch.tensor([sec], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        sec = float(tt[0])
+    sess.close()
+    h2d = 4 * E * (3 * rows + 2 * B * BASE_LEN + 3 * B * N_NEW * args.decode_steps)
+    d2h = 4 * E * (rows + B * N_NEW * args.decode_steps)
+    return {"value": total_bytes / sec / 1e9, "unit": UNIT, "ms_per_step": sec * 1e3, "h2d_bytes_per_step": h2d * world,
+            "d2h_bytes_per_step": d2h * world,
+            "path": "fblt_session_forward + fblt_session_cache_load + fblt_session_decode on pinned host buffers"}
+
+
+def run_cpu_baseline(args, torch, qkv, cu, kc, vc, qn, kn, vn, out_p, out_d, total_rows):
+    from oracle import binding as ob
+    use_ref = ob.have_ref()
+    threads = ob.host_cores()
+    nb, db = min(args.cpu_prefill_seqs, len(cu) - 1), min(args.cpu_decode_seqs, kc.shape[0])
+    cu_s = cu[: nb + 1].copy()
+    qkv_h = qkv[: int(cu_s[-1])].cpu().numpy()
+    kc_h, vc_h = kc[:db].cpu().numpy(), vc[:db].cpu().numpy()
+    qn_h, kn_h, vn_h = (x[: db * N_NEW].cpu().numpy() for x in (qn, kn, vn))
+    step_ids = list(range(0, args.decode_steps, max(1, args.decode_steps // args.cpu_decode_steps)))[: args.cpu_decode_steps]
+    est, ref_p, ref_d, desc = cpu_sample(qkv_h, cu_s, kc_h, vc_h, qn_h, kn_h, vn_h, step_ids, args.batch, total_rows,
+                                         args.decode_steps, threads, use_ref)
+    # the sample doubles as a parity check of the timed GPU outputs (same tensors)
+    err_p = float(np.abs(out_p[: int(cu_s[-1])].cpu().numpy() - ref_p).max())
+    err_d = max(float(np.abs(out_d[t, : db * N_NEW].cpu().numpy() - r).max()) for t, r in zip(step_ids, ref_d))
+    value = job_bytes(total_rows, args.batch, args.decode_steps) / est / 1e9
+    return {"value": value, "unit": UNIT, "cores": threads, "kind": "reference" if use_ref else "port", "sample": desc,
+            "est_job_seconds": est, "max_abs_err_vs_gpu": {"prefill": err_p, "decode": err_d}}
+
+
+if __name__ == "__main__":
+    main()

@@ -13,7 +13,7 @@ struct fblt_session {
     cudaStream_t stream = nullptr;
     int max_batch = 0, H = 0, hd = 0, cache_rows = 0, max_new = 0;
     int64_t E = 0, max_q_rows = 0, max_k_rows = 0;
-    float *d_q = nullptr, *d_k = nullptr, *d_v = nullptr, *d_out = nullptr;
+    float *d_in = nullptr, *d_out = nullptr; // d_in: one block holding q rows, then k rows, then v rows
     int32_t *d_tab = nullptr;
     size_t tab_cap = 0; // int32 entries
     float *kc = nullptr, *vc = nullptr;
@@ -27,9 +27,7 @@ namespace fblt {
 
 static void session_free(fblt_session *s) {
     if (!s) return;
-    cudaFree(s->d_q);
-    cudaFree(s->d_k);
-    cudaFree(s->d_v);
+    cudaFree(s->d_in);
     cudaFree(s->d_out);
     cudaFree(s->d_tab);
     cudaFree(s->kc);
@@ -95,14 +93,8 @@ extern "C" int fblt_session_create(fblt_session **out, int32_t max_batch, int32_
     } while (0)
     S_TRY(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
     const size_t fE = (size_t)s->E * sizeof(float);
-    if (max_q_rows > 0) {
-        S_TRY(cudaMalloc(&s->d_q, (size_t)max_q_rows * fE));
-        S_TRY(cudaMalloc(&s->d_out, (size_t)max_q_rows * fE));
-    }
-    if (max_k_rows > 0) {
-        S_TRY(cudaMalloc(&s->d_k, (size_t)max_k_rows * fE));
-        S_TRY(cudaMalloc(&s->d_v, (size_t)max_k_rows * fE));
-    }
+    if (max_q_rows > 0) S_TRY(cudaMalloc(&s->d_out, (size_t)max_q_rows * fE));
+    if (max_q_rows + max_k_rows > 0) S_TRY(cudaMalloc(&s->d_in, (size_t)(max_q_rows + 2 * max_k_rows) * fE));
     // tables: 8 per-sequence arrays plus doc / patch boundary lists
     s->tab_cap = (size_t)(max_batch + 4) * 10 + (size_t)max_k_rows + (size_t)max_q_rows + 2 * (size_t)max_batch + 64;
     S_TRY(cudaMalloc(&s->d_tab, s->tab_cap * sizeof(int32_t)));
@@ -147,9 +139,21 @@ extern "C" int fblt_session_forward(fblt_session *s, const fblt_attn_desc *hd) {
     if (hd->q_stride < E || hd->k_stride < E || hd->v_stride < E || hd->out_stride < E) return fail(FBLT_ERR_ARG, "session_forward: row stride smaller than num_heads*head_dim");
 
     const size_t wb = (size_t)E * sizeof(float);
-    FBLT_CUDA_TRY(cudaMemcpy2DAsync(s->d_q, wb, hd->q, (size_t)hd->q_stride * 4, wb, (size_t)tq, cudaMemcpyHostToDevice, s->stream));
-    FBLT_CUDA_TRY(cudaMemcpy2DAsync(s->d_k, wb, hd->k, (size_t)hd->k_stride * 4, wb, (size_t)tk, cudaMemcpyHostToDevice, s->stream));
-    FBLT_CUDA_TRY(cudaMemcpy2DAsync(s->d_v, wb, hd->v, (size_t)hd->v_stride * 4, wb, (size_t)tk, cudaMemcpyHostToDevice, s->stream));
+    float *dq = s->d_in, *dk = s->d_in + (size_t)s->max_q_rows * E, *dv = dk + (size_t)s->max_k_rows * E;
+    int64_t dstride = E;
+    // packed [T, 3E] rows (models/attention.c:95-98) travel as one contiguous copy and stay packed
+    const bool packed = tq == tk && hd->k == hd->q + E && hd->v == hd->q + 2 * E && hd->q_stride == 3 * E &&
+                        hd->k_stride == 3 * E && hd->v_stride == 3 * E;
+    if (packed) {
+        FBLT_CUDA_TRY(cudaMemcpyAsync(s->d_in, hd->q, (size_t)tq * 3 * wb, cudaMemcpyHostToDevice, s->stream));
+        dk = dq + E;
+        dv = dq + 2 * E;
+        dstride = 3 * E;
+    } else {
+        FBLT_CUDA_TRY(cudaMemcpy2DAsync(dq, wb, hd->q, (size_t)hd->q_stride * 4, wb, (size_t)tq, cudaMemcpyHostToDevice, s->stream));
+        FBLT_CUDA_TRY(cudaMemcpy2DAsync(dk, wb, hd->k, (size_t)hd->k_stride * 4, wb, (size_t)tk, cudaMemcpyHostToDevice, s->stream));
+        FBLT_CUDA_TRY(cudaMemcpy2DAsync(dv, wb, hd->v, (size_t)hd->v_stride * 4, wb, (size_t)tk, cudaMemcpyHostToDevice, s->stream));
+    }
 
     fblt_attn_desc d = *hd;
     TableArena ta{s};
@@ -175,11 +179,12 @@ extern "C" int fblt_session_forward(fblt_session *s, const fblt_attn_desc *hd) {
         // `packed` is pageable: the copy above has completed staging on return
     }
     if (ta.status != FBLT_OK) return ta.status;
-    d.q = s->d_q;
-    d.k = s->d_k;
-    d.v = s->d_v;
+    d.q = dq;
+    d.k = dk;
+    d.v = dv;
     d.out = s->d_out;
-    d.q_stride = d.k_stride = d.v_stride = d.out_stride = E;
+    d.q_stride = d.k_stride = d.v_stride = dstride;
+    d.out_stride = E;
     int st = fblt_attn_forward(&d, s->stream);
     if (st != FBLT_OK) return st;
     FBLT_CUDA_TRY(cudaMemcpy2DAsync(hd->out, (size_t)hd->out_stride * 4, s->d_out, wb, wb, (size_t)tq, cudaMemcpyDeviceToHost, s->stream));

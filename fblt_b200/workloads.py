@@ -62,14 +62,16 @@ def c1_byte_self_attention(seq_len: int = 512, window: int = 512) -> ForwardCase
                        MaskConfig(is_causal=True, sliding_window=window), packed=buf)
 
 
-def patch_self_attention(seed: int, batch: int, num_heads: int, name: str) -> ForwardCase:
-    """Block-causal patch-transformer attention: patch i attends to patches <= i; head_dim 64."""
+def patch_self_attention(seed: int, batch: int, num_heads: int, name: str, with_tensors: bool = True) -> ForwardCase:
+    """Block-causal patch-transformer attention: patch i attends to patches <= i; head_dim 64.
+    with_tensors=False returns only the patch structure (row tables and mask); q/k/v are then
+    empty [0, 3E] views for callers that fill device tensors themselves."""
     hd = 64
     E = num_heads * hd
     pb = synth.patch_batch(seed, batch)
     cu = np.zeros(batch + 1, dtype=np.int32)
     cu[1:] = np.cumsum(pb.num_patches)
-    buf = _packed_qkv(seed, int(cu[-1]), E, 1.0 / 8.0)
+    buf = _packed_qkv(seed, int(cu[-1]), E, 1.0 / 8.0) if with_tensors else np.zeros((0, 3 * E), np.float32)
     return ForwardCase(name, num_heads, hd, 1.0 / 8.0, buf[:, 0:E], buf[:, E:2 * E], buf[:, 2 * E:], cu, cu,
                        MaskConfig(is_causal=True), packed=buf,
                        meta={"patches": pb, "capped": pb.capped})
@@ -79,8 +81,8 @@ def c2_patch_attention(batch: int = 16) -> ForwardCase:
     return patch_self_attention(1, batch, 8, "c2_patch_self")
 
 
-def c5_prefill(batch: int = 2048) -> ForwardCase:
-    return patch_self_attention(4, batch, 16, "c5_prefill")
+def c5_prefill(batch: int = 2048, with_tensors: bool = True) -> ForwardCase:
+    return patch_self_attention(4, batch, 16, "c5_prefill", with_tensors)
 
 
 def c3_cross_attention(direction: str, batch: int = 32, seq_len: int = 512) -> ForwardCase:

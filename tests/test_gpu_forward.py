@@ -1,0 +1,145 @@
+"""Batched prefill / cross attention (fblt_attn_forward) against the CPU oracle on the
+benchmark configurations and on ragged edge cases, for both kernels and both precisions."""
+import numpy as np
+import pytest
+import torch
+
+from fblt_b200 import lib as L
+from fblt_b200 import ops, synth, workloads
+from fblt_b200.ops import MaskConfig
+from fblt_b200.workloads import ForwardCase
+from gpu_utils import forward_gpu
+from helpers import assert_close, oracle_forward
+
+pytestmark = pytest.mark.gpu
+
+KERNELS = [(L.IMPL_ROW, L.PREC_FP32), (L.IMPL_TILE, L.PREC_FP32), (L.IMPL_TILE, L.PREC_TF32)]
+# single-pass TF32 rounds every product to 11 bits: stated tolerance of that mode
+TF32_ATOL, TF32_RTOL = 2e-3, 2e-2
+
+
+def check(case: ForwardCase, kernels=KERNELS):
+    want, masks, _ = oracle_forward(case)
+    for impl, prec in kernels:
+        got, _ = forward_gpu(case, impl, prec)
+        what = f"{case.name} impl={impl} prec={prec}"
+        if prec == L.PREC_TF32:
+            assert_close(got, want, what, atol=TF32_ATOL, rtol=TF32_RTOL)
+        else:
+            assert_close(got, want, what)
+    return want
+
+
+def test_c1_byte_self_attention(cuda_lib):
+    check(workloads.c1_byte_self_attention())
+    check(workloads.c1_byte_self_attention(seq_len=300, window=77))
+
+
+def test_c2_patch_transformer_attention(cuda_lib):
+    case = workloads.c2_patch_attention()
+    assert case.q.shape[1] == 512 and len(case.cu_q) == 17
+    check(case)
+
+
+def test_c3_cross_attention(cuda_lib):
+    check(workloads.c3_cross_attention("enc"))
+    check(workloads.c3_cross_attention("dec_paper"))
+    check(workloads.c3_cross_attention("dec_leq"))
+    # default dispatch: short ranges -> row kernel, "<=" rule -> tile kernel; both must agree with the oracle
+    for d in ("enc", "dec_paper", "dec_leq"):
+        check(workloads.c3_cross_attention(d, batch=4), kernels=[(L.IMPL_AUTO, L.PREC_FP32)])
+
+
+def test_c5_prefill_sample(cuda_lib):
+    check(workloads.c5_prefill(batch=8))
+
+
+def random_case(seed, cu_q, cu_k, H, hd, mask, std=1.0):
+    E = H * hd
+    nq, nk = int(cu_q[-1]), int(cu_k[-1])
+    q = synth.normal(seed, 1, max(nq, 1) * E, std).reshape(-1, E)[:nq]
+    k = synth.normal(seed, 2, max(nk, 1) * E, std).reshape(-1, E)[:nk]
+    v = synth.normal(seed, 3, max(nk, 1) * E, std).reshape(-1, E)[:nk]
+    return ForwardCase(f"rand{seed}", H, hd, 1.0 / np.sqrt(hd), q, k, v, np.asarray(cu_q, np.int32),
+                       np.asarray(cu_k, np.int32), mask)
+
+
+@pytest.mark.parametrize("hd", [32, 64, 128])
+def test_ragged_lengths_all_head_dims(cuda_lib, hd):
+    # empty sequence, length 1, lengths around the 64-row tile edge
+    cu = np.concatenate([[0], np.cumsum([1, 0, 63, 64, 65, 130, 2, 200])])
+    check(random_case(40 + hd, cu, cu, 2, hd, MaskConfig(is_causal=True)))
+    check(random_case(41 + hd, cu, cu, 2, hd, MaskConfig(is_causal=True, sliding_window=48)))
+    check(random_case(42 + hd, cu, cu, 2, hd, MaskConfig()))  # bidirectional, no mask
+
+
+def test_docs_offsets_and_block_infer(cuda_lib):
+    cu = np.array([0, 150, 150 + 97])
+    docs = [np.array([40, 41, 120]), np.array([64])]
+    check(random_case(50, cu, cu, 2, 64, MaskConfig(is_causal=True, doc_bounds=docs)))
+    check(random_case(51, cu, cu, 2, 64, MaskConfig(is_causal=False, sliding_window=30, doc_bounds=docs)))
+    cu_q, cu_k = np.array([0, 5, 70]), np.array([0, 135, 135 + 201])
+    check(random_case(52, cu_q, cu_k, 2, 64, MaskConfig(is_causal=True, causal_offset=[130, 136], sliding_window=100)))
+    check(random_case(53, cu, cu, 2, 64, MaskConfig(num_clean=[146, 90])))
+
+
+def test_rows_without_keys_give_zeros(cuda_lib):
+    # window smaller than the causal offset gap: every key masked for the first rows of sequence 1
+    cu_q, cu_k = np.array([0, 4, 12]), np.array([0, 10, 30])
+    case = random_case(60, cu_q, cu_k, 1, 32, MaskConfig(is_causal=True, causal_offset=[6, 30], sliding_window=3))
+    want = check(case)
+    assert (want[4:] == 0).all()
+
+
+def test_explicit_group_ids_row_kernel(cuda_lib):
+    rng = np.random.default_rng(8)
+    cu_q, cu_k = np.array([0, 40, 75]), np.array([0, 50, 90])
+    m = MaskConfig(group_rule=L.GROUP_IDS, q_group_ids=rng.integers(0, 3, 75), k_group_ids=rng.integers(0, 3, 90))
+    check(random_case(61, cu_q, cu_k, 2, 48, m), kernels=[(L.IMPL_ROW, L.PREC_FP32), (L.IMPL_AUTO, L.PREC_FP32)])
+    case = random_case(62, cu_q, cu_k, 2, 64, m)
+    q, k, v = (torch.from_numpy(np.ascontiguousarray(x)).cuda() for x in (case.q, case.k, case.v))
+    out = torch.empty((75, 128), device="cuda")
+    b = ops.make_batch(q, k, v, out, cu_q, cu_k, 2, 64, 1.0, m, impl=L.IMPL_TILE)
+    with pytest.raises(L.FbltError) as e:
+        ops.attn_forward(b)
+    assert e.value.status == L.ERR_UNSUPPORTED
+
+
+def test_odd_head_dim_falls_back_to_row_kernel(cuda_lib):
+    cu = np.array([0, 33, 70])
+    check(random_case(63, cu, cu, 3, 20, MaskConfig(is_causal=True)), kernels=[(L.IMPL_AUTO, L.PREC_FP32)])
+
+
+def test_full_size_prefill_properties(cuda_lib):
+    """Config-5 prefill at full batch (2048 sequences, 16 heads x 64): properties that need no
+    CPU pass. (1) softmax weights sum to one: V == 1 gives out == 1 on every row; (2) the two
+    independent kernels agree; (3) linearity in V."""
+    case = workloads.c5_prefill(batch=2048, with_tensors=False)  # patch structure from the seeded generator
+    E = case.embed
+    rows = int(case.cu_q[-1])
+    gen = torch.Generator(device="cuda").manual_seed(4)
+    buf = torch.randn((rows, 3 * E), generator=gen, device="cuda") * 0.125
+    q, k, v = buf[:, 0:E], buf[:, E:2 * E], buf[:, 2 * E:]
+
+    def run(vv, impl, prec=L.PREC_FP32):
+        out = torch.full((rows, E), float("nan"), device="cuda")
+        b = ops.make_batch(q, k, vv, out, case.cu_q, case.cu_k, case.num_heads, case.head_dim, case.scale, case.mask,
+                           impl=impl, precision=prec)
+        ops.attn_forward(b)
+        torch.cuda.synchronize()
+        return out
+
+    ones = torch.ones((rows, E), device="cuda")
+    o1 = run(ones, L.IMPL_TILE)
+    assert float((o1 - 1).abs().max()) < 1e-5
+    o_tile = run(v, L.IMPL_TILE)
+    o_row = run(v, L.IMPL_ROW)
+    err = (o_tile - o_row).abs()
+    assert float((err - (1e-4 + 1e-3 * o_row.abs())).max()) <= 0
+    v2 = torch.roll(v, 1, 0).contiguous()
+    o2 = run(v2, L.IMPL_TILE)
+    o12 = run((v + v2).contiguous(), L.IMPL_TILE)
+    assert float((o12 - (o_tile + o2)).abs().max()) < 1e-4
+    # the first row of every sequence sees only itself: out == v exactly there
+    first = torch.from_numpy(case.cu_q[:-1].astype(np.int64)).cuda()
+    assert float((o_tile[first] - v[first]).abs().max()) < 1e-6

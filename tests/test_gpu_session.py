@@ -1,0 +1,69 @@
+"""Host-buffer sessions: the call a host program without device memory makes."""
+import numpy as np
+import pytest
+import torch
+
+from fblt_b200 import lib as L
+from fblt_b200 import ops, workloads
+from helpers import assert_close, oracle_decode, oracle_forward
+
+pytestmark = pytest.mark.gpu
+
+
+def test_session_forward_packed_and_cross(cuda_lib):
+    case = workloads.c2_patch_attention(batch=5)
+    want, _, _ = oracle_forward(case)
+    rows, E = int(case.cu_q[-1]), case.embed
+    s = ops.Session(8, case.num_heads, case.head_dim, max_q_rows=rows, max_k_rows=rows)
+    out = np.full((rows, E), np.nan, dtype=np.float32)
+    s.forward(case.q, case.k, case.v, out, case.cu_q, case.cu_k, case.scale, case.mask)   # views of one [T, 3E] buffer
+    assert_close(out, want, "session packed")
+    s.close()
+    for direction in ("enc", "dec_paper", "dec_leq"):
+        c = workloads.c3_cross_attention(direction, batch=3)
+        want, _, _ = oracle_forward(c)
+        s = ops.Session(4, c.num_heads, c.head_dim, max_q_rows=int(c.cu_q[-1]), max_k_rows=int(c.cu_k[-1]))
+        out = np.full((int(c.cu_q[-1]), c.embed), np.nan, dtype=np.float32)
+        s.forward(c.q, c.k, c.v, out, c.cu_q, c.cu_k, c.scale, c.mask)
+        assert_close(out, want, "session " + direction)
+        with pytest.raises(L.FbltError) as e:
+            big = workloads.c3_cross_attention(direction, batch=5)
+            s.forward(big.q, big.k, big.v, np.zeros((int(big.cu_q[-1]), big.embed), np.float32), big.cu_q, big.cu_k,
+                      big.scale, big.mask)
+        assert e.value.status == L.ERR_CAPACITY
+        s.close()
+
+
+def test_session_decode_steps_and_rollback(cuda_lib):
+    base = np.array([10, 64, 200, 33], dtype=np.int32)
+    n, steps = 4, 3
+    case = workloads.decode_case(120, 4, 4, n, True, lens=base, cache_rows=256)
+    E = case.embed
+    s = ops.Session(4, 4, 64, cache_rows=256, max_new=8)
+    s.cache_load(base, case.k_cache, case.v_cache, 256)
+    rng = np.random.default_rng(3)
+    lens = base.copy()
+    for step in range(steps):
+        advance = n if step != 1 else 2        # step 1 keeps only two of the four drafted rows
+        case.base_len = lens.copy()
+        case.q, case.k_new, case.v_new = (rng.standard_normal((4 * n, E)).astype(np.float32) for _ in range(3))
+        want, _ = oracle_decode(case)
+        out = np.full((4 * n, E), np.nan, dtype=np.float32)
+        s.decode(4, n, case.q, case.k_new, case.v_new, out, case.scale, block_mode=True, advance=advance)
+        assert_close(out, want, f"session decode step {step}")
+        for b in range(4):                      # host mirror of the cache, with the same rollback
+            case.k_cache[b, lens[b]:lens[b] + n] = case.k_new[b * n:(b + 1) * n]
+            case.v_cache[b, lens[b]:lens[b] + n] = case.v_new[b * n:(b + 1) * n]
+        lens += advance
+        assert (s.cache_lens(4) == lens).all()
+    # plain one-byte causal decode with a window on the same cache
+    case.n_new, case.block_mode, case.window, case.base_len = 1, False, 24, lens.copy()
+    case.q, case.k_new, case.v_new = (rng.standard_normal((4, E)).astype(np.float32) for _ in range(3))
+    want, _ = oracle_decode(case)
+    out = np.full((4, E), np.nan, dtype=np.float32)
+    s.decode(4, 1, case.q, case.k_new, case.v_new, out, case.scale, window=24)
+    assert_close(out, want, "session decode n=1 window")
+    with pytest.raises(L.FbltError) as e:
+        s.decode(4, 9, case.q, case.k_new, case.v_new, out, case.scale)
+    assert e.value.status == L.ERR_CAPACITY
+    s.close()
