@@ -208,9 +208,9 @@ def main():
     ap.add_argument("--batch", type=int, default=2048, help="total sequences over all ranks")
     ap.add_argument("--decode-steps", type=int, default=64)
     ap.add_argument("--e2e-steps", type=int, default=2)
-    ap.add_argument("--cpu-prefill-seqs", type=int, default=128)
-    ap.add_argument("--cpu-decode-seqs", type=int, default=32)
-    ap.add_argument("--cpu-decode-steps", type=int, default=4)
+    ap.add_argument("--cpu-prefill-seqs", type=int, default=512)
+    ap.add_argument("--cpu-decode-seqs", type=int, default=128)
+    ap.add_argument("--cpu-decode-steps", type=int, default=8)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     args = ap.parse_args()
