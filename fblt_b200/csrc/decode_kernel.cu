@@ -442,3 +442,86 @@ extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size
     default: return launch_decode_hd<128>(p, nq, s);
     }
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant: split-K partials in a fixed device array.
+// ---------------------------------------------------------------------------
+namespace fblt {
+
+// 4 MiB of partials, resident on every device that loads this library until
+// the process exits.
+constexpr size_t kStaticScratchBytes = (size_t)4 << 20;
+static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+constexpr int kMaxDevices = 64;
+static float *g_static_scratch_addr[kMaxDevices]; // device address per device ordinal, 0 = not looked up yet
+
+// In host code `g_decode_static_scratch` is only a handle for the symbol; the
+// address a kernel can dereference has to be asked for, once per device, with
+// that device current.
+static int static_scratch_address(float **out) {
+    int dev = -1;
+    FBLT_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(FBLT_ERR_LIMIT, "decode_static: device ordinal %d not supported", dev);
+    float *p = g_static_scratch_addr[dev];
+    if (!p) {
+        void *addr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&addr, g_decode_static_scratch);
+        if (e != cudaSuccess || !addr)
+            return fail(FBLT_ERR_CUDA, "decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        p = static_cast<float *>(addr);
+        g_static_scratch_addr[dev] = p; // same value whichever thread gets here first
+    }
+    *out = p;
+    return FBLT_OK;
+}
+
+} // namespace fblt
+
+extern "C" size_t fblt_attn_decode_static_capacity(void) { return fblt::kStaticScratchBytes; }
+
+extern "C" int fblt_attn_decode_static(const fblt_decode_desc *d, void *stream) {
+    using namespace fblt;
+    int st = validate_decode(d);
+    if (st != FBLT_OK) return st;
+    if (d->batch == 0) return FBLT_OK;
+    const int splits = resolve_splits(d);
+    const size_t need = fblt_attn_decode_workspace(d);
+    if (need > kStaticScratchBytes)
+        return fail(FBLT_ERR_LIMIT,
+                    "decode_static: %d splits of this batch need %zu bytes of partials; the built-in scratch holds %zu "
+                    "(use fblt_attn_decode with a caller workspace, or set splits = 1)",
+                    splits, need, kStaticScratchBytes);
+    float *scratch = nullptr;
+    st = static_scratch_address(&scratch);
+    if (st != FBLT_OK) return st;
+    DecodeParams p;
+    p.batch = d->batch;
+    p.H = d->num_heads;
+    p.n_new = d->n_new;
+    p.block_mode = d->block_mode ? 1 : 0;
+    p.window = d->window > 0 ? d->window : 0;
+    p.splits = splits;
+    const int nq = pick_nq(d->n_new);
+    p.qgroups = (d->n_new + nq - 1) / nq;
+    p.base_len = d->base_len;
+    p.kc = d->k_cache;
+    p.vc = d->v_cache;
+    p.seq_stride = d->cache_seq_stride;
+    p.row_stride = d->cache_row_stride;
+    p.q = d->q;
+    p.q_stride = d->q_stride;
+    p.kn = d->k_new;
+    p.vn = d->v_new;
+    p.new_stride = d->kv_new_stride;
+    p.out = d->out;
+    p.out_stride = d->out_stride;
+    p.ws = scratch; // every (row, split) slot is written before the merge kernel reads it: nothing to clear
+    p.qscale = d->scale * kLog2e;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (d->head_dim) {
+    case 32: return launch_decode_hd<32>(p, nq, s);
+    case 64: return launch_decode_hd<64>(p, nq, s);
+    default: return launch_decode_hd<128>(p, nq, s);
+    }
+}

@@ -96,6 +96,8 @@ SYMBOLS = {
     "fblt_mask_materialize": (C.c_int, [C.POINTER(AttnDesc), C.c_int32, C.c_void_p, c_i32_p, C.c_void_p]),
     "fblt_attn_decode_workspace": (C.c_size_t, [C.POINTER(DecodeDesc)]),
     "fblt_attn_decode": (C.c_int, [C.POINTER(DecodeDesc), C.c_void_p, C.c_size_t, C.c_void_p]),
+    "fblt_attn_decode_static_capacity": (C.c_size_t, []),
+    "fblt_attn_decode_static": (C.c_int, [C.POINTER(DecodeDesc), C.c_void_p]),
     "fblt_argmax_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "fblt_verify_accept": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),

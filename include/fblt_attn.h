@@ -324,6 +324,35 @@ typedef struct {
 size_t fblt_attn_decode_workspace(const fblt_decode_desc *desc);
 int fblt_attn_decode(const fblt_decode_desc *desc, void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * fblt_attn_decode without any allocation by anyone. (No counterpart in the
+ * reference: its operators take every temporary from the caller's arena.)
+ *
+ * Who needs it: a host loop that gave all device memory to a bump arena at
+ * start-up (the way the reference's runtime does) has nothing left to size a
+ * split-K workspace from in the middle of a generation, and a latency-bound
+ * decode loop cannot afford cudaMalloc, which may synchronise the whole device
+ * and can fail. Here the split-K partials live in a fixed array inside the
+ * library instead: fblt_attn_decode_static_capacity() bytes (4 MiB) of device
+ * memory on every GPU that loads the library, held until the process exits.
+ *
+ * Same descriptor, same results as fblt_attn_decode. Differences:
+ *   - a descriptor whose partials (fblt_attn_decode_workspace(desc) bytes)
+ *     exceed the capacity is rejected with FBLT_ERR_LIMIT; pass splits = 1
+ *     (no partials at all) or use fblt_attn_decode for those;
+ *   - the first call on each device looks the array's device address up
+ *     (cudaGetSymbolAddress, with that device current). Make that first call
+ *     during set-up, before any stream capture begins;
+ *   - all calls share the one array and it keeps whatever the last call left
+ *     there. Nothing has to start at zero: each call overwrites every slot it
+ *     later reads. Two calls whose kernels can overlap on the GPU (different
+ *     streams, or different host threads on one device) would overwrite each
+ *     other's partials: serialise them.
+ * The call itself uses no cudaMalloc, cudaFree or allocating library routine.
+ */
+size_t fblt_attn_decode_static_capacity(void);
+int fblt_attn_decode_static(const fblt_decode_desc *desc, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* L1: decision step (bit-exact integer / compare logic)                     */
 /* ------------------------------------------------------------------------ */
