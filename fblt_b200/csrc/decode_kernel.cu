@@ -54,6 +54,37 @@ __device__ __forceinline__ void scale4(float4 &a, float c) {
     a.w *= c;
 }
 
+__device__ __forceinline__ float fast_exp2(float x) { // 2^x; -inf -> 0, tiny results flush to 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Sums CNT values per lane across the lanes of a group (xor offsets O, O/2, .. 1).
+// While more than one value is left, a step keeps one half of the values and
+// trades the other half with the partner lane (lanes with bit O set keep the
+// upper half), so the value count halves each step; once a single value is
+// left the remaining steps are plain butterfly adds. The result is in v[0].
+template <int CNT, int O>
+__device__ __forceinline__ void lane_group_transpose_reduce(float *v, int lane) {
+    if constexpr (O >= 1) {
+        if constexpr (CNT > 1) {
+            constexpr int HALF = CNT / 2;
+            const bool upper = (lane & O) != 0;
+#pragma unroll
+            for (int i = 0; i < HALF; ++i) {
+                const float give = upper ? v[i] : v[i + HALF];
+                const float keep = upper ? v[i + HALF] : v[i];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, give, O);
+            }
+            lane_group_transpose_reduce<HALF, O / 2>(v, lane);
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], O);
+            lane_group_transpose_reduce<1, O / 2>(v, lane);
+        }
+    }
+}
+
 template <int HD>
 __host__ __device__ constexpr int dec_partial_floats() {
     return HD + 4; // acc[HD], m, l, 2 pad (keeps 16-byte alignment)
@@ -63,7 +94,8 @@ template <int HD, int NQ>
 __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p) {
     constexpr int LPK = HD / 4;   // lanes per key row
     constexpr int KPW = 32 / LPK; // key rows per warp load
-    constexpr int U = NQ == 1 ? 8 : (NQ <= 4 ? 4 : 2);
+    // keys per lane group and chunk: as many as fit "one score per lane", at most 8
+    constexpr int U = (LPK / NQ) > 8 ? 8 : ((LPK / NQ) < 1 ? 1 : (LPK / NQ));
     constexpr int CH = KPW * U; // keys per warp per chunk
 
     const int h = blockIdx.x, sp = blockIdx.y;
@@ -134,47 +166,67 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
     }
 
     // ---- unmasked stream -------------------------------------------------
-    for (int c = warp; c < nchunks; c += kDecWarps) {
-        const int jb = F0 + c * CH + grp;
-        float4 kk[U], vv[U];
+    // The U*NQ partial scores of a chunk are reduced over the LPK lanes of a
+    // key group with a transposing butterfly: each step halves the number of
+    // values a lane carries, so the reduction costs V-1 shuffles instead of
+    // V*log2(LPK), and leaves score (u, q) = (idx / NQ, idx % NQ) on the lanes
+    // with dl / REP == idx. Those lanes run the softmax for their own score
+    // only; probabilities and rescale factors are then broadcast for the PV
+    // accumulation, which every lane does for its four value columns.
+    {
+        constexpr int V = U * NQ;
+        static_assert(V <= LPK, "chunk shape must leave at most one score per lane");
+        constexpr int REP = LPK / V;     // lanes holding the same score after the reduction
+        const int idx = dl / REP;        // the score this lane owns
+        const int q_own = idx % NQ;
+        float m_own = -INFINITY, l_own = 0.0f;
+        for (int c = warp; c < nchunks; c += kDecWarps) {
+            const int jb = F0 + c * CH + grp;
+            float4 kk[U], vv[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int64_t off = (int64_t)(jb + u * KPW) * p.row_stride;
-            kk[u] = ld4(kc + off);
-            vv[u] = ld4(vc + off);
-        }
-        float s[U][NQ];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-            for (int q = 0; q < NQ; ++q) s[u][q] = dot4(qv[q], kk[u]);
-#pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1)
+            for (int u = 0; u < U; ++u) {
+                const int64_t off = (int64_t)(jb + u * KPW) * p.row_stride;
+                kk[u] = ld4(kc + off);
+                vv[u] = ld4(vc + off);
+            }
+            float s[V];
 #pragma unroll
             for (int u = 0; u < U; ++u)
 #pragma unroll
-                for (int q = 0; q < NQ; ++q) s[u][q] += __shfl_xor_sync(0xffffffffu, s[u][q], o);
+                for (int q = 0; q < NQ; ++q) s[u * NQ + q] = dot4(qv[q], kk[u]);
+            lane_group_transpose_reduce<V, LPK / 2>(s, lane);
+            float sv = s[0];
+            if (!finite_f(sv)) sv = -INFINITY;
+            float cmax = sv;
+#pragma unroll
+            for (int o = NQ * REP; o < LPK; o <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, o));
+            const float mn = fmaxf(m_own, cmax);
+            const float mref = mn == -INFINITY ? 0.0f : mn;
+            const float corr_own = fast_exp2(m_own - mref);
+            const float pe_own = fast_exp2(sv - mref);
+            float psum = pe_own;
+#pragma unroll
+            for (int o = NQ * REP; o < LPK; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+            l_own = l_own * corr_own + psum;
+            m_own = mn;
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                const float corr = __shfl_sync(0xffffffffu, corr_own, q * REP, LPK);
+                scale4(acc[q], corr);
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const float pe = __shfl_sync(0xffffffffu, pe_own, (u * NQ + q) * REP, LPK);
+                    fma4(acc[q], pe, vv[u]);
+                }
+            }
+        }
+        // hand the per-row state to every lane of the group for the code below
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
-            float mn = m[q];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (!finite_f(s[u][q])) s[u][q] = -INFINITY;
-                mn = fmaxf(mn, s[u][q]);
-            }
-            const float mref = mn == -INFINITY ? 0.0f : mn;
-            const float corr = exp2f(m[q] - mref);
-            float ls = l[q] * corr;
-            scale4(acc[q], corr);
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const float pe = exp2f(s[u][q] - mref);
-                ls += pe;
-                fma4(acc[q], pe, vv[u]);
-            }
-            l[q] = ls;
-            m[q] = mn;
+            m[q] = __shfl_sync(0xffffffffu, m_own, q * REP, LPK);
+            l[q] = __shfl_sync(0xffffffffu, l_own, q * REP, LPK);
         }
+        (void)q_own;
     }
 
     // ---- checked keys: window edge, chunk remainder, appended rows --------
