@@ -31,6 +31,13 @@ import numpy as np
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+_RESULT_FD = 1
+
+
+def emit(line: dict) -> None:
+    os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
+
+
 METRIC = "attn_algorithmic_bytes_per_s"
 UNIT = "GB/s"
 H, HD, E = 16, 64, 1024
@@ -186,7 +193,7 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(args, total_rows: int) -> dict:
@@ -211,13 +218,25 @@ def main():
     ap.add_argument("--cpu-prefill-seqs", type=int, default=512)
     ap.add_argument("--cpu-decode-seqs", type=int, default=128)
     ap.add_argument("--cpu-decode-steps", type=int, default=8)
+    ap.add_argument("--workload", default="scaled", choices=["scaled", "configs"],
+                    help="scaled = the headline job (one JSON line); configs = one line per small benchmark "
+                         "configuration (byte self-attention, patch attention, cross-attention, cache decode)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    # Libraries (NCCL's version banner, for one) write to stdout; keep stdout for the JSON
+    # result only and send everything else to stderr.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload == "configs":
+        run_small_configs(args)
         return
 
     import torch
@@ -360,9 +379,74 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "job_bytes": total_bytes,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_small_configs(args):
+    """Device time, roofline fraction, CPU reference time and max error of every small
+    configuration at its full size (inputs from the seeded host generators). L2 is flushed
+    between timed iterations because these working sets fit in it."""
+    import torch
+    sys.path.insert(0, str(ROOT / "tests"))
+    from fblt_b200 import lib as L
+    from fblt_b200 import ops, workloads
+    from gpu_utils import upload_case
+    from helpers import oracle_decode, oracle_forward
+    from oracle import binding as ob
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peak = float(json.loads(peaks_file.read_text())["hbm_gbs"]) if peaks_file.exists() else 6650.0
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        times = []
+        for _ in range(max(args.steps, 10)):
+            flush.zero_()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            fn()
+            t1.record()
+            torch.cuda.synchronize()
+            times.append(t0.elapsed_time(t1))
+        return statistics.median(times)
+
+    def report(name, ms, nbytes, cpu_s, err, extra=None):
+        line = {"workload": name, "ms": ms, "algorithmic_bytes": nbytes, "GB/s": nbytes / ms / 1e6,
+                "frac_of_hbm_peak": nbytes / ms / 1e6 / peak, "cpu_reference_ms": cpu_s * 1e3,
+                "cpu_cores": ob.host_cores(), "max_abs_err": err, "l2": "flushed between iterations"}
+        line.update(extra or {})
+        emit(line)
+
+    fwd = [workloads.c1_byte_self_attention(), workloads.c2_patch_attention(), workloads.c3_cross_attention("enc"),
+           workloads.c3_cross_attention("dec_paper"), workloads.c3_cross_attention("dec_leq")]
+    for case in fwd:
+        q, k, v = upload_case(case)
+        out = torch.empty((int(case.cu_q[-1]), case.embed), device="cuda")
+        for prec, tag in ((L.PREC_FP32, ""), (L.PREC_TF32, "+tf32")):
+            b = ops.make_batch(q, k, v, out, case.cu_q, case.cu_k, case.num_heads, case.head_dim, case.scale, case.mask,
+                               precision=prec)
+            ms = timed(lambda: ops.attn_forward(b))
+            if prec == L.PREC_FP32:
+                want, _, cpu_s = oracle_forward(case)
+            err = float(np.abs(out.cpu().numpy() - want).max())
+            report(case.name + tag, ms, case.algorithmic_bytes(), cpu_s, err)
+            if case.mask.group_rule in (L.GROUP_PATCH_ENC, L.GROUP_PATCH_DEC):
+                break   # row kernel: one precision
+    for case in (workloads.c4_decode(), workloads.c4_block_verify()):
+        kc, vc = torch.from_numpy(case.k_cache).cuda(), torch.from_numpy(case.v_cache).cuda()
+        base, q = torch.from_numpy(case.base_len).cuda(), torch.from_numpy(case.q).cuda()
+        kn, vn = torch.from_numpy(case.k_new).cuda(), torch.from_numpy(case.v_new).cuda()
+        out = torch.empty_like(q)
+        d = ops.make_decode(kc, vc, base, q, out, case.num_heads, case.head_dim, case.n_new, case.scale,
+                            block_mode=case.block_mode, k_new=kn, v_new=vn, max_len=int(case.base_len.max()) + case.n_new)
+        ws = ops.decode_workspace(d)
+        ms = timed(lambda: ops.attn_decode(d, ws))
+        want, cpu_s = oracle_decode(case)
+        err = float(np.abs(out.cpu().numpy() - want).max())
+        report(case.name, ms, case.algorithmic_bytes(), cpu_s, err, {"splits": int(d.splits)})
 
 
 # dram bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in

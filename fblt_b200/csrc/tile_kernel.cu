@@ -51,8 +51,16 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <int HD, bool X3>
-__global__ void __launch_bounds__(kTileThreads) tile_attn_kernel(fblt_attn_desc d) {
+__device__ __forceinline__ float ex2_fast(float x) { // 2^x; -inf -> 0, results below 2^-126 flush to 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// STAGES = 2 double-buffers the K/V tiles (long key ranges); STAGES = 1 keeps
+// one tile and lets four CTAs share an SM instead (key ranges of one or two tiles).
+template <int HD, bool X3, int STAGES>
+__global__ void __launch_bounds__(kTileThreads, STAGES == 1 ? 4 : 2) tile_attn_kernel(fblt_attn_desc d) {
     constexpr int LDS = HD + 4;    // padded row, floats
     constexpr int CPR = HD / 4;    // 16-byte chunks per row
     constexpr int NT_O = HD / 8;   // output n-tiles
@@ -60,7 +68,7 @@ __global__ void __launch_bounds__(kTileThreads) tile_attn_kernel(fblt_attn_desc 
     extern __shared__ __align__(16) float smem[];
     float *sQ = smem;
     float *sK = sQ + kBM * LDS;
-    float *sV = sK + 2 * kBN * LDS;
+    float *sV = sK + STAGES * kBN * LDS;
     __shared__ int s_lo[kBM], s_hi[kBM];
 
     const int b = blockIdx.z, h = blockIdx.y;
@@ -139,16 +147,28 @@ __global__ void __launch_bounds__(kTileThreads) tile_attn_kernel(fblt_attn_desc 
     const float qscale = d.scale * kLog2e;
 
     for (int kt = kt_begin; kt < kt_end; ++kt) {
-        const int stage = (kt - kt_begin) & 1;
-        if (kt + 1 < kt_end) load_kv(kt + 1, stage ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
+        int stage = 0;
+        if (STAGES == 2) {
+            stage = (kt - kt_begin) & 1;
+            if (kt + 1 < kt_end) load_kv(kt + 1, stage ^ 1);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            if (kt > kt_begin) {
+                load_kv(kt, 0);
+                cp_async_commit();
+            }
+            cp_async_wait<0>();
+        }
         __syncthreads();
 
         const int j0 = kt * kBN;
         if (whi > j0 && wlo < j0 + kBN) {
             const float *tK = sK + stage * kBN * LDS;
             const float *tV = sV + stage * kBN * LDS;
+            // 8-key column blocks of this tile that some row of the warp can see
+            const int nlo = wlo > j0 ? (wlo - j0) >> 3 : 0;
+            const int nhi = whi < j0 + kBN ? (whi - j0 + 7) >> 3 : 8;
 
             float sacc[8][4];
 #pragma unroll
@@ -165,6 +185,7 @@ __global__ void __launch_bounds__(kTileThreads) tile_attn_kernel(fblt_attn_desc 
                 split_tf32(sQ[(wr + g + 8) * LDS + ks * 8 + t + 4] * qscale, ahi[3], alo[3]);
 #pragma unroll
                 for (int n = 0; n < 8; ++n) {
+                    if (n < nlo || n >= nhi) continue; // scores stay 0 and are masked below
                     uint32_t bhi[2], blo[2];
                     split_tf32(tK[(n * 8 + g) * LDS + ks * 8 + t], bhi[0], blo[0]);
                     split_tf32(tK[(n * 8 + g) * LDS + ks * 8 + t + 4], bhi[1], blo[1]);
@@ -200,16 +221,16 @@ __global__ void __launch_bounds__(kTileThreads) tile_attn_kernel(fblt_attn_desc 
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
             const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
             const float ref0 = mn0 == -INFINITY ? 0.0f : mn0, ref1 = mn1 == -INFINITY ? 0.0f : mn1;
-            const float c0 = exp2f(m0 - ref0), c1 = exp2f(m1 - ref1);
+            const float c0 = ex2_fast(m0 - ref0), c1 = ex2_fast(m1 - ref1);
             m0 = mn0;
             m1 = mn1;
             float rs0 = 0.0f, rs1 = 0.0f;
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
-                sacc[n][0] = exp2f(sacc[n][0] - ref0);
-                sacc[n][1] = exp2f(sacc[n][1] - ref0);
-                sacc[n][2] = exp2f(sacc[n][2] - ref1);
-                sacc[n][3] = exp2f(sacc[n][3] - ref1);
+                sacc[n][0] = ex2_fast(sacc[n][0] - ref0);
+                sacc[n][1] = ex2_fast(sacc[n][1] - ref0);
+                sacc[n][2] = ex2_fast(sacc[n][2] - ref1);
+                sacc[n][3] = ex2_fast(sacc[n][3] - ref1);
                 rs0 += sacc[n][0] + sacc[n][1];
                 rs1 += sacc[n][2] + sacc[n][3];
             }
@@ -226,6 +247,7 @@ __global__ void __launch_bounds__(kTileThreads) tile_attn_kernel(fblt_attn_desc 
             // ---- O += P V ----------------------------------------------------
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
+                if (ks < nlo || ks >= nhi) continue; // every probability in this block is 0
                 uint32_t ahi[4], alo[4];
                 split_tf32(sacc[ks][0], ahi[0], alo[0]); // row g,   key 2t
                 split_tf32(sacc[ks][2], ahi[1], alo[1]); // row g+8, key 2t
@@ -244,7 +266,7 @@ __global__ void __launch_bounds__(kTileThreads) tile_attn_kernel(fblt_attn_desc 
                 }
             }
         }
-        __syncthreads(); // the stage is overwritten by the next iteration's prefetch
+        __syncthreads(); // the tile is overwritten by the next load
     }
     cp_async_wait<0>();
 
@@ -302,20 +324,27 @@ bool tile_kernel_supports(const fblt_attn_desc &d, const char **why) {
     return true;
 }
 
-template <int HD, bool X3>
-static int launch_tile_t(const fblt_attn_desc &d, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)(kBM + 4 * kBN) * (HD + 4) * sizeof(float);
-    static int configured_device = -1; // per (HD, X3) instantiation; the attribute is per device
+template <int HD, bool X3, int STAGES>
+static int launch_tile_s(const fblt_attn_desc &d, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)(kBM + 2 * STAGES * kBN) * (HD + 4) * sizeof(float);
+    static int configured_device = -1; // per instantiation; the attribute is per device
     int dev = 0;
     FBLT_CUDA_TRY(cudaGetDevice(&dev));
     if (configured_device != dev) {
-        FBLT_CUDA_TRY(cudaFuncSetAttribute(tile_attn_kernel<HD, X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        FBLT_CUDA_TRY(cudaFuncSetAttribute(tile_attn_kernel<HD, X3, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured_device = dev;
     }
     dim3 grid((d.max_q + kBM - 1) / kBM, d.num_heads, d.batch);
-    tile_attn_kernel<HD, X3><<<grid, kTileThreads, smem, stream>>>(d);
+    tile_attn_kernel<HD, X3, STAGES><<<grid, kTileThreads, smem, stream>>>(d);
     count_launch();
     return check_launch("tile_attn_kernel");
+}
+
+template <int HD, bool X3>
+static int launch_tile_t(const fblt_attn_desc &d, cudaStream_t stream) {
+    // at most two key tiles per sequence: occupancy beats intra-CTA prefetch
+    if (d.max_k <= 2 * kBN && HD <= 64) return launch_tile_s<HD, X3, 1>(d, stream);
+    return launch_tile_s<HD, X3, 2>(d, stream);
 }
 
 int launch_tile_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
