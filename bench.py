@@ -297,8 +297,11 @@ def main():
     dec_t0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.warmup + args.steps)]
     dec_t1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.warmup + args.steps)]
 
+    pre_t0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.warmup + args.steps)]
+
     def one_step(it: int):
         with torch.cuda.stream(main_stream):
+            pre_t0[it].record(main_stream)
             ops.attn_forward(pre, main_stream)
             if world > 1:
                 ev_pre_done.record(main_stream)
@@ -336,10 +339,11 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     ms = t_begin.elapsed_time(t_end)
     dec_ms = sum(dec_t0[args.warmup + i].elapsed_time(dec_t1[args.warmup + i]) for i in range(args.steps))
+    pre_ms = sum(pre_t0[args.warmup + i].elapsed_time(dec_t0[args.warmup + i]) for i in range(args.steps))
     if world > 1:
-        tt = torch.tensor([ms, dec_ms], device=dev, dtype=torch.float64)
+        tt = torch.tensor([ms, dec_ms, pre_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, dec_ms = float(tt[0]), float(tt[1])
+        ms, dec_ms, pre_ms = float(tt[0]), float(tt[1]), float(tt[2])
         lt = torch.tensor([launches], device=dev, dtype=torch.int64)
         dist.all_reduce(lt)
         launches = int(lt[0])
@@ -361,6 +365,16 @@ def main():
                 "algorithmic_bytes_per_launch": launch_bytes, "traffic": NCU_TRAFFIC_PER_ALGORITHMIC_BYTE and
                 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * launch_bytes}
 
+    # secondary kernel: the prefill tile kernel (one launch per step; at N > 1 the time includes
+    # enqueueing the overlapped gather)
+    pre_launch_ms = pre_ms / args.steps
+    pre_bytes = prefill_bytes(rows)
+    pre_flops = 4.0 * HD * H * float(sum(int(n) * (int(n) + 1) // 2 for n in np.diff(cu)))  # allowed pairs only
+    prefill = {"kernel": "tile_attn_kernel<64,fp32x3>", "launch_ms": pre_launch_ms,
+               "algorithmic_bytes_per_launch": pre_bytes, "achieved_GBps": pre_bytes / pre_launch_ms / 1e6,
+               "frac_of_hbm_peak": pre_bytes / pre_launch_ms / 1e6 / peak,
+               "algorithmic_tflops": pre_flops / pre_launch_ms / 1e9}
+
     # ---- host-buffer leg (sessions): copies inside the timed region -------------
     e2e = None
     if not args.no_e2e:
@@ -376,7 +390,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(args, total_rows),
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": roofline, "prefill": prefill, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "job_bytes": total_bytes,
         }
         emit(line)
