@@ -464,8 +464,8 @@ def run_small_configs(args):
 
 
 # dram bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in
-# profiles/ (None until captured).
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = None
+# profiles/; traffic of a full launch is scaled from it by the rows processed.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.010  # profiles/decode_attn_kernel_config5.md (256-sequence capture)
 
 
 def run_e2e(args, torch, ops, dev, qkv, cu, rows, B, cache_rows, kc, vc, qn, kn, vn, world, total_bytes, barrier):
