@@ -7,6 +7,8 @@ namespace fblt {
 int launch_row_kernel(const fblt_attn_desc &d, cudaStream_t stream);
 int launch_tile_kernel(const fblt_attn_desc &d, cudaStream_t stream);
 bool tile_kernel_supports(const fblt_attn_desc &d, const char **why);
+int launch_tile5_kernel(const fblt_attn_desc &d, cudaStream_t stream);
+bool tile5_kernel_supports(const fblt_attn_desc &d, const char **why);
 
 static int validate_desc(const fblt_attn_desc *d) {
     if (!d) return fail(FBLT_ERR_ARG, "attn: NULL descriptor");
@@ -92,6 +94,9 @@ extern "C" int fblt_attn_forward(const fblt_attn_desc *d, void *stream) {
     case FBLT_IMPL_TILE:
         if (!tile_kernel_supports(*d, &why)) return fail(FBLT_ERR_UNSUPPORTED, "tile kernel: %s", why);
         return launch_tile_kernel(*d, s);
+    case FBLT_IMPL_TCGEN05:
+        if (!tile5_kernel_supports(*d, &why)) return fail(FBLT_ERR_UNSUPPORTED, "%s", why);
+        return launch_tile5_kernel(*d, s);
     case FBLT_IMPL_AUTO:
         // short per-row key ranges (a patch's own bytes, one latent) stay on the row kernel
         if ((d->mask.group_rule == FBLT_GROUP_NONE || d->mask.group_rule == FBLT_GROUP_PATCH_LEQ) && d->max_k >= 32 &&

@@ -35,6 +35,7 @@ struct DecodeParams {
     int64_t out_stride;
     float *ws;
     float qscale;
+    const float *rope_cos, *rope_sin; // [positions, HD/2] tables, or NULL: q / k_new arrive rotated
 };
 
 __device__ __forceinline__ float4 ld4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
@@ -83,6 +84,20 @@ __device__ __forceinline__ void lane_group_transpose_reduce(float *v, int lane) 
             lane_group_transpose_reduce<1, O / 2>(v, lane);
         }
     }
+}
+
+// Rotary embedding of the two (even, odd) pairs a lane holds, for absolute position `pos`:
+// out[2i] = x[2i] c_i - x[2i+1] s_i, out[2i+1] = x[2i+1] c_i + x[2i] s_i (ops/reductions_cpu.c:217-228).
+// Products and sums are rounded separately, as the CPU code does, so rotated rows match it exactly.
+__device__ __forceinline__ float4 rope_pairs(float4 x, const float *cs, const float *sn, int pos, int half, int pair0) {
+    const float2 c = __ldg(reinterpret_cast<const float2 *>(cs + (int64_t)pos * half + pair0));
+    const float2 s = __ldg(reinterpret_cast<const float2 *>(sn + (int64_t)pos * half + pair0));
+    float4 o;
+    o.x = __fsub_rn(__fmul_rn(x.x, c.x), __fmul_rn(x.y, s.x));
+    o.y = __fadd_rn(__fmul_rn(x.y, c.x), __fmul_rn(x.x, s.x));
+    o.z = __fsub_rn(__fmul_rn(x.z, c.y), __fmul_rn(x.w, s.y));
+    o.w = __fadd_rn(__fmul_rn(x.w, c.y), __fmul_rn(x.z, s.y));
+    return o;
 }
 
 template <int HD>
@@ -156,6 +171,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
     for (int q = 0; q < NQ; ++q) {
         if (q < nv) {
             qv[q] = ld4(p.q + (int64_t)(b * n + r0 + q) * p.q_stride + hoff);
+            if (p.rope_cos) qv[q] = rope_pairs(qv[q], p.rope_cos, p.rope_sin, base + r0 + q, HD / 2, dl * 2);
             scale4(qv[q], p.qscale);
         } else {
             qv[q] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -242,6 +258,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
                     const int64_t off = (int64_t)(b * n + (j - base)) * p.new_stride + hoff;
                     kk = ld4(p.kn + off);
                     vv = ld4(p.vn + off);
+                    if (p.rope_cos) kk = rope_pairs(kk, p.rope_cos, p.rope_sin, j, HD / 2, dl * 2);
                 } else {
                     const int64_t off = (int64_t)j * p.row_stride;
                     kk = ld4(kc + off);
@@ -345,7 +362,9 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
             const int row = t / LPK, c = t - row * LPK;
             const int64_t src = (int64_t)(b * n + row) * p.new_stride + (int64_t)h * HD + c * 4;
             const int64_t dst = (int64_t)b * p.seq_stride + (int64_t)(base + row) * p.row_stride + (int64_t)h * HD + c * 4;
-            *reinterpret_cast<float4 *>(p.kc + dst) = ld4(p.kn + src);
+            float4 knew = ld4(p.kn + src);
+            if (p.rope_cos) knew = rope_pairs(knew, p.rope_cos, p.rope_sin, base + row, HD / 2, c * 2);
+            *reinterpret_cast<float4 *>(p.kc + dst) = knew;
             *reinterpret_cast<float4 *>(p.vc + dst) = ld4(p.vn + src);
         }
     }
@@ -408,6 +427,9 @@ static int validate_decode(const fblt_decode_desc *d) {
     if (!d->base_len || !d->k_cache || !d->v_cache || !d->q || !d->out)
         return fail(FBLT_ERR_ARG, "decode: NULL buffer");
     if ((d->k_new == nullptr) != (d->v_new == nullptr)) return fail(FBLT_ERR_ARG, "decode: k_new and v_new go together");
+    if ((d->rope_cos == nullptr) != (d->rope_sin == nullptr)) return fail(FBLT_ERR_ARG, "decode: rope_cos and rope_sin go together");
+    if (d->rope_cos && !d->k_new) return fail(FBLT_ERR_ARG, "decode: rotary tables need k_new / v_new (rows still unrotated)");
+    if (((uintptr_t)d->rope_cos | (uintptr_t)d->rope_sin) & 7) return fail(FBLT_ERR_ARG, "decode: rotary tables must be 8-byte aligned");
     const int64_t E = (int64_t)d->num_heads * d->head_dim;
     if (d->cache_row_stride < E || d->q_stride < E || d->out_stride < E || (d->k_new && d->kv_new_stride < E))
         return fail(FBLT_ERR_ARG, "decode: row stride smaller than num_heads*head_dim");
@@ -480,6 +502,8 @@ extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size
     p.out_stride = d->out_stride;
     p.ws = (float *)workspace;
     p.qscale = d->scale * kLog2e;
+    p.rope_cos = d->rope_cos;
+    p.rope_sin = d->rope_sin;
     if (p.splits > 1) {
         const size_t need = fblt_attn_decode_workspace(d);
         if (!workspace || workspace_bytes < need)
@@ -570,6 +594,8 @@ extern "C" int fblt_attn_decode_static(const fblt_decode_desc *d, void *stream) 
     p.out_stride = d->out_stride;
     p.ws = scratch; // every (row, split) slot is written before the merge kernel reads it: nothing to clear
     p.qscale = d->scale * kLog2e;
+    p.rope_cos = d->rope_cos;
+    p.rope_sin = d->rope_sin;
     cudaStream_t s = (cudaStream_t)stream;
     switch (d->head_dim) {
     case 32: return launch_decode_hd<32>(p, nq, s);

@@ -1,0 +1,518 @@
+// L1 tcgen05 tile kernel (head_dim 64): the same range-masked attention as
+// tile_kernel.cu, with both GEMMs on the 5th-generation tensor cores.
+//
+//   CTA   = (128 query rows, head, sequence), 128 threads: thread t owns row t,
+//           which is also TMEM lane t, so the softmax needs no shuffles.
+//   Q     = loaded once, split into TF32 (hi, lo) parts, kept in TMEM as the A
+//           operand of S = Q K^T (128 columns).
+//   K, V  = 64-key tiles; every thread loads 16-byte pieces from HBM, splits
+//           them into (hi, lo) and stores them in the no-swizzle K-major UMMA
+//           core-matrix layout (K as [key][dim], V transposed to [dim][key]).
+//   S     = 3 x 8 tcgen05.mma (lo*hi + hi*lo + hi*hi) of shape 128x64x8 into
+//           64 TMEM columns; one elected thread issues, tcgen05.commit arrives on
+//           an mbarrier, every thread reads its row back with tcgen05.ld.
+//   P     = softmax in registers (log2 domain, finite-only maximum, key range per
+//           row), split into (hi, lo), stored K-major in shared memory; the hi
+//           plane reuses the K tile's space, which is free once S is complete.
+//   O     = 3 x 8 tcgen05.mma of shape 128x64x8 accumulating in 64 TMEM columns;
+//           rescaled in TMEM only when a row's maximum moved.
+//
+// 96 KB of shared memory and 256 TMEM columns per CTA: two CTAs share an SM and
+// overlap each other's load / MMA / softmax phases.
+//
+// Every mbarrier wait is bounded: after kSpinLimit polls the CTA records an
+// error code, stops issuing work, frees its TMEM and returns.
+#include "common.cuh"
+
+#include <limits.h>
+
+namespace fblt {
+
+constexpr int kT5Rows = 128, kT5Keys = 64, kT5HD = 64, kT5Threads = 128;
+constexpr uint32_t kSpinLimit = 1u << 22; // x ~100 ns per poll: well under a second
+constexpr int kPlaneKV = kT5Keys * kT5HD * 4;   // 16 KB: one (hi or lo) plane of a K or V tile
+constexpr int kPlaneP = kT5Rows * kT5Keys * 4;  // 32 KB: one plane of P
+// shared memory map (bytes): [0,32K) K hi|lo, reused by P hi; [32K,64K) V hi|lo; [64K,96K) P lo
+constexpr int kOffK = 0, kOffV = 2 * kPlaneKV, kOffPlo = 4 * kPlaneKV, kT5Smem = 4 * kPlaneKV + kPlaneP;
+// TMEM columns
+constexpr uint32_t kColQhi = 0, kColQlo = 64, kColS = 128, kColO = 192, kT5Cols = 256;
+
+__device__ unsigned int g_t5_error; // 0 = ok; otherwise (code << 24) | blockIdx.x of the first CTA that gave up
+
+// ---- PTX wrappers ------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+// Bounded wait for the phase with the given parity; false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done)
+                     : "r"(addr), "r"(parity)
+                     : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor], TF32 inputs, fp32 accumulate
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+// D[tmem] (+)= A[smem descriptor] * B[smem descriptor]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
+                 : "memory");
+}
+
+// 32 consecutive TMEM columns of this thread's lane -> registers / back
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+                   "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                   "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr)
+                 : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                 "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+                 "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+                 "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+
+__device__ __forceinline__ uint32_t t5_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float t5_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Shared-memory matrix descriptor, no swizzle: start address, leading-dimension
+// and stride byte offsets in 16-byte units, descriptor version 1 (bits 46-47).
+__device__ __forceinline__ uint64_t t5_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+
+// Instruction descriptor: fp32 accumulate (bits 4-5 = 1), A and B TF32 (bits 7-9, 10-12 = 2),
+// A K-major, B K-major or MN-major (bit 16), N / 8 at bits 17-22, M / 16 at bits 24-28.
+__host__ __device__ constexpr uint32_t t5_idesc(int m, int n, int b_mn_major) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(m >> 4) << 24);
+}
+
+// ---- the kernel -----------------------------------------------------------------
+
+template <bool X3>
+__global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_desc d) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    __shared__ __align__(8) uint64_t bar_s, bar_o;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int s_lo[kT5Rows], s_hi[kT5Rows];
+
+    const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
+    const int q0 = d.cu_q[b], nq = d.cu_q[b + 1] - q0;
+    const int k0 = d.cu_k[b], nk = d.cu_k[b + 1] - k0;
+    if (qt * kT5Rows >= nq) return; // before any allocation or barrier
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int i = qt * kT5Rows + tid; // this thread's query row
+    const uint32_t sbase = smem_u32(smem);
+
+    if (tid == 0) {
+        mbar_init(&bar_s, 1);
+        mbar_init(&bar_o, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        tmem_alloc(&tmem_slot, kT5Cols);
+        tmem_relinquish();
+    }
+    int lo = INT_MAX, hi = 0;
+    if (i < nq) {
+        const SeqMask s = resolve_mask(d.mask, b, q0, k0, nq, nk);
+        row_range(s, i, lo, hi);
+        if (hi <= lo) {
+            lo = INT_MAX;
+            hi = 0;
+        }
+    }
+    s_lo[tid] = lo;
+    s_hi[tid] = hi;
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16); // this warp's lanes
+
+    int cmin = INT_MAX, cmax = 0;
+    for (int r = 0; r < kT5Rows; ++r) {
+        cmin = min(cmin, s_lo[r]);
+        cmax = max(cmax, s_hi[r]);
+    }
+    const int kt_begin = cmax > 0 ? cmin / kT5Keys : 0;
+    const int kt_end = cmax > 0 ? (cmax + kT5Keys - 1) / kT5Keys : 0;
+
+    // ---- Q row -> (hi, lo) TF32 parts in TMEM --------------------------------------
+    {
+        const float qscale = d.scale * kLog2e;
+        const float *qrow = d.q + (int64_t)(q0 + (i < nq ? i : 0)) * d.q_stride + (int64_t)h * kT5HD;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            uint32_t qh[32], ql[32];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < nq) v = __ldg(reinterpret_cast<const float4 *>(qrow + half * 32 + c * 4));
+                const float e[4] = {v.x * qscale, v.y * qscale, v.z * qscale, v.w * qscale};
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    qh[c * 4 + x] = t5_tf32(e[x]);
+                    ql[c * 4 + x] = __float_as_uint(e[x] - __uint_as_float(qh[c * 4 + x]));
+                }
+            }
+            tmem_st32(trow + kColQhi + half * 32, qh);
+            if (X3) tmem_st32(trow + kColQlo + half * 32, ql);
+        }
+        tc_wait_st();
+    }
+
+    constexpr uint32_t kIdescS = t5_idesc(kT5Rows, kT5Keys, 0);
+    constexpr uint32_t kIdescO = t5_idesc(kT5Rows, kT5HD, 0);
+    const float *kbase = d.k + (int64_t)k0 * d.k_stride + (int64_t)h * kT5HD;
+    const float *vbase = d.v + (int64_t)k0 * d.v_stride + (int64_t)h * kT5HD;
+
+    float m = -INFINITY, l = 0.0f;
+    bool failed = false, dbg_skip = false;
+    uint32_t phase = 0;
+
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
+        // ---- previous tile's O MMAs must be done before V / P are overwritten -------
+        if (kt > kt_begin) {
+            const bool ok = mbar_wait(&bar_o, phase ^ 1);
+            if (__syncthreads_or(!ok)) {
+                failed = true;
+                break;
+            }
+            tc_fence_after();
+        }
+        // ---- K and V tiles: HBM -> registers -> (hi, lo) -> UMMA layout -------------
+        {
+            float4 kr[8], vr[8];
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int bid = it * 4 + warp;           // 32 blocks of 8 rows x 4 chunks
+                const int r = (bid & 7) * 8 + (lane & 7); // key row inside the tile
+                const int c = (bid >> 3) * 4 + (lane >> 3);
+                const int j = kt * kT5Keys + r;
+                kr[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                vr[it] = kr[it];
+                if (j < nk) {
+                    kr[it] = __ldg(reinterpret_cast<const float4 *>(kbase + (int64_t)j * d.k_stride + c * 4));
+                    vr[it] = __ldg(reinterpret_cast<const float4 *>(vbase + (int64_t)j * d.v_stride + c * 4));
+                }
+            }
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+                const int bid = it * 4 + warp;
+                const int r = (bid & 7) * 8 + (lane & 7);
+                const int c = (bid >> 3) * 4 + (lane >> 3);
+                const uint32_t koff = c * 1024 + (r >> 3) * 128 + (r & 7) * 16;
+                // V goes in transposed, [dim][key] K-major like the K tile: element (key r, dim n) at
+                // (r / 4) * 1024 + (n / 8) * 128 + (n % 8) * 16 + (r % 4) * 4
+                const uint32_t voff = (r >> 2) * 1024 + (r & 3) * 4;
+                const float ke[4] = {kr[it].x, kr[it].y, kr[it].z, kr[it].w};
+                const float ve[4] = {vr[it].x, vr[it].y, vr[it].z, vr[it].w};
+                uint4 khi, klo, vhi, vlo;
+                uint32_t *kh = &khi.x, *kl = &klo.x, *vh = &vhi.x, *vl = &vlo.x;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    kh[x] = t5_tf32(ke[x]);
+                    kl[x] = __float_as_uint(ke[x] - __uint_as_float(kh[x]));
+                    vh[x] = t5_tf32(ve[x]);
+                    vl[x] = __float_as_uint(ve[x] - __uint_as_float(vh[x]));
+                }
+                *reinterpret_cast<uint4 *>(smem + kOffK + koff) = khi;
+                if (X3) *reinterpret_cast<uint4 *>(smem + kOffK + kPlaneKV + koff) = klo;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const int n = c * 4 + x;
+                    const uint32_t o = voff + (n >> 3) * 128 + (n & 7) * 16;
+                    *reinterpret_cast<uint32_t *>(smem + kOffV + o) = vh[x];
+                    if (X3) *reinterpret_cast<uint32_t *>(smem + kOffV + kPlaneKV + o) = vl[x];
+                }
+            }
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+
+        // ---- S = Q K^T ----------------------------------------------------------------
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint64_t bh = t5_desc(sbase + kOffK + ks * 2048, 1024, 128);
+                const uint64_t bl = t5_desc(sbase + kOffK + kPlaneKV + ks * 2048, 1024, 128);
+                const uint32_t ah = tmem + kColQhi + ks * 8, al = tmem + kColQlo + ks * 8;
+                if (X3) {
+                    mma_ts(tmem + kColS, al, bh, kIdescS, ks > 0);
+                    mma_ts(tmem + kColS, ah, bl, kIdescS, 1);
+                    mma_ts(tmem + kColS, ah, bh, kIdescS, 1);
+                } else {
+                    mma_ts(tmem + kColS, ah, bh, kIdescS, ks > 0);
+                }
+            }
+            tc_commit(&bar_s);
+        }
+        {
+            const bool ok = mbar_wait(&bar_s, phase);
+            if (__syncthreads_or(!ok)) {
+                failed = true;
+                break;
+            }
+            tc_fence_after();
+        }
+
+        if (d.reserved2 == 1 || d.reserved2 == 2) { // debug taps: raw S row / Q hi row of the first tile
+            float t0[32], t1[32];
+            const uint32_t col = d.reserved2 == 1 ? kColS : kColQhi;
+            tmem_ld32(trow + col, t0);
+            tmem_ld32(trow + col + 32, t1);
+            tc_wait_ld();
+            if (i < nq && kt == kt_begin) {
+                float *orow = d.out + (int64_t)(q0 + i) * d.out_stride + (int64_t)h * kT5HD;
+                for (int c = 0; c < 32; ++c) {
+                    orow[c] = t0[c];
+                    orow[32 + c] = t1[c];
+                }
+            }
+            dbg_skip = true;
+            break;
+        }
+        // ---- softmax of this thread's row; P -> shared memory as the next A operand -----
+        const int j0 = kt * kT5Keys;
+        float corr = 1.0f;
+        {
+            float s[64];
+            {
+                float t0[32], t1[32];
+                tmem_ld32(trow + kColS, t0);
+                tmem_ld32(trow + kColS + 32, t1);
+                tc_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    s[c] = t0[c];
+                    s[32 + c] = t1[c];
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                const int j = j0 + c;
+                const bool ok = finite_f(s[c]) && j >= lo && j < hi;
+                s[c] = ok ? s[c] : -INFINITY;
+                mx = fmaxf(mx, s[c]);
+            }
+            const float mn = fmaxf(m, mx);
+            const float ref = mn == -INFINITY ? 0.0f : mn;
+            corr = t5_ex2(m - ref);
+            m = mn;
+            float rs = 0.0f;
+            const uint32_t prow = (tid >> 3) * 128 + (tid & 7) * 16;
+#pragma unroll
+            for (int kc = 0; kc < 16; ++kc) {
+                uint4 ph, pl;
+                uint32_t *h4 = &ph.x, *l4 = &pl.x;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float p = t5_ex2(s[kc * 4 + x] - ref);
+                    rs += p;
+                    h4[x] = t5_tf32(p);
+                    l4[x] = __float_as_uint(p - __uint_as_float(h4[x]));
+                }
+                *reinterpret_cast<uint4 *>(smem + kOffK + kc * 2048 + prow) = ph; // K tile space, S is complete
+                if (X3) *reinterpret_cast<uint4 *>(smem + kOffPlo + kc * 2048 + prow) = pl;
+            }
+            l = l * corr + rs;
+        }
+        // ---- rescale the running output where a row maximum moved -------------------------
+        if (kt > kt_begin && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float o[32];
+                uint32_t w[32];
+                tmem_ld32(trow + kColO + half * 32, o);
+                tc_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) w[c] = __float_as_uint(o[c] * corr);
+                tmem_st32(trow + kColO + half * 32, w);
+            }
+            tc_wait_st();
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncthreads();
+
+        // ---- O += P V ----------------------------------------------------------------------
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const uint64_t ah = t5_desc(sbase + kOffK + ks * 4096, 2048, 128);
+                const uint64_t al = t5_desc(sbase + kOffPlo + ks * 4096, 2048, 128);
+                const uint64_t bh = t5_desc(sbase + kOffV + ks * 2048, 1024, 128);
+                const uint64_t bl = t5_desc(sbase + kOffV + kPlaneKV + ks * 2048, 1024, 128);
+                const uint32_t first = (kt > kt_begin || ks > 0) ? 1u : 0u;
+                if (X3) {
+                    mma_ss(tmem + kColO, al, bh, kIdescO, first);
+                    mma_ss(tmem + kColO, ah, bl, kIdescO, 1);
+                    mma_ss(tmem + kColO, ah, bh, kIdescO, 1);
+                } else {
+                    mma_ss(tmem + kColO, ah, bh, kIdescO, first);
+                }
+            }
+            tc_commit(&bar_o);
+        }
+        phase ^= 1;
+    }
+
+    // ---- epilogue ----------------------------------------------------------------------------
+    if (!failed && !dbg_skip && kt_begin < kt_end) {
+        const bool ok = mbar_wait(&bar_o, phase ^ 1);
+        if (__syncthreads_or(!ok)) failed = true;
+        tc_fence_after();
+    }
+    if (dbg_skip) {
+    } else if (failed) {
+        if (tid == 0) atomicCAS(&g_t5_error, 0u, (1u << 24) | (blockIdx.x & 0xffffffu));
+    } else {
+        float *orow = d.out + (int64_t)(q0 + (i < nq ? i : 0)) * d.out_stride + (int64_t)h * kT5HD;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float o[32];
+            if (kt_begin < kt_end) {
+                tmem_ld32(trow + kColO + half * 32, o);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) o[c] = 0.0f;
+            }
+            if (i < nq) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (l > 0.0f) v = make_float4(o[c * 4] / l, o[c * 4 + 1] / l, o[c * 4 + 2] / l, o[c * 4 + 3] / l);
+                    if (d.reserved2 == 3) v = make_float4(o[c * 4], o[c * 4 + 1], o[c * 4 + 2], l);
+                    *reinterpret_cast<float4 *>(orow + half * 32 + c * 4) = v;
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem, kT5Cols);
+}
+
+bool tile5_kernel_supports(const fblt_attn_desc &d, const char **why) {
+    if (d.head_dim != 64) {
+        *why = "tcgen05 kernel: head_dim must be 64";
+        return false;
+    }
+    if (d.mask.group_rule == FBLT_GROUP_IDS) {
+        *why = "explicit group ids are not a key range";
+        return false;
+    }
+    if ((d.q_stride | d.k_stride | d.v_stride | d.out_stride) & 3) {
+        *why = "row strides must be multiples of 4 elements";
+        return false;
+    }
+    if (((uintptr_t)d.q | (uintptr_t)d.k | (uintptr_t)d.v | (uintptr_t)d.out) & 15) {
+        *why = "q/k/v/out must be 16-byte aligned";
+        return false;
+    }
+    if (d.batch > 65535 || d.num_heads > 65535) {
+        *why = "batch/heads exceed 65535";
+        return false;
+    }
+    return true;
+}
+
+template <bool X3>
+static int launch_tile5_t(const fblt_attn_desc &d, cudaStream_t stream) {
+    static int configured_device = -1;
+    int dev = 0;
+    FBLT_CUDA_TRY(cudaGetDevice(&dev));
+    if (configured_device != dev) {
+        FBLT_CUDA_TRY(cudaFuncSetAttribute(tile5_attn_kernel<X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5Smem));
+        configured_device = dev;
+    }
+    dim3 grid((d.max_q + kT5Rows - 1) / kT5Rows, d.num_heads, d.batch);
+    tile5_attn_kernel<X3><<<grid, kT5Threads, kT5Smem, stream>>>(d);
+    count_launch();
+    return check_launch("tile5_attn_kernel");
+}
+
+int launch_tile5_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
+    return d.precision != FBLT_PREC_TF32 ? launch_tile5_t<true>(d, stream) : launch_tile5_t<false>(d, stream);
+}
+
+} // namespace fblt
+
+// 0 when no tcgen05 CTA has given up on a bounded wait since the last call; otherwise the
+// recorded code. Synchronises the device and clears the word.
+extern "C" int fblt_tcgen05_error(void) {
+    unsigned int v = 0, zero = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, fblt::g_t5_error, sizeof(v)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(fblt::g_t5_error, &zero, sizeof(zero));
+    return (int)v;
+}

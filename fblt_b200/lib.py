@@ -18,7 +18,7 @@ c_u8_p = C.POINTER(C.c_uint8)
 OK, ERR_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_CAPACITY, ERR_LIMIT = range(7)
 BACKEND_CPU, BACKEND_CUDA = 0, 1
 GROUP_NONE, GROUP_PATCH_ENC, GROUP_PATCH_DEC, GROUP_PATCH_LEQ, GROUP_IDS = range(5)
-IMPL_AUTO, IMPL_ROW, IMPL_TILE = range(3)
+IMPL_AUTO, IMPL_ROW, IMPL_TILE, IMPL_TCGEN05 = range(4)
 PREC_FP32, PREC_TF32 = 0, 1
 
 
@@ -78,6 +78,7 @@ class DecodeDesc(C.Structure):
         ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("kv_new_stride", C.c_int64),
         ("out", C.c_void_p), ("out_stride", C.c_int64),
         ("scale", C.c_float), ("reserved", C.c_int32),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
     ]
 
 
@@ -113,6 +114,7 @@ SYMBOLS = {
     "fblt_session_decode": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
     "fblt_session_cache_lens": (C.c_int, [C.c_void_p, c_i32_p, C.c_int32]),
+    "fblt_tcgen05_error": (C.c_int, []),
     "fblt_launch_count": (C.c_uint64, []),
     "fblt_abi_sizes": (C.c_size_t, [C.POINTER(C.c_size_t), C.c_size_t]),
 }

@@ -221,7 +221,8 @@ def mask_materialize(batch: AttnBatch, seq: int):
 def make_decode(k_cache: torch.Tensor, v_cache: torch.Tensor, base_len: torch.Tensor, q: torch.Tensor,
                 out: torch.Tensor, num_heads: int, head_dim: int, n_new: int, scale: float, *,
                 block_mode: bool = False, window: int = 0, k_new: Optional[torch.Tensor] = None,
-                v_new: Optional[torch.Tensor] = None, max_len: Optional[int] = None, splits: int = 0) -> L.DecodeDesc:
+                v_new: Optional[torch.Tensor] = None, max_len: Optional[int] = None, splits: int = 0,
+                rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None) -> L.DecodeDesc:
     """k_cache / v_cache: [batch, cache_rows, E] fp32 CUDA; base_len: int32 CUDA [batch];
     q/out (and k_new/v_new): [batch * n_new, E]."""
     d = L.DecodeDesc()
@@ -237,6 +238,8 @@ def make_decode(k_cache: torch.Tensor, v_cache: torch.Tensor, base_len: torch.Te
         d.k_new, d.v_new, d.kv_new_stride = k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0)
     d.out, d.out_stride = out.data_ptr(), out.stride(0)
     d.scale = float(scale)
+    if rope_cos is not None:
+        d.rope_cos, d.rope_sin = rope_cos.data_ptr(), rope_sin.data_ptr()
     return d
 
 

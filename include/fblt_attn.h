@@ -204,7 +204,8 @@ typedef struct {
 typedef enum {
     FBLT_IMPL_AUTO = 0,   /* pick per shape */
     FBLT_IMPL_ROW = 1,    /* one warp per (query row, head), fp32 FMA; any head_dim % 4 == 0 up to 256, any mask */
-    FBLT_IMPL_TILE = 2    /* tensor-core tiles (head_dim 32/64/128, range masks) */
+    FBLT_IMPL_TILE = 2,   /* tensor-core tiles, mma.sync TF32 (head_dim 32/64/128, range masks) */
+    FBLT_IMPL_TCGEN05 = 3 /* tensor-core tiles, tcgen05 + TMEM (head_dim 64, range masks) */
 } fblt_impl;
 
 typedef enum {
@@ -317,6 +318,14 @@ typedef struct {
     int64_t out_stride;
     float scale;
     int32_t reserved;
+    /* Optional fused rotary embedding (the per-head rope_apply + strided copies of
+     * infer/kv_cache.c:347-366): device tables [positions, head_dim/2] as
+     * blt_rope_precompute fills them (ops/reductions_cpu.c:179-197). When given, q and
+     * k_new hold the un-rotated rows of the QKV projection; the kernel rotates row r with
+     * position base + r (interleaved pairs, ops/reductions_cpu.c:217-228), attends, and
+     * writes the rotated K rows to the cache. NULL: rows arrive already rotated. */
+    const float *rope_cos;
+    const float *rope_sin;
 } fblt_decode_desc;
 
 /* Bytes of device scratch fblt_attn_decode needs for this descriptor (0 when
@@ -434,6 +443,13 @@ int fblt_session_decode(fblt_session *s, int32_t batch, int32_t n_new, int32_t b
                         int32_t advance);
 /* Current cache lengths (host copy), for checks. */
 int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch);
+
+/*
+ * The tcgen05 kernel bounds every mbarrier wait; a CTA whose wait runs out records a code,
+ * frees its TMEM and returns without writing its rows. This call synchronises the device,
+ * returns that code (0 = none, -1 = CUDA error) and clears it.
+ */
+int fblt_tcgen05_error(void);
 
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t fblt_launch_count(void);

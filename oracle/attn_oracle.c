@@ -384,3 +384,35 @@ size_t oracle_aligned_commit_select(const fblt_patch_info *patches, size_t num_p
     }
     return pick;
 }
+
+/* ---- rotary embedding (for the fused decode prologue) ---------------------- */
+
+/* ops/reductions_cpu.c:179-197 */
+void oracle_rope_precompute(size_t max_seq_len, float theta, size_t head_dim, float *cos_out, float *sin_out) {
+    const size_t half = head_dim / 2;
+    for (size_t pos = 0; pos < max_seq_len; ++pos) {
+        for (size_t i = 0; i < half; ++i) {
+            const float freq = 1.0f / powf(theta, (float)(2 * i) / (float)head_dim);
+            const float angle = (float)pos * freq;
+            cos_out[pos * half + i] = cosf(angle);
+            sin_out[pos * half + i] = sinf(angle);
+        }
+    }
+}
+
+/* ops/reductions_cpu.c:199-233: x, out are [rows, heads, head_dim]; cos/sin [rows, head_dim/2] */
+void oracle_rope_apply(const float *x, const float *cos_t, const float *sin_t, float *out, size_t rows,
+                       size_t heads, size_t head_dim) {
+    const size_t half = head_dim / 2;
+    for (size_t t = 0; t < rows; ++t) {
+        for (size_t h = 0; h < heads; ++h) {
+            const float *xv = x + (t * heads + h) * head_dim;
+            float *ov = out + (t * heads + h) * head_dim;
+            for (size_t i = 0; i < half; ++i) {
+                const float a = xv[2 * i], b = xv[2 * i + 1];
+                ov[2 * i] = a * cos_t[t * half + i] - b * sin_t[t * half + i];
+                ov[2 * i + 1] = b * cos_t[t * half + i] + a * sin_t[t * half + i];
+            }
+        }
+    }
+}

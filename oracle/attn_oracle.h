@@ -69,4 +69,9 @@ uint32_t oracle_unmask_select_eb(const float *scores, const uint8_t *masked, siz
 size_t oracle_block_adapt_b(size_t cur_b, double rolling_acceptance, size_t b_min, size_t b_max, float target);
 size_t oracle_aligned_commit_select(const fblt_patch_info *patches, size_t num_patches, size_t lo, size_t hi);
 
+/* ops/reductions_cpu.c:179-197 and :199-233 (rotary tables and their application). */
+void oracle_rope_precompute(size_t max_seq_len, float theta, size_t head_dim, float *cos_out, float *sin_out);
+void oracle_rope_apply(const float *x, const float *cos_t, const float *sin_t, float *out, size_t rows, size_t heads,
+                       size_t head_dim);
+
 #endif

@@ -103,6 +103,31 @@ def ref() -> C.CDLL:
     return _ref
 
 
+def rope_tables(max_len: int, head_dim: int, theta: float = 500000.0, use_ref: bool = False):
+    """cos/sin tables [max_len, head_dim/2] as blt_rope_precompute fills them."""
+    cs = np.empty((max_len, head_dim // 2), dtype=np.float32)
+    sn = np.empty_like(cs)
+    fn = ref().ref_rope_precompute if use_ref else oracle().oracle_rope_precompute
+    fn.argtypes = [C.c_size_t, C.c_float, C.c_size_t, c_f_p, c_f_p]
+    fn.restype = None
+    fn(max_len, theta, head_dim, _fp(cs), _fp(sn))
+    return cs, sn
+
+
+def rope_apply(x: np.ndarray, cos_rows: np.ndarray, sin_rows: np.ndarray, heads: int, head_dim: int,
+               use_ref: bool = False) -> np.ndarray:
+    """x: [rows, heads*head_dim]; cos_rows/sin_rows: [rows, head_dim/2] (already gathered per row)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    cos_rows = np.ascontiguousarray(cos_rows, dtype=np.float32)
+    sin_rows = np.ascontiguousarray(sin_rows, dtype=np.float32)
+    out = np.empty_like(x)
+    fn = ref().ref_rope_apply if use_ref else oracle().oracle_rope_apply
+    fn.argtypes = [c_f_p, c_f_p, c_f_p, c_f_p, C.c_size_t, C.c_size_t, C.c_size_t]
+    fn.restype = None
+    fn(_fp(x), _fp(cos_rows), _fp(sin_rows), _fp(out), x.shape[0], heads, head_dim)
+    return out
+
+
 def host_cores() -> int:
     try:
         return len(os.sched_getaffinity(0))

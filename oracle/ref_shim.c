@@ -26,6 +26,7 @@
 #include "ops/attn_core.h"
 #include "ops/mask_builder.h"
 #include "ops/patch_pool.h"
+#include "ops/rope.h"
 
 void ref_attention_head(const blt_attention_head_args *a) { blt_attention_head_core(BLT_BACKEND_CPU, a); }
 
@@ -148,6 +149,24 @@ size_t ref_block_adapt_b(size_t cur, double acc, size_t lo, size_t hi, float tar
 }
 size_t ref_aligned_commit_select(const blt_patch_info *p, size_t n, size_t lo, size_t hi) {
     return blt_aligned_commit_select(p, n, lo, hi);
+}
+
+void ref_rope_precompute(size_t max_seq_len, float theta, size_t head_dim, float *cos_out, float *sin_out) {
+    blt_rope_config cfg = {.theta = theta, .head_dim = head_dim};
+    blt_tensor c, s;
+    blt_tensor_view_2d(&c, cos_out, max_seq_len, head_dim / 2, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&s, sin_out, max_seq_len, head_dim / 2, BLT_BACKEND_CPU);
+    blt_rope_precompute(max_seq_len, &cfg, &c, &s);
+}
+
+void ref_rope_apply(const float *x, const float *cos_t, const float *sin_t, float *out, size_t rows, size_t heads,
+                    size_t head_dim) {
+    blt_tensor xt, ct, st, ot;
+    blt_tensor_view_3d(&xt, (void *)x, rows, heads, head_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_3d(&ot, out, rows, heads, head_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&ct, (void *)cos_t, rows, head_dim / 2, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&st, (void *)sin_t, rows, head_dim / 2, BLT_BACKEND_CPU);
+    blt_rope_apply(&xt, &ct, &st, &ot);
 }
 
 /* sizeof / offsetof of the ABI structs, for the layout check of include/fblt_attn.h. */

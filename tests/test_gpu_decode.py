@@ -137,3 +137,38 @@ def test_full_size_decode_properties(cuda_lib):
     torch.cuda.synchronize()
     err = (out2 - o_c[:sub * n]).abs()
     assert float((err - (1e-4 + 1e-3 * out2.abs())).max()) <= 0
+
+
+@pytest.mark.parametrize("n_new,block_mode", [(1, False), (4, True), (6, False)])
+def test_fused_rotary_prologue(cuda_lib, n_new, block_mode):
+    """q / k_new handed over un-rotated with the rotary tables: the kernel must give what the
+    reference gives when it rotates per head first (infer/kv_cache.c:347-366) and then attends,
+    and the K rows it writes through must equal the CPU-rotated rows bit for bit."""
+    import copy
+    from oracle import binding as ob
+    from helpers import use_ref
+    lens = np.array([0, 5, 130, 300], dtype=np.int32)
+    case = workloads.decode_case(150 + n_new, len(lens), 4, n_new, block_mode, lens=lens)
+    H, hd, E = case.num_heads, case.head_dim, case.embed
+    cos_t, sin_t = ob.rope_tables(512, hd, use_ref=use_ref())
+    pos = (lens[:, None] + np.arange(n_new)[None, :]).reshape(-1)
+    rot = copy.copy(case)
+    rot.q = ob.rope_apply(case.q, cos_t[pos], sin_t[pos], H, hd, use_ref=use_ref())
+    rot.k_new = ob.rope_apply(case.k_new, cos_t[pos], sin_t[pos], H, hd, use_ref=use_ref())
+    want, _ = oracle_decode(rot)
+
+    kc, vc = torch.from_numpy(case.k_cache).cuda(), torch.from_numpy(case.v_cache).cuda()
+    base, q = torch.from_numpy(case.base_len).cuda(), torch.from_numpy(case.q).cuda()
+    kn, vn = torch.from_numpy(case.k_new).cuda(), torch.from_numpy(case.v_new).cuda()
+    out = torch.full_like(q, float("nan"))
+    cos_d, sin_d = torch.from_numpy(cos_t).cuda(), torch.from_numpy(sin_t).cuda()   # must outlive the descriptor
+    for splits in (1, 3):
+        d = ops.make_decode(kc, vc, base, q, out, H, hd, n_new, case.scale, block_mode=block_mode, k_new=kn, v_new=vn,
+                            max_len=int(lens.max()) + n_new, splits=splits, rope_cos=cos_d, rope_sin=sin_d)
+        ops.attn_decode(d, ops.decode_workspace(d))
+        torch.cuda.synchronize()
+        assert_close(out.cpu().numpy(), want, f"fused rotary splits={splits}")
+    kc_h = kc.cpu().numpy()
+    for b in range(len(lens)):
+        got = kc_h[b, lens[b]:lens[b] + n_new]
+        assert got.tobytes() == rot.k_new[b * n_new:(b + 1) * n_new].tobytes()

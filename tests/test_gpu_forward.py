@@ -18,8 +18,13 @@ KERNELS = [(L.IMPL_ROW, L.PREC_FP32), (L.IMPL_TILE, L.PREC_FP32), (L.IMPL_TILE, 
 TF32_ATOL, TF32_RTOL = 2e-3, 2e-2
 
 
+T5_KERNELS = [(L.IMPL_TCGEN05, L.PREC_FP32), (L.IMPL_TCGEN05, L.PREC_TF32)]
+
+
 def check(case: ForwardCase, kernels=KERNELS):
     want, masks, _ = oracle_forward(case)
+    if kernels is KERNELS and case.head_dim == 64 and case.mask.group_rule != L.GROUP_IDS:
+        kernels = KERNELS + T5_KERNELS          # the tcgen05 kernel takes head_dim 64
     for impl, prec in kernels:
         got, _ = forward_gpu(case, impl, prec)
         what = f"{case.name} impl={impl} prec={prec}"
@@ -27,6 +32,8 @@ def check(case: ForwardCase, kernels=KERNELS):
             assert_close(got, want, what, atol=TF32_ATOL, rtol=TF32_RTOL)
         else:
             assert_close(got, want, what)
+        if impl == L.IMPL_TCGEN05:
+            assert L.load().fblt_tcgen05_error() == 0, "a tcgen05 CTA gave up on a bounded wait"
     return want
 
 
@@ -136,6 +143,11 @@ def test_full_size_prefill_properties(cuda_lib):
     o_row = run(v, L.IMPL_ROW)
     err = (o_tile - o_row).abs()
     assert float((err - (1e-4 + 1e-3 * o_row.abs())).max()) <= 0
+    o_t5 = run(v, L.IMPL_TCGEN05)
+    assert L.load().fblt_tcgen05_error() == 0
+    err = (o_t5 - o_row).abs()
+    assert float((err - (1e-4 + 1e-3 * o_row.abs())).max()) <= 0
+    del o_t5
     v2 = torch.roll(v, 1, 0).contiguous()
     o2 = run(v2, L.IMPL_TILE)
     o12 = run((v + v2).contiguous(), L.IMPL_TILE)
