@@ -99,9 +99,11 @@ extern "C" int fblt_attn_forward(const fblt_attn_desc *d, void *stream) {
         return launch_tile5_kernel(*d, s);
     case FBLT_IMPL_AUTO:
         // short per-row key ranges (a patch's own bytes, one latent) stay on the row kernel
-        if ((d->mask.group_rule == FBLT_GROUP_NONE || d->mask.group_rule == FBLT_GROUP_PATCH_LEQ) && d->max_k >= 32 &&
-            tile_kernel_supports(*d, &why))
-            return launch_tile_kernel(*d, s);
+        if ((d->mask.group_rule == FBLT_GROUP_NONE || d->mask.group_rule == FBLT_GROUP_PATCH_LEQ) && d->max_k >= 32) {
+            // 128-row tcgen05 tiles once sequences fill most of a tile; 64-row mma.sync tiles otherwise
+            if (d->max_q >= 96 && tile5_kernel_supports(*d, &why)) return launch_tile5_kernel(*d, s);
+            if (tile_kernel_supports(*d, &why)) return launch_tile_kernel(*d, s);
+        }
         return launch_row_kernel(*d, s);
     default: return fail(FBLT_ERR_ARG, "attn: unknown impl %d", d->impl);
     }

@@ -189,6 +189,8 @@ extern "C" int fblt_session_forward(fblt_session *s, const fblt_attn_desc *hd) {
     if (st != FBLT_OK) return st;
     FBLT_CUDA_TRY(cudaMemcpy2DAsync(hd->out, (size_t)hd->out_stride * 4, s->d_out, wb, wb, (size_t)tq, cudaMemcpyDeviceToHost, s->stream));
     FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    if (const int code = fblt_tcgen05_error())
+        return fail(FBLT_ERR_CUDA, "session_forward: a tcgen05 CTA gave up on a bounded wait (code 0x%x)", code);
     return FBLT_OK;
 }
 

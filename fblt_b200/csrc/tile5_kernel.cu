@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t bar_s, bar_o;
     __shared__ uint32_t tmem_slot;
-    __shared__ int s_lo[kT5Rows], s_hi[kT5Rows];
+    __shared__ int s_lo[4], s_hi[4]; // per-warp minimum / maximum of the rows' key ranges
 
     const int b = blockIdx.z, h = blockIdx.y, qt = blockIdx.x;
     const int q0 = d.cu_q[b], nq = d.cu_q[b + 1] - q0;
@@ -185,21 +185,109 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
             hi = 0;
         }
     }
-    s_lo[tid] = lo;
-    s_hi[tid] = hi;
+    {
+        int wl = lo, wh = hi;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            wl = min(wl, __shfl_xor_sync(0xffffffffu, wl, o));
+            wh = max(wh, __shfl_xor_sync(0xffffffffu, wh, o));
+        }
+        if (lane == 0) {
+            s_lo[warp] = wl;
+            s_hi[warp] = wh;
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16); // this warp's lanes
 
-    int cmin = INT_MAX, cmax = 0;
-    for (int r = 0; r < kT5Rows; ++r) {
-        cmin = min(cmin, s_lo[r]);
-        cmax = max(cmax, s_hi[r]);
-    }
+    const int cmin = min(min(s_lo[0], s_lo[1]), min(s_lo[2], s_lo[3]));
+    const int cmax = max(max(s_hi[0], s_hi[1]), max(s_hi[2], s_hi[3]));
     const int kt_begin = cmax > 0 ? cmin / kT5Keys : 0;
     const int kt_end = cmax > 0 ? (cmax + kT5Keys - 1) / kT5Keys : 0;
+
+    constexpr uint32_t kIdescS = t5_idesc(kT5Rows, kT5Keys, 0);
+    constexpr uint32_t kIdescO = t5_idesc(kT5Rows, kT5HD, 0);
+    const float *kbase = d.k + (int64_t)k0 * d.k_stride + (int64_t)h * kT5HD;
+    const float *vbase = d.v + (int64_t)k0 * d.v_stride + (int64_t)h * kT5HD;
+
+    float m = -INFINITY, l = 0.0f;
+    bool failed = false, dbg_skip = false;
+    uint32_t phase = 0;
+
+    // K/V tile staging. Loads: 16-byte pieces into registers (issued one tile ahead so that HBM
+    // latency hides behind the previous tile's MMAs and softmax). Stores: K as [key][dim] core
+    // matrices with 16-byte stores; V transposed to [dim][key] with 4-byte stores whose lane
+    // mapping (4 keys x 2 pieces x 4 rotations of the element order) touches 32 distinct banks.
+    float4 kr[8], vr[8];
+    const int v_rl = (lane & 3) + 4 * (lane >> 3), v_cl = (lane >> 2) & 1, v_xo = lane >> 3;
+    auto load_tile = [&](int kt) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int bid = it * 4 + warp;
+            {   // K: 8 keys x 4 pieces per warp step
+                const int r = (bid & 7) * 8 + (lane & 7), c = (bid >> 3) * 4 + (lane >> 3);
+                const int j = kt * kT5Keys + r;
+                kr[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (j < nk) kr[it] = __ldg(reinterpret_cast<const float4 *>(kbase + (int64_t)j * d.k_stride + c * 4));
+            }
+            {   // V: 16 keys x 2 pieces per warp step
+                const int r = (bid & 3) * 16 + v_rl, c = (bid >> 2) * 2 + v_cl;
+                const int j = kt * kT5Keys + r;
+                vr[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (j < nk) vr[it] = __ldg(reinterpret_cast<const float4 *>(vbase + (int64_t)j * d.v_stride + c * 4));
+            }
+        }
+    };
+    auto store_tile = [&]() {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int bid = it * 4 + warp;
+            {
+                const int r = (bid & 7) * 8 + (lane & 7), c = (bid >> 3) * 4 + (lane >> 3);
+                const uint32_t koff = c * 1024 + (r >> 3) * 128 + (r & 7) * 16;
+                const float ke[4] = {kr[it].x, kr[it].y, kr[it].z, kr[it].w};
+                uint4 khi, klo;
+                uint32_t *kh = &khi.x, *kl = &klo.x;
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    kh[x] = t5_tf32(ke[x]);
+                    kl[x] = __float_as_uint(ke[x] - __uint_as_float(kh[x]));
+                }
+                *reinterpret_cast<uint4 *>(smem + kOffK + koff) = khi;
+                if (X3) *reinterpret_cast<uint4 *>(smem + kOffK + kPlaneKV + koff) = klo;
+            }
+            {
+                const int r = (bid & 3) * 16 + v_rl, c = (bid >> 2) * 2 + v_cl;
+                // rotate the four elements by v_xo so that store step s writes element (s + v_xo) & 3
+                float e0 = vr[it].x, e1 = vr[it].y, e2 = vr[it].z, e3 = vr[it].w;
+                if (v_xo & 1) {
+                    const float t = e0;
+                    e0 = e1; e1 = e2; e2 = e3; e3 = t;
+                }
+                if (v_xo & 2) {
+                    float t = e0;
+                    e0 = e2; e2 = t;
+                    t = e1;
+                    e1 = e3; e3 = t;
+                }
+                const float ve[4] = {e0, e1, e2, e3};
+                const uint32_t vbase_off = (r >> 2) * 1024 + (r & 3) * 4;
+#pragma unroll
+                for (int st = 0; st < 4; ++st) {
+                    const int n = c * 4 + ((st + v_xo) & 3);
+                    const uint32_t o = vbase_off + (n >> 3) * 128 + (n & 7) * 16;
+                    const uint32_t vh = t5_tf32(ve[st]);
+                    *reinterpret_cast<uint32_t *>(smem + kOffV + o) = vh;
+                    if (X3) *reinterpret_cast<uint32_t *>(smem + kOffV + kPlaneKV + o) = __float_as_uint(ve[st] - __uint_as_float(vh));
+                }
+            }
+        }
+    };
+
+    if (kt_begin < kt_end) load_tile(kt_begin);
 
     // ---- Q row -> (hi, lo) TF32 parts in TMEM --------------------------------------
     {
@@ -225,14 +313,6 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
         tc_wait_st();
     }
 
-    constexpr uint32_t kIdescS = t5_idesc(kT5Rows, kT5Keys, 0);
-    constexpr uint32_t kIdescO = t5_idesc(kT5Rows, kT5HD, 0);
-    const float *kbase = d.k + (int64_t)k0 * d.k_stride + (int64_t)h * kT5HD;
-    const float *vbase = d.v + (int64_t)k0 * d.v_stride + (int64_t)h * kT5HD;
-
-    float m = -INFINITY, l = 0.0f;
-    bool failed = false, dbg_skip = false;
-    uint32_t phase = 0;
 
     for (int kt = kt_begin; kt < kt_end; ++kt) {
         // ---- previous tile's O MMAs must be done before V / P are overwritten -------
@@ -244,53 +324,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
             }
             tc_fence_after();
         }
-        // ---- K and V tiles: HBM -> registers -> (hi, lo) -> UMMA layout -------------
-        {
-            float4 kr[8], vr[8];
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-                const int bid = it * 4 + warp;           // 32 blocks of 8 rows x 4 chunks
-                const int r = (bid & 7) * 8 + (lane & 7); // key row inside the tile
-                const int c = (bid >> 3) * 4 + (lane >> 3);
-                const int j = kt * kT5Keys + r;
-                kr[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                vr[it] = kr[it];
-                if (j < nk) {
-                    kr[it] = __ldg(reinterpret_cast<const float4 *>(kbase + (int64_t)j * d.k_stride + c * 4));
-                    vr[it] = __ldg(reinterpret_cast<const float4 *>(vbase + (int64_t)j * d.v_stride + c * 4));
-                }
-            }
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-                const int bid = it * 4 + warp;
-                const int r = (bid & 7) * 8 + (lane & 7);
-                const int c = (bid >> 3) * 4 + (lane >> 3);
-                const uint32_t koff = c * 1024 + (r >> 3) * 128 + (r & 7) * 16;
-                // V goes in transposed, [dim][key] K-major like the K tile: element (key r, dim n) at
-                // (r / 4) * 1024 + (n / 8) * 128 + (n % 8) * 16 + (r % 4) * 4
-                const uint32_t voff = (r >> 2) * 1024 + (r & 3) * 4;
-                const float ke[4] = {kr[it].x, kr[it].y, kr[it].z, kr[it].w};
-                const float ve[4] = {vr[it].x, vr[it].y, vr[it].z, vr[it].w};
-                uint4 khi, klo, vhi, vlo;
-                uint32_t *kh = &khi.x, *kl = &klo.x, *vh = &vhi.x, *vl = &vlo.x;
-#pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    kh[x] = t5_tf32(ke[x]);
-                    kl[x] = __float_as_uint(ke[x] - __uint_as_float(kh[x]));
-                    vh[x] = t5_tf32(ve[x]);
-                    vl[x] = __float_as_uint(ve[x] - __uint_as_float(vh[x]));
-                }
-                *reinterpret_cast<uint4 *>(smem + kOffK + koff) = khi;
-                if (X3) *reinterpret_cast<uint4 *>(smem + kOffK + kPlaneKV + koff) = klo;
-#pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    const int n = c * 4 + x;
-                    const uint32_t o = voff + (n >> 3) * 128 + (n & 7) * 16;
-                    *reinterpret_cast<uint32_t *>(smem + kOffV + o) = vh[x];
-                    if (X3) *reinterpret_cast<uint32_t *>(smem + kOffV + kPlaneKV + o) = vl[x];
-                }
-            }
-        }
+        store_tile();
         fence_async_smem();
         tc_fence_before();
         __syncthreads();
@@ -313,6 +347,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
             }
             tc_commit(&bar_s);
         }
+        if (kt + 1 < kt_end) load_tile(kt + 1); // in flight while S completes and the softmax runs
         {
             const bool ok = mbar_wait(&bar_s, phase);
             if (__syncthreads_or(!ok)) {
