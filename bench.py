@@ -274,13 +274,17 @@ def main():
     qn = torch.randn((B * N_NEW, E), generator=gen, device=dev)
     kn = torch.randn((B * N_NEW, E), generator=gen, device=dev)
     vn = torch.randn((B * N_NEW, E), generator=gen, device=dev)
-    out_d = torch.empty((args.decode_steps, B * N_NEW, E), device=dev)
+    # two decode-output buffers: step i's rows are gathered while step i + 1 computes into the other
+    out_d2 = [torch.empty((args.decode_steps, B * N_NEW, E), device=dev) for _ in range(2 if world > 1 else 1)]
+    out_d = out_d2[0]
     lens_all = (BASE_LEN + N_NEW * torch.arange(args.decode_steps, device=dev, dtype=torch.int32))[:, None] \
         .expand(args.decode_steps, B).contiguous()
     pre = ops.make_batch(qkv[:, 0:E], qkv[:, E:2 * E], qkv[:, 2 * E:], out_p, cu, cu, H, HD, SCALE,
                          ops.MaskConfig(is_causal=True))
-    dec = [ops.make_decode(kc, vc, lens_all[t], qn, out_d[t], H, HD, N_NEW, SCALE, block_mode=True, k_new=kn,
-                           v_new=vn, max_len=BASE_LEN + N_NEW * (t + 1)) for t in range(args.decode_steps)]
+    dec2 = [[ops.make_decode(kc, vc, lens_all[t], qn, od[t], H, HD, N_NEW, SCALE, block_mode=True, k_new=kn,
+                             v_new=vn, max_len=BASE_LEN + N_NEW * (t + 1)) for t in range(args.decode_steps)]
+            for od in out_d2]
+    dec = dec2[0]
     ws = ops.decode_workspace(dec[-1])
 
     main_stream = torch.cuda.Stream(device=dev)
@@ -294,6 +298,9 @@ def main():
         assert equal, "decode gather assumes equal sequence counts per rank"
 
     ev_pre_done = torch.cuda.Event()
+    ev_dec_done = [torch.cuda.Event() for _ in out_d2]
+    ev_gathered = [torch.cuda.Event() for _ in out_d2]   # the buffer's rows have left: it may be overwritten
+    ev_pre_gathered = torch.cuda.Event()
     dec_t0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.warmup + args.steps)]
     dec_t1 = [torch.cuda.Event(enable_timing=True) for _ in range(args.warmup + args.steps)]
 
@@ -301,20 +308,29 @@ def main():
 
     def one_step(it: int):
         with torch.cuda.stream(main_stream):
+            buf = it % len(out_d2)
             pre_t0[it].record(main_stream)
+            if world > 1 and it > 0:
+                main_stream.wait_event(ev_pre_gathered)      # last step's prefill rows have been sent
             ops.attn_forward(pre, main_stream)
             if world > 1:
                 ev_pre_done.record(main_stream)
                 comm_stream.wait_event(ev_pre_done)
                 with torch.cuda.stream(comm_stream):   # prefill rows travel while decode runs
                     shard.gather_rows(out_p, rows_per_rank, padded=pad_p, gathered=gath_p)
+                    ev_pre_gathered.record(comm_stream)
+                if it >= len(out_d2):
+                    main_stream.wait_event(ev_gathered[buf])  # this buffer's previous rows have been sent
             dec_t0[it].record(main_stream)
             for t in range(args.decode_steps):
-                ops.attn_decode(dec[t], ws, main_stream)
+                ops.attn_decode(dec2[buf][t], ws, main_stream)
             dec_t1[it].record(main_stream)
-            if world > 1:
-                dist.all_gather_into_tensor(gath_d.view(-1, E), out_d.view(-1, E))
-                main_stream.wait_stream(comm_stream)
+            if world > 1:   # decode rows travel while the next step computes
+                ev_dec_done[buf].record(main_stream)
+                comm_stream.wait_event(ev_dec_done[buf])
+                with torch.cuda.stream(comm_stream):
+                    dist.all_gather_into_tensor(gath_d.view(-1, E), out_d2[buf].view(-1, E))
+                    ev_gathered[buf].record(comm_stream)
 
     def barrier():
         if world > 1:
@@ -333,6 +349,7 @@ def main():
     t_begin.record(main_stream)
     for it in range(args.steps):
         one_step(args.warmup + it)
+    main_stream.wait_stream(comm_stream)   # the timed region ends when the last gather has landed
     t_end.record(main_stream)
     barrier()
     launches = lib.fblt_launch_count() - launches0
@@ -383,7 +400,8 @@ def main():
     # ---- CPU baseline on a bounded sample of the same tensors (rank 0, one GPU) ----
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
-        cpu = run_cpu_baseline(args, torch, qkv, cu, kc, vc, qn, kn, vn, out_p, out_d, total_rows)
+        cpu = run_cpu_baseline(args, torch, qkv, cu, kc, vc, qn, kn, vn, out_p,
+                               out_d2[(args.warmup + args.steps - 1) % len(out_d2)], total_rows)
 
     if rank == 0:
         line = {
