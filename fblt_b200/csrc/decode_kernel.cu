@@ -7,8 +7,11 @@
 //   * a key row of one head (head_dim floats) is covered by head_dim/4 lanes
 //     with one 16-byte load each, so a warp instruction fetches 32/(head_dim/4)
 //     complete rows, and U such loads for K and V are in flight per lane;
-//   * scores are reduced inside the lane group with xor shuffles, softmax is
-//     online per lane group in the log2 domain, groups / warps merge at the end;
+//   * the partial scores of a chunk are reduced inside the lane group with a
+//     transposing butterfly that leaves one complete score per lane; that lane
+//     runs the online softmax (log2 domain) for it and the probabilities are
+//     broadcast for the PV accumulation; groups / warps merge at the end;
+//   * optionally the rotary embedding of the new q / k rows is applied on load;
 //   * keys every row of the CTA can see take the unmasked path; the few keys at
 //     the window edge and the freshly appended rows take a per-row checked path;
 //   * split-K writes (m, l, acc) partials to caller scratch; a second small
@@ -23,7 +26,7 @@ constexpr int kDecWarps = 4;
 constexpr int kDecThreads = kDecWarps * 32;
 
 struct DecodeParams {
-    int batch, H, n_new, block_mode, window, splits, qgroups;
+    int batch, H, n_new, block_mode, window, splits, qgroups, base_add;
     const int32_t *base_len;
     float *kc, *vc;
     int64_t seq_stride, row_stride;
@@ -118,7 +121,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int grp = lane / LPK, dl = lane % LPK;
     const int n = p.n_new;
-    const int base = p.base_len[b];
+    const int base = p.base_len[b] + p.base_add;
     const int total = base + n;
     const int r0 = qg * NQ;
     const int nv = min(NQ, n - r0); // valid rows in this query group (>= 1)
@@ -489,6 +492,7 @@ extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size
     const int nq = pick_nq(d->n_new);
     p.qgroups = (d->n_new + nq - 1) / nq;
     p.base_len = d->base_len;
+    p.base_add = d->base_add;
     p.kc = d->k_cache;
     p.vc = d->v_cache;
     p.seq_stride = d->cache_seq_stride;
@@ -581,6 +585,7 @@ extern "C" int fblt_attn_decode_static(const fblt_decode_desc *d, void *stream) 
     const int nq = pick_nq(d->n_new);
     p.qgroups = (d->n_new + nq - 1) / nq;
     p.base_len = d->base_len;
+    p.base_add = d->base_add;
     p.kc = d->k_cache;
     p.vc = d->v_cache;
     p.seq_stride = d->cache_seq_stride;

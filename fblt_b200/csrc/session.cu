@@ -19,6 +19,10 @@ struct fblt_session {
     float *kc = nullptr, *vc = nullptr;
     int32_t *d_lens = nullptr, *h_lens = nullptr;
     float *d_qn = nullptr, *d_kn = nullptr, *d_vn = nullptr, *d_on = nullptr;
+    // second staging slot, copy streams and events of the pipelined multi-step decode
+    float *d_qn2 = nullptr, *d_kn2 = nullptr, *d_vn2 = nullptr, *d_on2 = nullptr;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_kernel[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
     void *ws = nullptr;
     size_t ws_bytes = 0;
 };
@@ -37,6 +41,17 @@ static void session_free(fblt_session *s) {
     cudaFree(s->d_kn);
     cudaFree(s->d_vn);
     cudaFree(s->d_on);
+    cudaFree(s->d_qn2);
+    cudaFree(s->d_kn2);
+    cudaFree(s->d_vn2);
+    cudaFree(s->d_on2);
+    for (int i = 0; i < 2; ++i) {
+        if (s->ev_in[i]) cudaEventDestroy(s->ev_in[i]);
+        if (s->ev_kernel[i]) cudaEventDestroy(s->ev_kernel[i]);
+        if (s->ev_out[i]) cudaEventDestroy(s->ev_out[i]);
+    }
+    if (s->copy_in) cudaStreamDestroy(s->copy_in);
+    if (s->copy_out) cudaStreamDestroy(s->copy_out);
     cudaFree(s->ws);
     if (s->h_lens) cudaFreeHost(s->h_lens);
     if (s->stream) cudaStreamDestroy(s->stream);
@@ -112,6 +127,17 @@ extern "C" int fblt_session_create(fblt_session **out, int32_t max_batch, int32_
         S_TRY(cudaMalloc(&s->d_kn, nb));
         S_TRY(cudaMalloc(&s->d_vn, nb));
         S_TRY(cudaMalloc(&s->d_on, nb));
+        S_TRY(cudaMalloc(&s->d_qn2, nb));
+        S_TRY(cudaMalloc(&s->d_kn2, nb));
+        S_TRY(cudaMalloc(&s->d_vn2, nb));
+        S_TRY(cudaMalloc(&s->d_on2, nb));
+        S_TRY(cudaStreamCreateWithFlags(&s->copy_in, cudaStreamNonBlocking));
+        S_TRY(cudaStreamCreateWithFlags(&s->copy_out, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            S_TRY(cudaEventCreateWithFlags(&s->ev_in[i], cudaEventDisableTiming));
+            S_TRY(cudaEventCreateWithFlags(&s->ev_kernel[i], cudaEventDisableTiming));
+            S_TRY(cudaEventCreateWithFlags(&s->ev_out[i], cudaEventDisableTiming));
+        }
         // split-K partials exist only while (sequences x heads) is below the
         // launch-width target, which bounds units x splits
         s->ws_bytes = (size_t)2048 * max_new * ((size_t)head_dim + 4) * sizeof(float);
@@ -276,6 +302,76 @@ extern "C" int fblt_session_decode(fblt_session *s, int32_t batch, int32_t n_new
     FBLT_CUDA_TRY(cudaMemcpyAsync(out, s->d_on, nb, cudaMemcpyDeviceToHost, s->stream));
     FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
     for (int b = 0; b < batch; ++b) s->h_lens[b] += advance;
+    return FBLT_OK;
+}
+
+extern "C" int fblt_session_decode_steps(fblt_session *s, int32_t batch, int32_t n_new, int32_t steps, int32_t block_mode,
+                                         int32_t window, float scale, const float *q_new, const float *k_new,
+                                         const float *v_new, int64_t in_step_stride, float *out,
+                                         int64_t out_step_stride, int32_t advance) {
+    using namespace fblt;
+    if (!s || !q_new || !k_new || !v_new || !out) return fail(FBLT_ERR_ARG, "session_decode_steps: NULL argument");
+    if (batch < 0 || batch > s->max_batch || !s->kc) return fail(FBLT_ERR_CAPACITY, "session_decode_steps: batch %d exceeds the session", batch);
+    if (n_new < 1 || n_new > s->max_new) return fail(FBLT_ERR_CAPACITY, "session_decode_steps: n_new %d outside 1..%d", n_new, s->max_new);
+    if (advance < 0 || advance > n_new || steps < 0) return fail(FBLT_ERR_ARG, "session_decode_steps: bad advance / steps");
+    if (batch == 0 || steps == 0) return FBLT_OK;
+    int32_t max_len = 0;
+    for (int b = 0; b < batch; ++b) {
+        const int64_t last = (int64_t)s->h_lens[b] + (int64_t)(steps - 1) * advance + n_new;
+        if (last > s->cache_rows) return fail(FBLT_ERR_CAPACITY, "session_decode_steps: sequence %d would exceed cache_rows %d", b, s->cache_rows);
+        max_len = (int32_t)last > max_len ? (int32_t)last : max_len;
+    }
+    const size_t nb = (size_t)batch * n_new * s->E * sizeof(float);
+    FBLT_CUDA_TRY(cudaMemcpyAsync(s->d_lens, s->h_lens, (size_t)batch * sizeof(int32_t), cudaMemcpyHostToDevice, s->stream));
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    float *dq[2] = {s->d_qn, s->d_qn2}, *dk[2] = {s->d_kn, s->d_kn2}, *dv[2] = {s->d_vn, s->d_vn2}, *dout[2] = {s->d_on, s->d_on2};
+    for (int t = 0; t < steps; ++t) {
+        const int slot = t & 1;
+        // inputs of step t: once the kernel of step t-2 has finished reading this slot
+        if (t >= 2) FBLT_CUDA_TRY(cudaStreamWaitEvent(s->copy_in, s->ev_kernel[slot], 0));
+        FBLT_CUDA_TRY(cudaMemcpyAsync(dq[slot], q_new + (size_t)t * in_step_stride, nb, cudaMemcpyHostToDevice, s->copy_in));
+        FBLT_CUDA_TRY(cudaMemcpyAsync(dk[slot], k_new + (size_t)t * in_step_stride, nb, cudaMemcpyHostToDevice, s->copy_in));
+        FBLT_CUDA_TRY(cudaMemcpyAsync(dv[slot], v_new + (size_t)t * in_step_stride, nb, cudaMemcpyHostToDevice, s->copy_in));
+        FBLT_CUDA_TRY(cudaEventRecord(s->ev_in[slot], s->copy_in));
+        // kernel of step t: inputs present, and the output slot drained by step t-2's copy
+        FBLT_CUDA_TRY(cudaStreamWaitEvent(s->stream, s->ev_in[slot], 0));
+        if (t >= 2) FBLT_CUDA_TRY(cudaStreamWaitEvent(s->stream, s->ev_out[slot], 0));
+        fblt_decode_desc d;
+        memset(&d, 0, sizeof(d));
+        d.batch = batch;
+        d.num_heads = s->H;
+        d.head_dim = s->hd;
+        d.n_new = n_new;
+        d.block_mode = block_mode;
+        d.window = window;
+        d.max_len = max_len;
+        d.base_len = s->d_lens;
+        d.base_add = t * advance;
+        d.k_cache = s->kc;
+        d.v_cache = s->vc;
+        d.cache_seq_stride = (int64_t)s->cache_rows * s->E;
+        d.cache_row_stride = s->E;
+        d.q = dq[slot];
+        d.q_stride = s->E;
+        d.k_new = dk[slot];
+        d.v_new = dv[slot];
+        d.kv_new_stride = s->E;
+        d.out = dout[slot];
+        d.out_stride = s->E;
+        d.scale = scale;
+        if (fblt_attn_decode_workspace(&d) > s->ws_bytes) d.splits = 1;
+        const int st = fblt_attn_decode(&d, s->ws, s->ws_bytes, s->stream);
+        if (st != FBLT_OK) return st;
+        FBLT_CUDA_TRY(cudaEventRecord(s->ev_kernel[slot], s->stream));
+        // outputs of step t
+        FBLT_CUDA_TRY(cudaStreamWaitEvent(s->copy_out, s->ev_kernel[slot], 0));
+        FBLT_CUDA_TRY(cudaMemcpyAsync(out + (size_t)t * out_step_stride, dout[slot], nb, cudaMemcpyDeviceToHost, s->copy_out));
+        FBLT_CUDA_TRY(cudaEventRecord(s->ev_out[slot], s->copy_out));
+    }
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->copy_out));
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->copy_in));
+    for (int b = 0; b < batch; ++b) s->h_lens[b] += steps * advance;
     return FBLT_OK;
 }
 

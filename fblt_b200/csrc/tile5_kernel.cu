@@ -214,7 +214,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
     const float *vbase = d.v + (int64_t)k0 * d.v_stride + (int64_t)h * kT5HD;
 
     float m = -INFINITY, l = 0.0f;
-    bool failed = false, dbg_skip = false;
+    bool failed = false;
     uint32_t phase = 0;
 
     // K/V tile staging. Loads: 16-byte pieces into registers (issued one tile ahead so that HBM
@@ -357,22 +357,6 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
             tc_fence_after();
         }
 
-        if (d.reserved2 == 1 || d.reserved2 == 2) { // debug taps: raw S row / Q hi row of the first tile
-            float t0[32], t1[32];
-            const uint32_t col = d.reserved2 == 1 ? kColS : kColQhi;
-            tmem_ld32(trow + col, t0);
-            tmem_ld32(trow + col + 32, t1);
-            tc_wait_ld();
-            if (i < nq && kt == kt_begin) {
-                float *orow = d.out + (int64_t)(q0 + i) * d.out_stride + (int64_t)h * kT5HD;
-                for (int c = 0; c < 32; ++c) {
-                    orow[c] = t0[c];
-                    orow[32 + c] = t1[c];
-                }
-            }
-            dbg_skip = true;
-            break;
-        }
         // ---- softmax of this thread's row; P -> shared memory as the next A operand -----
         const int j0 = kt * kT5Keys;
         float corr = 1.0f;
@@ -461,13 +445,12 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
     }
 
     // ---- epilogue ----------------------------------------------------------------------------
-    if (!failed && !dbg_skip && kt_begin < kt_end) {
+    if (!failed && kt_begin < kt_end) {
         const bool ok = mbar_wait(&bar_o, phase ^ 1);
         if (__syncthreads_or(!ok)) failed = true;
         tc_fence_after();
     }
-    if (dbg_skip) {
-    } else if (failed) {
+    if (failed) {
         if (tid == 0) atomicCAS(&g_t5_error, 0u, (1u << 24) | (blockIdx.x & 0xffffffu));
     } else {
         float *orow = d.out + (int64_t)(q0 + (i < nq ? i : 0)) * d.out_stride + (int64_t)h * kT5HD;
@@ -486,7 +469,6 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 for (int c = 0; c < 8; ++c) {
                     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (l > 0.0f) v = make_float4(o[c * 4] / l, o[c * 4 + 1] / l, o[c * 4 + 2] / l, o[c * 4 + 3] / l);
-                    if (d.reserved2 == 3) v = make_float4(o[c * 4], o[c * 4 + 1], o[c * 4 + 2], l);
                     *reinterpret_cast<float4 *>(orow + half * 32 + c * 4) = v;
                 }
             }

@@ -77,7 +77,7 @@ class DecodeDesc(C.Structure):
         ("q", C.c_void_p), ("q_stride", C.c_int64),
         ("k_new", C.c_void_p), ("v_new", C.c_void_p), ("kv_new_stride", C.c_int64),
         ("out", C.c_void_p), ("out_stride", C.c_int64),
-        ("scale", C.c_float), ("reserved", C.c_int32),
+        ("scale", C.c_float), ("base_add", C.c_int32),
         ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
     ]
 
@@ -113,6 +113,9 @@ SYMBOLS = {
     "fblt_session_cache_load": (C.c_int, [C.c_void_p, C.c_int32, c_i32_p, C.c_void_p, C.c_void_p, C.c_int64]),
     "fblt_session_decode": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),
+    "fblt_session_decode_steps": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
+                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                            C.c_int32]),
     "fblt_session_cache_lens": (C.c_int, [C.c_void_p, c_i32_p, C.c_int32]),
     "fblt_tcgen05_error": (C.c_int, []),
     "fblt_launch_count": (C.c_uint64, []),

@@ -337,6 +337,14 @@ class Session:
                                               _ptr(q_new), _ptr(k_new), _ptr(v_new), _ptr(out),
                                               n_new if advance is None else advance))
 
+    def decode_steps(self, batch: int, n_new: int, steps: int, q_new, k_new, v_new, out, scale: float, *,
+                     in_step_stride: int = 0, out_step_stride: int = 0, block_mode: bool = False, window: int = 0,
+                     advance: Optional[int] = None) -> None:
+        """`steps` decode steps with known inputs, copies and kernels overlapped (strides in elements)."""
+        L.check(self._lib.fblt_session_decode_steps(self._h, batch, n_new, steps, int(block_mode), window, float(scale),
+                                                    _ptr(q_new), _ptr(k_new), _ptr(v_new), in_step_stride, _ptr(out),
+                                                    out_step_stride, n_new if advance is None else advance))
+
     def cache_lens(self, batch: int) -> np.ndarray:
         out = np.zeros(batch, dtype=np.int32)
         L.check(self._lib.fblt_session_cache_lens(self._h, out.ctypes.data_as(L.c_i32_p), batch))

@@ -317,7 +317,7 @@ typedef struct {
     float *out; /* device [batch*n_new rows] */
     int64_t out_stride;
     float scale;
-    int32_t reserved;
+    int32_t base_add; /* added to every base_len[b]: lets a run of steps share one length table */
     /* Optional fused rotary embedding (the per-head rope_apply + strided copies of
      * infer/kv_cache.c:347-366): device tables [positions, head_dim/2] as
      * blt_rope_precompute fills them (ops/reductions_cpu.c:179-197). When given, q and
@@ -441,6 +441,18 @@ int fblt_session_cache_load(fblt_session *s, int32_t batch, const int32_t *lens,
 int fblt_session_decode(fblt_session *s, int32_t batch, int32_t n_new, int32_t block_mode, int32_t window,
                         float scale, const float *q_new, const float *k_new, const float *v_new, float *out,
                         int32_t advance);
+/*
+ * A run of `steps` decode / block-verify steps whose input rows are all known up front
+ * (step t reads q_new + t * in_step_stride etc., writes out + t * out_step_stride; a stride
+ * of 0 re-reads the same rows). Same result as calling fblt_session_decode `steps` times,
+ * but the host->device copy of step t+1, the kernel of step t and the device->host copy of
+ * step t-1 overlap on three streams over double-buffered staging. Returns when all outputs
+ * are in host memory.
+ */
+int fblt_session_decode_steps(fblt_session *s, int32_t batch, int32_t n_new, int32_t steps, int32_t block_mode,
+                              int32_t window, float scale, const float *q_new, const float *k_new,
+                              const float *v_new, int64_t in_step_stride, float *out, int64_t out_step_stride,
+                              int32_t advance);
 /* Current cache lengths (host copy), for checks. */
 int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch);
 

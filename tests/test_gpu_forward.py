@@ -155,3 +155,15 @@ def test_full_size_prefill_properties(cuda_lib):
     # the first row of every sequence sees only itself: out == v exactly there
     first = torch.from_numpy(case.cu_q[:-1].astype(np.int64)).cuda()
     assert float((o_tile[first] - v[first]).abs().max()) < 1e-6
+
+
+def test_long_sequences_many_key_tiles(cuda_lib):
+    """Eleven 64-key tiles per row block: exercises the running-maximum rescale of the
+    accumulator in TMEM (tcgen05 kernel) and the two-stage pipeline (mma.sync kernel)."""
+    cu = np.array([0, 700, 700 + 130])
+    check(random_case(70, cu, cu, 2, 64, MaskConfig(is_causal=True)))
+    check(random_case(71, cu, cu, 2, 64, MaskConfig(is_causal=True, sliding_window=150)))
+    check(random_case(72, cu, cu, 2, 64, MaskConfig()))
+    # rectangular: 300 queries over 700 keys with a causal offset
+    cu_q, cu_k = np.array([0, 300]), np.array([0, 700])
+    check(random_case(73, cu_q, cu_k, 2, 64, MaskConfig(is_causal=True, causal_offset=[400])))

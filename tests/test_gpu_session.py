@@ -67,3 +67,33 @@ def test_session_decode_steps_and_rollback(cuda_lib):
         s.decode(4, 9, case.q, case.k_new, case.v_new, out, case.scale)
     assert e.value.status == L.ERR_CAPACITY
     s.close()
+
+
+def test_session_decode_steps_pipeline_equals_single_steps(cuda_lib):
+    """The overlapped multi-step call must return what the same steps give one at a time."""
+    base = np.array([7, 64, 130], dtype=np.int32)
+    n, steps, B = 4, 5, 3
+    case = workloads.decode_case(121, B, 4, n, True, lens=base, cache_rows=192)
+    E = case.embed
+    rng = np.random.default_rng(9)
+    q_all, k_all, v_all = (rng.standard_normal((steps, B * n, E)).astype(np.float32) for _ in range(3))
+    outs = []
+    for pipelined in (False, True):
+        s = ops.Session(B, 4, 64, cache_rows=192, max_new=n)
+        s.cache_load(base, case.k_cache, case.v_cache, 192)
+        out = np.full((steps, B * n, E), np.nan, dtype=np.float32)
+        if pipelined:
+            s.decode_steps(B, n, steps, q_all, k_all, v_all, out, case.scale, in_step_stride=B * n * E,
+                           out_step_stride=B * n * E, block_mode=True, advance=3)
+        else:
+            for t in range(steps):
+                s.decode(B, n, q_all[t], k_all[t], v_all[t], out[t], case.scale, block_mode=True, advance=3)
+        assert (s.cache_lens(B) == base + steps * 3).all()
+        outs.append(out)
+        s.close()
+    assert np.isfinite(outs[1]).all()
+    assert outs[0].tobytes() == outs[1].tobytes()
+    # and step 0 against the oracle
+    case.q, case.k_new, case.v_new = q_all[0], k_all[0], v_all[0]
+    want, _ = oracle_decode(case)
+    assert_close(outs[1][0], want, "pipelined step 0")
