@@ -75,20 +75,39 @@ __device__ __forceinline__ SeqMask resolve_mask(const fblt_mask_desc &m, int b, 
     return s;
 }
 
-// Number of entries of a[0..n) that are <= x (a ascending).
-__device__ __forceinline__ int count_le(const int32_t *a, int n, int x) {
-    int lo = 0, hi = n;
-    while (lo < hi) {
-        const int mid = (lo + hi) >> 1;
-        if (a[mid] <= x) lo = mid + 1;
-        else hi = mid;
+// Number of entries of a[0..n) that are <= x (a ascending): two ways to search.
+// ThreadSearch: one thread, binary search (each step waits for the previous load).
+struct ThreadSearch {
+    __device__ __forceinline__ int count_le(const int32_t *a, int n, int x) const {
+        int lo = 0, hi = n;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (a[mid] <= x) lo = mid + 1;
+            else hi = mid;
+        }
+        return lo;
     }
-    return lo;
-}
+};
+// WarpSearch: all 32 lanes of a converged warp ask the same question; every lane tests
+// its own entries (coalesced, independent loads) and the votes are counted.
+struct WarpSearch {
+    int lane;
+    __device__ __forceinline__ int count_le(const int32_t *a, int n, int x) const {
+        int c = 0;
+        for (int base = 0; base < n; base += 32) {
+            const int idx = base + lane;
+            const bool le = idx < n && a[idx] <= x;
+            c += __popc(__ballot_sync(0xffffffffu, le));
+        }
+        return c;
+    }
+};
+__device__ __forceinline__ int count_le(const int32_t *a, int n, int x) { return ThreadSearch().count_le(a, n, x); }
 
 // Patch that contains byte `pos`, clamped to [0, P-1].
-__device__ __forceinline__ int patch_of(const SeqMask &s, int pos) {
-    int p = count_le(s.pb, s.P + 1, pos) - 1;
+template <class Search = ThreadSearch>
+__device__ __forceinline__ int patch_of(const SeqMask &s, int pos, const Search &srch = Search()) {
+    int p = srch.count_le(s.pb, s.P + 1, pos) - 1;
     if (p < 0) p = 0;
     if (p > s.P - 1) p = s.P - 1;
     return p;
@@ -96,28 +115,32 @@ __device__ __forceinline__ int patch_of(const SeqMask &s, int pos) {
 
 // Decoder latent of byte `pos`: the rule of blt_patch_decoder_latent_at
 // (ops/patch_pool_cpu.c:114-131) over a boundary array.
-__device__ __forceinline__ int latent_at(const SeqMask &s, int pos) {
+template <class Search = ThreadSearch>
+__device__ __forceinline__ int latent_at(const SeqMask &s, int pos, const Search &srch = Search()) {
     if (pos < s.pb[0]) return 0;
     if (pos >= s.pb[s.P]) return s.P - 1;
-    const int p = count_le(s.pb, s.P + 1, pos) - 1;
+    const int p = srch.count_le(s.pb, s.P + 1, pos) - 1;
     const bool closes = (pos + 1 == s.pb[p + 1]) && (p + 1 < s.P);
     if (closes) return p;
     return p == 0 ? 0 : p - 1;
 }
 
 // Group (patch / latent) a query row belongs to under the PATCH_* rules.
-__device__ __forceinline__ int query_group(const SeqMask &s, int i) {
+template <class Search = ThreadSearch>
+__device__ __forceinline__ int query_group(const SeqMask &s, int i, const Search &srch = Search()) {
     if (s.group_rule == FBLT_GROUP_PATCH_ENC) return i / s.subtokens;
     if (s.group_rule == FBLT_GROUP_PATCH_DEC) {
         if (s.trailing_closed && i == s.nq - 1) return s.P - 1;
-        return latent_at(s, s.q_pos_off + i);
+        return latent_at(s, s.q_pos_off + i, srch);
     }
-    return patch_of(s, s.q_pos_off + i); // PATCH_LEQ
+    return patch_of(s, s.q_pos_off + i, srch); // PATCH_LEQ
 }
 
 // Contiguous key range [lo, hi) a query row may attend to. Valid for every
 // rule except explicit group ids, whose equality test stays per key.
-__device__ __forceinline__ void row_range(const SeqMask &s, int i, int &lo_out, int &hi_out) {
+template <class Search = ThreadSearch>
+__device__ __forceinline__ void row_range(const SeqMask &s, int i, int &lo_out, int &hi_out,
+                                          const Search &srch = Search()) {
     int lo = 0, hi = s.nk;
     if (s.num_clean >= 0) {
         if (i < s.num_clean) hi = min(hi, min(s.num_clean, i + 1));
@@ -130,7 +153,7 @@ __device__ __forceinline__ void row_range(const SeqMask &s, int i, int &lo_out, 
         }
     }
     if (s.ndoc > 0) {
-        const int d = count_le(s.doc, s.ndoc, i);
+        const int d = srch.count_le(s.doc, s.ndoc, i);
         if (d > 0) lo = max(lo, s.doc[d - 1]);
         if (d < s.ndoc) hi = min(hi, s.doc[d]);
     }
@@ -138,7 +161,7 @@ __device__ __forceinline__ void row_range(const SeqMask &s, int i, int &lo_out, 
         if (s.P <= 0) {
             hi = lo;
         } else {
-            const int g = query_group(s, i);
+            const int g = query_group(s, i, srch);
             if (s.group_rule == FBLT_GROUP_PATCH_ENC) {
                 if (g < s.P) {
                     lo = max(lo, s.pb[g]);

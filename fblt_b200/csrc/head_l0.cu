@@ -16,7 +16,7 @@ namespace fblt {
 
 constexpr int kL0Threads = 128;
 constexpr int kL0Warps = kL0Threads / 32;
-constexpr size_t kL0MaxSmemScores = 50 * 1024; // floats (200 KB)
+constexpr size_t kL0MaxSmem = 220 * 1024; // bytes of dynamic shared memory the kernel may ask for
 
 __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -118,9 +118,10 @@ static int launch_l0(const fblt_head_args *a, cudaStream_t stream) {
     if (a->head_dim == 0) return fail(FBLT_ERR_ARG, "head: head_dim must be > 0");
     if (a->nq == 0) return FBLT_OK;
     if (a->nq > 0x7fffffffu) return fail(FBLT_ERR_LIMIT, "head: nq too large");
+    if (a->head_dim > 8192) return fail(FBLT_ERR_LIMIT, "head: head_dim %zu > 8192", a->head_dim);
     const size_t hd_pad = (a->head_dim + 31) & ~(size_t)31;
     const size_t fixed = (hd_pad + 32 + kL0Warps * 32) * sizeof(float);
-    int in_smem = a->nk <= kL0MaxSmemScores;
+    int in_smem = fixed + a->nk * sizeof(float) <= kL0MaxSmem;
     float *gscores = nullptr;
     if (!in_smem) {
         gscores = a->weights_out ? a->weights_out : a->scores_scratch;
@@ -130,11 +131,8 @@ static int launch_l0(const fblt_head_args *a, cudaStream_t stream) {
     }
     const size_t smem = fixed + (in_smem ? a->nk * sizeof(float) : 0);
     if (smem > 48 * 1024) {
-        static thread_local size_t granted = 0;
-        if (smem > granted) {
-            FBLT_CUDA_TRY(cudaFuncSetAttribute(l0_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            granted = smem;
-        }
+        // raised to the largest size this kernel ever uses; cheap and safe to repeat (per device, any thread)
+        FBLT_CUDA_TRY(cudaFuncSetAttribute(l0_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kL0MaxSmem));
     }
     l0_head_kernel<<<(unsigned)a->nq, kL0Threads, smem, stream>>>(*a, gscores, in_smem);
     count_launch();

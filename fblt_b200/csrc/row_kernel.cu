@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
 
     const SeqMask s = resolve_mask(d.mask, b, q0, k0, nq, nk);
     int lo, hi;
-    row_range(s, i, lo, hi);
+    row_range(s, i, lo, hi, WarpSearch{lane}); // the whole warp works on row i
     const bool by_ids = s.group_rule == FBLT_GROUP_IDS;
     const int my_group = by_ids ? s.qg[i] : 0;
 
@@ -39,27 +39,63 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
     const float *kb = d.k + (int64_t)k0 * d.k_stride + (int64_t)h * hd;
     const float *vb = d.v + (int64_t)k0 * d.v_stride + (int64_t)h * hd;
 
-    for (int j = lo; j < hi; ++j) {
+    // Four keys per step: their K and V pieces are requested together, so a row with a short
+    // key range (a patch's bytes) pays one memory round trip, not one per key.
+    constexpr int G = 4;
+    const int grouped_end = (hi - lo >= G) ? hi : lo; // ranges shorter than a group use the tail loop only
+    for (int j0 = lo; j0 < grouped_end; j0 += G) {
+        float kk[G][NT], vv[G][NT];
+        bool take[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const int j = j0 + g;
+            const bool in_range = j < hi; // uniform over the warp
+            take[g] = in_range && !(by_ids && s.kg[in_range ? j : lo] != my_group);
+            const float *kj = kb + (int64_t)j * d.k_stride;
+            const float *vj = vb + (int64_t)j * d.v_stride;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const int dd = lane + 32 * t;
+                kk[g][t] = (in_range && dd < hd) ? kj[dd] : 0.0f;
+                vv[g][t] = (in_range && dd < hd) ? vj[dd] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            if (j0 + g >= hi) break; // past the end of the range (uniform over the warp)
+            float part = 0.0f;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) part += qv[t] * kk[g][t];
+            part = warp_sum(part);
+            if (!take[g] || !finite_f(part)) continue; // masked key, or non-finite score: weight 0
+            const float mn = fmaxf(m, part);
+            const float corr = exp2f(m - mn);
+            const float p = exp2f(part - mn);
+            l = l * corr + p;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) acc[t] = acc[t] * corr + p * vv[g][t];
+            m = mn;
+        }
+    }
+    for (int j = grouped_end; j < hi; ++j) { // one or a few keys (decoder cross-attention: a single latent)
         if (by_ids && s.kg[j] != my_group) continue;
         const float *kj = kb + (int64_t)j * d.k_stride;
-        float part = 0.0f;
+        const float *vj = vb + (int64_t)j * d.v_stride;
+        float part = 0.0f, vloc[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
             const int dd = lane + 32 * t;
-            if (dd < hd) part += qv[t] * kj[dd];
+            part += dd < hd ? qv[t] * kj[dd] : 0.0f;
+            vloc[t] = dd < hd ? vj[dd] : 0.0f;
         }
         part = warp_sum(part);
-        if (!finite_f(part)) continue; // non-finite score: weight 0
+        if (!finite_f(part)) continue;
         const float mn = fmaxf(m, part);
         const float corr = exp2f(m - mn);
         const float p = exp2f(part - mn);
         l = l * corr + p;
-        const float *vj = vb + (int64_t)j * d.v_stride;
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            const int dd = lane + 32 * t;
-            if (dd < hd) acc[t] = acc[t] * corr + p * vj[dd];
-        }
+        for (int t = 0; t < NT; ++t) acc[t] = acc[t] * corr + p * vloc[t];
         m = mn;
     }
 

@@ -24,6 +24,7 @@
 // error code, stops issuing work, frees its TMEM and returns.
 #include "common.cuh"
 
+#include <atomic>
 #include <limits.h>
 
 namespace fblt {
@@ -505,12 +506,13 @@ bool tile5_kernel_supports(const fblt_attn_desc &d, const char **why) {
 
 template <bool X3>
 static int launch_tile5_t(const fblt_attn_desc &d, cudaStream_t stream) {
-    static int configured_device = -1;
+    static std::atomic<uint64_t> configured{0}; // one bit per device ordinal; the attribute is per device
     int dev = 0;
     FBLT_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_device != dev) {
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
         FBLT_CUDA_TRY(cudaFuncSetAttribute(tile5_attn_kernel<X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kT5Smem));
-        configured_device = dev;
+        configured.fetch_or(bit, std::memory_order_release);
     }
     dim3 grid((d.max_q + kT5Rows - 1) / kT5Rows, d.num_heads, d.batch);
     tile5_attn_kernel<X3><<<grid, kT5Threads, kT5Smem, stream>>>(d);

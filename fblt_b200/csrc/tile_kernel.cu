@@ -18,6 +18,7 @@
 // inside every row's range skip the per-element range test.
 #include "common.cuh"
 
+#include <atomic>
 #include <limits.h>
 
 namespace fblt {
@@ -327,12 +328,13 @@ bool tile_kernel_supports(const fblt_attn_desc &d, const char **why) {
 template <int HD, bool X3, int STAGES>
 static int launch_tile_s(const fblt_attn_desc &d, cudaStream_t stream) {
     constexpr size_t smem = (size_t)(kBM + 2 * STAGES * kBN) * (HD + 4) * sizeof(float);
-    static int configured_device = -1; // per instantiation; the attribute is per device
+    static std::atomic<uint64_t> configured{0}; // one bit per device ordinal; the attribute is per device
     int dev = 0;
     FBLT_CUDA_TRY(cudaGetDevice(&dev));
-    if (configured_device != dev) {
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
         FBLT_CUDA_TRY(cudaFuncSetAttribute(tile_attn_kernel<HD, X3, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured_device = dev;
+        configured.fetch_or(bit, std::memory_order_release);
     }
     dim3 grid((d.max_q + kBM - 1) / kBM, d.num_heads, d.batch);
     tile_attn_kernel<HD, X3, STAGES><<<grid, kTileThreads, smem, stream>>>(d);
