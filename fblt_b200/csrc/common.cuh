@@ -223,6 +223,24 @@ __device__ __forceinline__ bool pair_allowed(const SeqMask &s, int i, int j) {
     return ok;
 }
 
+// ---- rotary embedding ------------------------------------------------------------
+// One (even, odd) pair: out0 = x0 c - x1 s, out1 = x1 c + x0 s (ops/reductions_cpu.c:217-228).
+// Products and sums are rounded separately, as the CPU code does, so rotated values match it.
+__device__ __forceinline__ void rope_rotate(float &x0, float &x1, float c, float s) {
+    const float a = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+    const float b = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+    x0 = a;
+    x1 = b;
+}
+// The two pairs of a 16-byte piece starting at even column 2 * pair0, for position `pos`.
+__device__ __forceinline__ float4 rope_rotate4(float4 x, const float *cs, const float *sn, int pos, int half, int pair0) {
+    const float2 c = __ldg(reinterpret_cast<const float2 *>(cs + (int64_t)pos * half + pair0));
+    const float2 s = __ldg(reinterpret_cast<const float2 *>(sn + (int64_t)pos * half + pair0));
+    rope_rotate(x.x, x.y, c.x, s.x);
+    rope_rotate(x.z, x.w, c.y, s.y);
+    return x;
+}
+
 // ---- small device helpers ---------------------------------------------------
 
 __device__ __forceinline__ bool finite_f(float x) { return fabsf(x) < INFINITY; }

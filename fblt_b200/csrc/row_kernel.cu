@@ -10,7 +10,24 @@ namespace fblt {
 
 constexpr int kRowWarps = 4;
 
+// Rotary embedding when a lane holds columns lane + 32 t: the partner of an (even, odd) pair
+// sits in the neighbouring lane.
 template <int NT>
+__device__ __forceinline__ void rope_lanes(float (&x)[NT], const float *cs, const float *sn, int pos, int hd, int lane) {
+    const int half = hd >> 1;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        const int dd = lane + 32 * t;
+        const float other = __shfl_xor_sync(0xffffffffu, x[t], 1);
+        if (dd < hd) {
+            const float c = cs[(int64_t)pos * half + (dd >> 1)], s = sn[(int64_t)pos * half + (dd >> 1)];
+            x[t] = (lane & 1) ? __fadd_rn(__fmul_rn(x[t], c), __fmul_rn(other, s))
+                              : __fsub_rn(__fmul_rn(x[t], c), __fmul_rn(other, s));
+        }
+    }
+}
+
+template <int NT, bool ROPE>
 __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc d) {
     const int b = blockIdx.z, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -32,9 +49,13 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
         const int dd = lane + 32 * t;
-        qv[t] = dd < hd ? qrow[dd] * qscale : 0.0f;
+        qv[t] = dd < hd ? qrow[dd] : 0.0f;
         acc[t] = 0.0f;
     }
+    constexpr bool rope = ROPE; // a separate instantiation: the plain kernel keeps its register count
+    if constexpr (rope) rope_lanes<NT>(qv, d.rope_cos, d.rope_sin, i + s.causal_off, hd, lane);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) qv[t] *= qscale;
     float m = -INFINITY, l = 0.0f;
     const float *kb = d.k + (int64_t)k0 * d.k_stride + (int64_t)h * hd;
     const float *vb = d.v + (int64_t)k0 * d.v_stride + (int64_t)h * hd;
@@ -59,6 +80,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
                 kk[g][t] = (in_range && dd < hd) ? kj[dd] : 0.0f;
                 vv[g][t] = (in_range && dd < hd) ? vj[dd] : 0.0f;
             }
+            if constexpr (rope) rope_lanes<NT>(kk[g], d.rope_cos, d.rope_sin, in_range ? j : 0, hd, lane);
         }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
@@ -81,13 +103,16 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
         if (by_ids && s.kg[j] != my_group) continue;
         const float *kj = kb + (int64_t)j * d.k_stride;
         const float *vj = vb + (int64_t)j * d.v_stride;
-        float part = 0.0f, vloc[NT];
+        float part = 0.0f, vloc[NT], kloc[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
             const int dd = lane + 32 * t;
-            part += dd < hd ? qv[t] * kj[dd] : 0.0f;
+            kloc[t] = dd < hd ? kj[dd] : 0.0f;
             vloc[t] = dd < hd ? vj[dd] : 0.0f;
         }
+        if constexpr (rope) rope_lanes<NT>(kloc, d.rope_cos, d.rope_sin, j, hd, lane);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) part += qv[t] * kloc[t];
         part = warp_sum(part);
         if (!finite_f(part)) continue;
         const float mn = fmaxf(m, part);
@@ -113,10 +138,16 @@ int launch_row_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
     if (d.num_heads > 65535 || d.batch > 65535) return fail(FBLT_ERR_LIMIT, "row kernel: batch/heads exceed 65535");
     dim3 grid((d.max_q + kRowWarps - 1) / kRowWarps, d.num_heads, d.batch);
     const int nt = (d.head_dim + 31) / 32;
-    if (nt <= 1) row_attn_kernel<1><<<grid, kRowWarps * 32, 0, stream>>>(d);
-    else if (nt <= 2) row_attn_kernel<2><<<grid, kRowWarps * 32, 0, stream>>>(d);
-    else if (nt <= 4) row_attn_kernel<4><<<grid, kRowWarps * 32, 0, stream>>>(d);
-    else row_attn_kernel<8><<<grid, kRowWarps * 32, 0, stream>>>(d);
+#define FBLT_ROW_LAUNCH(NT_)                                                                  \
+    do {                                                                                      \
+        if (d.rope_cos) row_attn_kernel<NT_, true><<<grid, kRowWarps * 32, 0, stream>>>(d);   \
+        else row_attn_kernel<NT_, false><<<grid, kRowWarps * 32, 0, stream>>>(d);             \
+    } while (0)
+    if (nt <= 1) FBLT_ROW_LAUNCH(1);
+    else if (nt <= 2) FBLT_ROW_LAUNCH(2);
+    else if (nt <= 4) FBLT_ROW_LAUNCH(4);
+    else FBLT_ROW_LAUNCH(8);
+#undef FBLT_ROW_LAUNCH
     count_launch();
     return check_launch("row_attn_kernel");
 }

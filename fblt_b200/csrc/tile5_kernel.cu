@@ -232,7 +232,10 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 const int r = (bid & 7) * 8 + (lane & 7), c = (bid >> 3) * 4 + (lane >> 3);
                 const int j = kt * kT5Keys + r;
                 kr[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (j < nk) kr[it] = __ldg(reinterpret_cast<const float4 *>(kbase + (int64_t)j * d.k_stride + c * 4));
+                if (j < nk) {
+                    kr[it] = __ldg(reinterpret_cast<const float4 *>(kbase + (int64_t)j * d.k_stride + c * 4));
+                    if (d.rope_cos) kr[it] = rope_rotate4(kr[it], d.rope_cos, d.rope_sin, j, kT5HD / 2, c * 2);
+                }
             }
             {   // V: 16 keys x 2 pieces per warp step
                 const int r = (bid & 3) * 16 + v_rl, c = (bid >> 2) * 2 + v_cl;
@@ -300,7 +303,12 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i < nq) v = __ldg(reinterpret_cast<const float4 *>(qrow + half * 32 + c * 4));
+                if (i < nq) {
+                    v = __ldg(reinterpret_cast<const float4 *>(qrow + half * 32 + c * 4));
+                    if (d.rope_cos)
+                        v = rope_rotate4(v, d.rope_cos, d.rope_sin, i + (d.mask.causal_offset ? d.mask.causal_offset[b] : 0),
+                                         kT5HD / 2, half * 16 + c * 2);
+                }
                 const float e[4] = {v.x * qscale, v.y * qscale, v.z * qscale, v.w * qscale};
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {

@@ -164,6 +164,27 @@ __global__ void __launch_bounds__(kTileThreads, STAGES == 1 ? 4 : 2) tile_attn_k
         __syncthreads();
 
         const int j0 = kt * kBN;
+        if (d.rope_cos) { // rotate the freshly landed K tile (and, once, the Q tile) in shared memory
+            float *rK = sK + stage * kBN * LDS;
+            for (int c = tid; c < kBN * CPR; c += kTileThreads) {
+                const int r = c / CPR, cc = c - r * CPR;
+                if (j0 + r < nk) {
+                    float4 *p4 = reinterpret_cast<float4 *>(rK + r * LDS + cc * 4);
+                    *p4 = rope_rotate4(*p4, d.rope_cos, d.rope_sin, j0 + r, HD / 2, cc * 2);
+                }
+            }
+            if (kt == kt_begin) {
+                const int off = d.mask.causal_offset ? d.mask.causal_offset[b] : 0;
+                for (int c = tid; c < kBM * CPR; c += kTileThreads) {
+                    const int r = c / CPR, cc = c - r * CPR;
+                    if (qt * kBM + r < nq) {
+                        float4 *p4 = reinterpret_cast<float4 *>(sQ + r * LDS + cc * 4);
+                        *p4 = rope_rotate4(*p4, d.rope_cos, d.rope_sin, qt * kBM + r + off, HD / 2, cc * 2);
+                    }
+                }
+            }
+            __syncthreads();
+        }
         if (whi > j0 && wlo < j0 + kBN) {
             const float *tK = sK + stage * kBN * LDS;
             const float *tV = sV + stage * kBN * LDS;

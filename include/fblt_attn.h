@@ -248,6 +248,14 @@ typedef struct {
     float scale;
     int32_t reserved2;
     fblt_mask_desc mask;
+    /* Optional fused rotary embedding for self-attention prefill (replaces the 2 x heads
+     * blt_rope_apply_packed launches of models/attention.c:73-89): device tables
+     * [positions, head_dim/2] as blt_rope_precompute fills them. When given, q and k hold the
+     * un-rotated QKV projection; query row i is rotated with position i + causal_offset[b]
+     * and key row j with position j (interleaved pairs, ops/reductions_cpu.c:217-228)
+     * as they are loaded. NULL: q / k arrive rotated. head_dim must be even. */
+    const float *rope_cos;
+    const float *rope_sin;
 } fblt_attn_desc;
 
 int fblt_attn_forward(const fblt_attn_desc *desc, void *stream);

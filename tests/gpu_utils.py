@@ -20,11 +20,16 @@ def upload_case(case: ForwardCase):
             torch.from_numpy(np.ascontiguousarray(case.v)).cuda())
 
 
-def forward_gpu(case: ForwardCase, impl: int = L.IMPL_AUTO, precision: int = L.PREC_FP32, fill: float = float("nan")):
+def forward_gpu(case: ForwardCase, impl: int = L.IMPL_AUTO, precision: int = L.PREC_FP32, fill: float = float("nan"),
+                rope=None):
+    """rope: optional (cos, sin) numpy tables [positions, head_dim/2]; the kernels then rotate Q and K."""
     q, k, v = upload_case(case)
+    rope_kw = {}
+    if rope is not None:
+        rope_kw = dict(rope_cos=torch.from_numpy(rope[0]).cuda(), rope_sin=torch.from_numpy(rope[1]).cuda())
     out = torch.full((int(case.cu_q[-1]), case.embed), fill, dtype=torch.float32, device="cuda")
     batch = ops.make_batch(q, k, v, out, case.cu_q, case.cu_k, case.num_heads, case.head_dim, case.scale, case.mask,
-                           impl=impl, precision=precision)
+                           impl=impl, precision=precision, **rope_kw)
     ops.attn_forward(batch)
     torch.cuda.synchronize()
     return out.cpu().numpy(), batch

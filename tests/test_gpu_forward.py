@@ -9,6 +9,9 @@ from fblt_b200 import ops, synth, workloads
 from fblt_b200.ops import MaskConfig
 from fblt_b200.workloads import ForwardCase
 from gpu_utils import forward_gpu
+import dataclasses
+
+import oracle.binding as ob
 from helpers import assert_close, oracle_forward
 
 pytestmark = pytest.mark.gpu
@@ -167,3 +170,42 @@ def test_long_sequences_many_key_tiles(cuda_lib):
     # rectangular: 300 queries over 700 keys with a causal offset
     cu_q, cu_k = np.array([0, 300]), np.array([0, 700])
     check(random_case(73, cu_q, cu_k, 2, 64, MaskConfig(is_causal=True, causal_offset=[400])))
+
+
+@pytest.mark.parametrize("hd", [32, 64, 128])
+def test_fused_rotary_embedding(cuda_lib, hd):
+    """Unrotated Q/K plus the cos/sin tables: the kernels rotate query row i with position
+    i + causal_offset and key row j with position j (the order of models/attention.c:
+    rope_apply on Q and K, then the head operator). The oracle rotates on the CPU first."""
+    H = 2
+    lens_k = [200, 65, 1, 0, 130]
+    lens_q = [200, 65, 1, 0, 30]               # last sequence: queries are the tail of the keys
+    off = [0, 0, 0, 0, 100]
+    cu_q = np.concatenate([[0], np.cumsum(lens_q)])
+    cu_k = np.concatenate([[0], np.cumsum(lens_k)])
+    cs, sn = ob.rope_tables(256, hd)
+    for mask in (MaskConfig(is_causal=True, causal_offset=off),
+                 MaskConfig(is_causal=True, sliding_window=48, causal_offset=off)):
+        raw = random_case(70 + hd, cu_q, cu_k, H, hd, mask)
+        pos_q = np.concatenate([np.arange(n) + o for n, o in zip(lens_q, off)]).astype(np.int64)
+        pos_k = np.concatenate([np.arange(n) for n in lens_k]).astype(np.int64)
+        rotated = dataclasses.replace(raw, q=ob.rope_apply(raw.q, cs[pos_q], sn[pos_q], H, hd),
+                                      k=ob.rope_apply(raw.k, cs[pos_k], sn[pos_k], H, hd))
+        want, _, _ = oracle_forward(rotated)
+        kernels = KERNELS + (T5_KERNELS if hd == 64 else [])
+        for impl, prec in kernels:
+            got, _ = forward_gpu(raw, impl, prec, rope=(cs, sn))
+            tol = dict(atol=TF32_ATOL, rtol=TF32_RTOL) if prec == L.PREC_TF32 else {}
+            assert_close(got, want, f"rope hd={hd} impl={impl} prec={prec}", **tol)
+
+
+def test_rotary_tables_are_validated(cuda_lib):
+    cs, sn = ob.rope_tables(64, 32)
+    case = random_case(90, [0, 8], [0, 8], 1, 32, MaskConfig(is_causal=True))
+    q, k, v = (torch.from_numpy(x).cuda() for x in (case.q, case.k, case.v))
+    out = torch.empty_like(q)
+    batch = ops.make_batch(q, k, v, out, case.cu_q, case.cu_k, 1, 32, case.scale, case.mask,
+                           rope_cos=torch.from_numpy(cs).cuda(), rope_sin=torch.from_numpy(sn).cuda())
+    batch.desc.rope_sin = None                  # one table without the other
+    with pytest.raises(L.FbltError):
+        ops.attn_forward(batch)
