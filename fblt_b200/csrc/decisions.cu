@@ -7,12 +7,7 @@ namespace fblt {
 // Strict-'>' scan from index 0 (infer/self_speculation.c:21-31): the lowest
 // index among equal maxima wins; a NaN never wins a comparison, and a NaN in
 // slot 0 makes every later comparison false, so slot 0 is returned.
-__global__ void __launch_bounds__(128) argmax_rows_kernel(const float *logits, int64_t stride, int rows, int vocab,
-                                                          int32_t *ids) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 4 + warp;
-    if (row >= rows) return;
-    const float *x = logits + (int64_t)row * stride;
+__device__ __forceinline__ int warp_argmax_row(const float *x, int vocab, int lane) {
     const float first = x[0];
     float best = -INFINITY;
     int arg = 0x7fffffff;
@@ -33,7 +28,16 @@ __global__ void __launch_bounds__(128) argmax_rows_kernel(const float *logits, i
             arg = oa;
         }
     }
-    if (lane == 0) ids[row] = (first != first) ? 0 : arg;
+    return (first != first) ? 0 : arg; // same value in every lane
+}
+
+__global__ void __launch_bounds__(128) argmax_rows_kernel(const float *logits, int64_t stride, int rows, int vocab,
+                                                          int32_t *ids) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 4 + warp;
+    if (row >= rows) return;
+    const int arg = warp_argmax_row(logits + (int64_t)row * stride, vocab, lane);
+    if (lane == 0) ids[row] = arg;
 }
 
 // Algorithm 2 accept loop (infer/self_speculation.c:158-182), one thread per
@@ -64,6 +68,104 @@ __global__ void verify_accept_kernel(uint8_t *x, int64_t x_stride, const int32_t
     }
 }
 
+// Cell selection of one unmask round (infer/block_generation.c:20-58); the same code runs
+// on the host (the fblt_unmask_select_* entry points) and in unmask_step_kernel.
+__host__ __device__ inline uint32_t select_confidence(const float *scores, const uint8_t *masked, size_t B, float alpha) {
+    uint32_t picked = 0;
+    long lead = -1;
+    for (size_t b = 0; b < B; ++b) {
+        if (!masked[b]) continue;
+        if (lead < 0 || scores[b] > scores[lead]) lead = (long)b;
+        if (scores[b] >= alpha) picked |= 1u << b;
+    }
+    if (!picked && lead >= 0) picked = 1u << lead; // always make progress
+    return picked;
+}
+
+__host__ __device__ inline uint32_t select_eb(const float *scores, const uint8_t *masked, size_t B, float gamma) {
+    size_t rank[32];
+    size_t n = 0;
+    for (size_t b = 0; b < B && b < 32; ++b) { // ascending entropy, stable
+        if (!masked[b]) continue;
+        size_t slot = n++;
+        for (; slot > 0 && scores[rank[slot - 1]] > scores[b]; --slot) rank[slot] = rank[slot - 1];
+        rank[slot] = b;
+    }
+    if (!n) return 0;
+    uint32_t picked = 0;
+    float budget_used = 0.0f;
+    for (size_t t = 0; t < n; ++t) {
+        if (t > 0 && !(budget_used + scores[rank[t]] <= gamma)) break;
+        budget_used += scores[rank[t]];
+        picked |= 1u << rank[t];
+    }
+    return picked;
+}
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// One unmask round of blt_draft_block for a batch of candidates (infer/block_generation.c:
+// 225-252): a CTA per candidate; a warp per cell computes the softmax statistics of its
+// logits row the way row_analyze does (:65-80 -- maximum probability and entropy in nats,
+// accumulated in double) and the greedy byte (:82-92); one thread then runs the selection
+// and writes the chosen cells' bytes.
+constexpr int kUnmaskWarps = 8;
+__global__ void __launch_bounds__(kUnmaskWarps * 32)
+    unmask_step_kernel(const float *logits, int64_t stride, int B, int vocab, int strategy, float threshold,
+                       uint8_t *masked, uint8_t *tokens, uint32_t *sel_out, float *conf_out, float *ent_out,
+                       int32_t *remaining_out) {
+    __shared__ float conf[32], ent[32];
+    __shared__ int pred[32];
+    const int c = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t *mk = masked + (int64_t)c * B;
+    for (int b = warp; b < B; b += kUnmaskWarps) {
+        const float *row = logits + ((int64_t)c * B + b) * stride;
+        float mx = -INFINITY; // row[0] then strict '>' == maximum over the row
+        for (int v = lane; v < vocab; v += 32) mx = fmaxf(mx, row[v]);
+        mx = warp_max(mx);
+        double sum = 0.0;
+        for (int v = lane; v < vocab; v += 32) sum += exp((double)row[v] - (double)mx);
+        sum = warp_sum_d(sum);
+        double pmax = 0.0, H = 0.0;
+        for (int v = lane; v < vocab; v += 32) {
+            const double p = exp((double)row[v] - (double)mx) / sum;
+            if (p > pmax) pmax = p;
+            if (p > 1e-12) H -= p * log(p);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) pmax = fmax(pmax, __shfl_xor_sync(0xffffffffu, pmax, o));
+        H = warp_sum_d(H);
+        const int arg = warp_argmax_row(row, vocab, lane);
+        if (lane == 0) {
+            conf[b] = (float)pmax;
+            ent[b] = (float)H;
+            pred[b] = arg;
+            if (conf_out) conf_out[(int64_t)c * B + b] = (float)pmax;
+            if (ent_out) ent_out[(int64_t)c * B + b] = (float)H;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t sel = strategy == FBLT_UNMASK_CONFIDENCE ? select_confidence(conf, mk, (size_t)B, threshold)
+                                                                : select_eb(ent, mk, (size_t)B, threshold);
+        int left = 0;
+        for (int b = 0; b < B; ++b) {
+            if (sel & (1u << b)) {
+                tokens[(int64_t)c * B + b] = (uint8_t)pred[b];
+                mk[b] = 0;
+            }
+            left += mk[b] ? 1 : 0;
+        }
+        if (sel_out) sel_out[c] = sel;
+        if (remaining_out) remaining_out[c] = left;
+    }
+}
+
 } // namespace fblt
 
 extern "C" int fblt_argmax_rows(const float *logits, int64_t stride, int32_t rows, int32_t vocab, int32_t *ids_out,
@@ -88,38 +190,40 @@ extern "C" int fblt_verify_accept(uint8_t *x, int64_t x_stride, const int32_t *p
     return check_launch("verify_accept_kernel");
 }
 
+extern "C" int fblt_unmask_step(const float *logits, int64_t stride, int32_t batch, int32_t B, int32_t vocab,
+                                int32_t strategy, float threshold, uint8_t *masked, uint8_t *tokens,
+                                uint32_t *sel_out, float *conf_out, float *ent_out, int32_t *remaining_out,
+                                void *stream) {
+    using namespace fblt;
+    if (!logits || !masked || !tokens || batch < 0 || vocab < 1 || stride < vocab)
+        return fail(FBLT_ERR_ARG, "unmask_step: bad arguments");
+    if (B < 1 || B > 32) return fail(FBLT_ERR_LIMIT, "unmask_step: block size %d outside 1..32", B);
+    if (strategy != FBLT_UNMASK_CONFIDENCE && strategy != FBLT_UNMASK_ENTROPY_BOUNDED)
+        return fail(FBLT_ERR_ARG, "unmask_step: unknown strategy %d", strategy);
+    if (batch == 0) return FBLT_OK;
+    unmask_step_kernel<<<batch, kUnmaskWarps * 32, 0, (cudaStream_t)stream>>>(
+        logits, stride, B, vocab, strategy, threshold, masked, tokens, sel_out, conf_out, ent_out, remaining_out);
+    count_launch();
+    return check_launch("unmask_step_kernel");
+}
+
+extern "C" size_t fblt_kv_common_patches(const fblt_patch_info *cached, size_t num_cached,
+                                         const fblt_patch_info *patches, size_t num_patches) {
+    size_t same = 0;
+    while (same < num_cached && same < num_patches && cached[same].start_idx == patches[same].start_idx &&
+           cached[same].length == patches[same].length)
+        ++same;
+    return same;
+}
+
 // ---- host mirrors of the selection helpers --------------------------------------
 
 extern "C" uint32_t fblt_unmask_select_confidence(const float *scores, const uint8_t *masked, size_t B, float alpha) {
-    uint32_t picked = 0;
-    long lead = -1;
-    for (size_t b = 0; b < B; ++b) {
-        if (!masked[b]) continue;
-        if (lead < 0 || scores[b] > scores[lead]) lead = (long)b;
-        if (scores[b] >= alpha) picked |= 1u << b;
-    }
-    if (!picked && lead >= 0) picked = 1u << lead; // always make progress
-    return picked;
+    return fblt::select_confidence(scores, masked, B, alpha);
 }
 
 extern "C" uint32_t fblt_unmask_select_eb(const float *scores, const uint8_t *masked, size_t B, float gamma) {
-    size_t rank[32];
-    size_t n = 0;
-    for (size_t b = 0; b < B && b < 32; ++b) { // ascending entropy, stable
-        if (!masked[b]) continue;
-        size_t slot = n++;
-        for (; slot > 0 && scores[rank[slot - 1]] > scores[b]; --slot) rank[slot] = rank[slot - 1];
-        rank[slot] = b;
-    }
-    if (!n) return 0;
-    uint32_t picked = 0;
-    float budget_used = 0.0f;
-    for (size_t t = 0; t < n; ++t) {
-        if (t > 0 && !(budget_used + scores[rank[t]] <= gamma)) break;
-        budget_used += scores[rank[t]];
-        picked |= 1u << rank[t];
-    }
-    return picked;
+    return fblt::select_eb(scores, masked, B, gamma);
 }
 
 extern "C" size_t fblt_aligned_commit_select(const fblt_patch_info *patches, size_t num_patches, size_t lo, size_t hi) {

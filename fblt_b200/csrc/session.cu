@@ -375,6 +375,25 @@ extern "C" int fblt_session_decode_steps(fblt_session *s, int32_t batch, int32_t
     return FBLT_OK;
 }
 
+extern "C" int fblt_session_cache_truncate(fblt_session *s, int32_t batch, const int32_t *lens) {
+    using namespace fblt;
+    if (!s || !lens || batch < 0 || batch > s->max_batch) return fail(FBLT_ERR_ARG, "cache_truncate: bad arguments");
+    if (!s->kc) return fail(FBLT_ERR_ARG, "cache_truncate: session has no cache");
+    for (int b = 0; b < batch; ++b)
+        if (lens[b] < 0 || lens[b] > s->cache_rows)
+            return fail(FBLT_ERR_CAPACITY, "cache_truncate: length %d of sequence %d outside [0, %d]", lens[b], b, s->cache_rows);
+    // earlier steps have completed (every session call returns with its stream idle)
+    for (int b = 0; b < batch; ++b) s->h_lens[b] = lens[b];
+    return FBLT_OK;
+}
+
+extern "C" int fblt_session_cache_reset(fblt_session *s) {
+    using namespace fblt;
+    if (!s) return fail(FBLT_ERR_ARG, "cache_reset: NULL session");
+    memset(s->h_lens, 0, (size_t)s->max_batch * sizeof(int32_t));
+    return FBLT_OK;
+}
+
 extern "C" int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch) {
     using namespace fblt;
     if (!s || !lens_out || batch < 0 || batch > s->max_batch) return fail(FBLT_ERR_ARG, "cache_lens: bad arguments");

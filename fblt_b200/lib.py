@@ -107,6 +107,9 @@ SYMBOLS = {
     "fblt_unmask_select_eb": (C.c_uint32, [c_float_p, c_u8_p, C.c_size_t, C.c_float]),
     "fblt_aligned_commit_select": (C.c_size_t, [C.POINTER(PatchInfo), C.c_size_t, C.c_size_t, C.c_size_t]),
     "fblt_block_adapt_b": (C.c_size_t, [C.c_size_t, C.c_double, C.c_size_t, C.c_size_t, C.c_float]),
+    "fblt_unmask_step": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
+                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "fblt_kv_common_patches": (C.c_size_t, [C.POINTER(PatchInfo), C.c_size_t, C.POINTER(PatchInfo), C.c_size_t]),
     "fblt_session_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int32, C.c_int32]),
     "fblt_session_destroy": (None, [C.c_void_p]),
@@ -117,11 +120,15 @@ SYMBOLS = {
     "fblt_session_decode_steps": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                             C.c_int32]),
+    "fblt_session_cache_truncate": (C.c_int, [C.c_void_p, C.c_int32, c_i32_p]),
+    "fblt_session_cache_reset": (C.c_int, [C.c_void_p]),
     "fblt_session_cache_lens": (C.c_int, [C.c_void_p, c_i32_p, C.c_int32]),
     "fblt_tcgen05_error": (C.c_int, []),
     "fblt_launch_count": (C.c_uint64, []),
     "fblt_abi_sizes": (C.c_size_t, [C.POINTER(C.c_size_t), C.c_size_t]),
 }
+
+UNMASK_CONFIDENCE, UNMASK_ENTROPY_BOUNDED = 0, 1
 
 _lib = None
 

@@ -267,6 +267,22 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     return ids
 
 
+def unmask_step(logits: torch.Tensor, masked: torch.Tensor, tokens: torch.Tensor, strategy: int, threshold: float):
+    """One unmask round over a batch of candidates. logits [batch*B, V] float32, masked/tokens
+    [batch, B] uint8 (updated in place). Returns (sel [batch] int64 bit masks, conf [batch,B],
+    ent [batch,B], remaining [batch])."""
+    batch, B = masked.shape
+    dev = logits.device
+    sel = torch.empty(batch, dtype=torch.int32, device=dev)          # same bits as the uint32 the kernel writes
+    conf = torch.empty(batch, B, dtype=torch.float32, device=dev)
+    ent = torch.empty(batch, B, dtype=torch.float32, device=dev)
+    left = torch.empty(batch, dtype=torch.int32, device=dev)
+    L.check(L.load().fblt_unmask_step(logits.data_ptr(), logits.stride(0), batch, B, logits.shape[1], strategy,
+                                      float(threshold), masked.data_ptr(), tokens.data_ptr(), sel.data_ptr(),
+                                      conf.data_ptr(), ent.data_ptr(), left.data_ptr(), _stream_ptr(None)))
+    return sel.to(torch.int64) & 0xFFFFFFFF, conf, ent, left
+
+
 def verify_accept(x: torch.Tensor, pred: torch.Tensor, l: torch.Tensor, r: torch.Tensor, target_len: torch.Tensor):
     """In-place accept-until-mismatch over a batch of candidates; returns (new_len, accepted)."""
     batch = x.shape[0]
@@ -348,6 +364,13 @@ class Session:
         L.check(self._lib.fblt_session_decode_steps(self._h, batch, n_new, steps, int(block_mode), window, float(scale),
                                                     _ptr(q_new), _ptr(k_new), _ptr(v_new), in_step_stride, _ptr(out),
                                                     out_step_stride, n_new if advance is None else advance))
+
+    def cache_truncate(self, lens) -> None:
+        lens_h = np.ascontiguousarray(np.asarray(lens, dtype=np.int32))
+        L.check(self._lib.fblt_session_cache_truncate(self._h, len(lens_h), lens_h.ctypes.data_as(L.c_i32_p)))
+
+    def cache_reset(self) -> None:
+        L.check(self._lib.fblt_session_cache_reset(self._h))
 
     def cache_lens(self, batch: int) -> np.ndarray:
         out = np.zeros(batch, dtype=np.int32)

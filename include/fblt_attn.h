@@ -408,6 +408,32 @@ uint32_t fblt_unmask_select_eb(const float *scores, const uint8_t *masked, size_
 size_t fblt_aligned_commit_select(const fblt_patch_info *patches, size_t num_patches, size_t lo, size_t hi);
 size_t fblt_block_adapt_b(size_t cur_b, double rolling_acceptance, size_t b_min, size_t b_max, float target);
 
+/*
+ * One unmask round of the block-diffusion drafter for a batch of candidates,
+ * on the device: replaces the full-logit download, row_analyze / row_argmax
+ * host loops and the selection call of infer/block_generation.c:225-252.
+ * logits is [batch * B, stride] (row c * B + b = cell b of candidate c, the
+ * block rows only); masked and tokens are [batch, B] bytes, updated in
+ * place: every selected cell gets tokens = argmax byte, masked = 0.
+ * Per cell p_max and entropy (nats) of softmax(row) are accumulated in double
+ * like the reference; strategy FBLT_UNMASK_CONFIDENCE selects masked cells
+ * with p_max >= threshold (else the most confident one), ENTROPY_BOUNDED the
+ * largest ascending-entropy prefix whose sum stays <= threshold. Optional
+ * outputs: sel_out [batch] bit b = cell b chosen, conf_out / ent_out
+ * [batch, B], remaining_out [batch] = cells still masked. 1 <= B <= 32.
+ * All pointers device.
+ */
+enum { FBLT_UNMASK_CONFIDENCE = 0, FBLT_UNMASK_ENTROPY_BOUNDED = 1 }; /* blt_unmask_strategy, block_generation.h:37-41 */
+int fblt_unmask_step(const float *logits, int64_t stride, int32_t batch, int32_t B, int32_t vocab, int32_t strategy,
+                     float threshold, uint8_t *masked, uint8_t *tokens, uint32_t *sel_out, float *conf_out,
+                     float *ent_out, int32_t *remaining_out, void *stream);
+
+/* Leading patches identical (start and length) in a cached boundary snapshot and a new
+ * segmentation: blt_kv_cache_common_patches (infer/kv_cache.c:101-109) over plain arrays.
+ * Host arrays. */
+size_t fblt_kv_common_patches(const fblt_patch_info *cached, size_t num_cached, const fblt_patch_info *patches,
+                              size_t num_patches);
+
 /* ------------------------------------------------------------------------ */
 /* host-buffer sessions (what a host-side caller with no device memory uses) */
 /* ------------------------------------------------------------------------ */
@@ -461,6 +487,12 @@ int fblt_session_decode_steps(fblt_session *s, int32_t batch, int32_t n_new, int
                               int32_t window, float scale, const float *q_new, const float *k_new,
                               const float *v_new, int64_t in_step_stride, float *out, int64_t out_step_stride,
                               int32_t advance);
+/* Per-sequence blt_kv_cache_truncate (infer/kv_cache.c:94-99): sets the valid length of
+ * every sequence's cache tier to lens[b] (<= cache_rows; shrinking rolls back, growing
+ * covers rows the caller has just written). No data is cleared. */
+int fblt_session_cache_truncate(fblt_session *s, int32_t batch, const int32_t *lens);
+/* blt_kv_cache_reset (infer/kv_cache.c:89-92): all lengths to 0. */
+int fblt_session_cache_reset(fblt_session *s);
 /* Current cache lengths (host copy), for checks. */
 int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch);
 

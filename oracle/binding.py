@@ -97,6 +97,8 @@ def ref() -> C.CDLL:
         lib.ref_block_adapt_b.argtypes = [C.c_size_t, C.c_double, C.c_size_t, C.c_size_t, C.c_float]
         lib.ref_aligned_commit_select.restype = C.c_size_t
         lib.ref_aligned_commit_select.argtypes = [C.POINTER(PatchInfo), C.c_size_t, C.c_size_t, C.c_size_t]
+        lib.ref_kv_common_patches.restype = C.c_size_t
+        lib.ref_kv_common_patches.argtypes = [C.POINTER(PatchInfo), C.c_size_t, C.POINTER(PatchInfo), C.c_size_t]
         lib.ref_struct_layout.restype = C.c_size_t
         lib.ref_struct_layout.argtypes = [c_sz_p, C.c_size_t]
         _ref = lib

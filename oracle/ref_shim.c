@@ -21,6 +21,7 @@
 #include "core/allocator.h"
 #include "core/backend.h"
 #include "infer/block_generation.h"
+#include "infer/kv_cache.h"
 #include "infer/self_speculation.h"
 #include "models/patcher.h"
 #include "ops/attn_core.h"
@@ -149,6 +150,16 @@ size_t ref_block_adapt_b(size_t cur, double acc, size_t lo, size_t hi, float tar
 }
 size_t ref_aligned_commit_select(const blt_patch_info *p, size_t n, size_t lo, size_t hi) {
     return blt_aligned_commit_select(p, n, lo, hi);
+}
+
+/* blt_kv_cache_common_patches reads only the boundary snapshot and its count. */
+size_t ref_kv_common_patches(const blt_patch_info *cached, size_t num_cached, const blt_patch_info *patches,
+                             size_t num_patches) {
+    blt_kv_cache cache;
+    memset(&cache, 0, sizeof(cache));
+    cache.cached_patches = (blt_patch_info *)cached;
+    cache.cross_num_patches = num_cached;
+    return blt_kv_cache_common_patches(&cache, patches, num_patches);
 }
 
 void ref_rope_precompute(size_t max_seq_len, float theta, size_t head_dim, float *cos_out, float *sin_out) {

@@ -98,6 +98,28 @@ def test_selection_helpers_match_oracle():
                 assert lib.fblt_block_adapt_b(cur, acc, lo, hi, 0.5) == o.oracle_block_adapt_b(cur, acc, lo, hi, 0.5)
 
 
+def test_common_patches_matches_reference_or_definition():
+    """Leading patches equal in start and length (infer/kv_cache.c:101-109)."""
+    lib = L.load()
+    rng = np.random.default_rng(11)
+    for _ in range(200):
+        cuts_a = np.unique(np.concatenate([[0], rng.integers(1, 64, size=int(rng.integers(0, 12))), [64]]))
+        cuts_b = cuts_a.copy()
+        if rng.random() < 0.8 and len(cuts_b) > 2:                      # perturb one interior boundary
+            k = int(rng.integers(1, len(cuts_b) - 1))
+            cuts_b = np.unique(np.concatenate([cuts_b[:k], [min(int(cuts_b[k]) + 1, 63)], cuts_b[k + 1:]]))
+        a, na = ob.patch_array(cuts_a.tolist())
+        b, nb = ob.patch_array(cuts_b.tolist())
+        ncached = int(rng.integers(0, na + 1))
+        want = 0
+        while (want < ncached and want < nb and a[want].start_idx == b[want].start_idx
+               and a[want].length == b[want].length):
+            want += 1
+        assert lib.fblt_kv_common_patches(a, ncached, b, nb) == want
+        if ob.have_ref():
+            assert ob.ref().ref_kv_common_patches(a, ncached, b, nb) == want
+
+
 def test_synth_is_deterministic_and_sliceable():
     a = synth.normal(5, synth.TAG_Q, 1000)
     b = synth.normal(5, synth.TAG_Q, 400, start=333)

@@ -90,3 +90,57 @@ def test_argmax_over_attention_outputs_agrees_with_cpu(cuda_lib):
         top2 = np.sort(lw[i])[-2:]
         assert top2[1] - top2[0] < 1e-3, f"row {i}: argmax differs with margin {top2[1] - top2[0]}"
     assert len(diff) <= 2
+
+
+def oracle_unmask_round(logits, masked, tokens, B, strategy, thr):
+    """Host loop of infer/block_generation.c:229-252 over the oracle's functions."""
+    o = ob.oracle()
+    batch = masked.shape[0]
+    conf = np.zeros((batch, B), np.float32)
+    ent = np.zeros((batch, B), np.float32)
+    sel = np.zeros(batch, np.int64)
+    for c in range(batch):
+        pred = np.zeros(B, np.int32)
+        for b in range(B):
+            row = np.ascontiguousarray(logits[c * B + b])
+            pm, en = C.c_float(), C.c_float()
+            o.oracle_row_analyze(row.ctypes.data_as(ob.c_f_p), len(row), C.byref(pm), C.byref(en))
+            conf[c, b], ent[c, b] = pm.value, en.value
+            pred[b] = o.oracle_argmax_row(row.ctypes.data_as(ob.c_f_p), len(row))
+        m = np.ascontiguousarray(masked[c])
+        mp = m.ctypes.data_as(C.POINTER(C.c_uint8))
+        if strategy == 0:
+            s = o.oracle_unmask_select_confidence(conf[c].ctypes.data_as(ob.c_f_p), mp, B, thr)
+        else:
+            s = o.oracle_unmask_select_eb(ent[c].ctypes.data_as(ob.c_f_p), mp, B, thr)
+        sel[c] = s
+        for b in range(B):
+            if s & (1 << b):
+                tokens[c, b] = pred[b]
+                masked[c, b] = 0
+    return sel, conf, ent
+
+
+@pytest.mark.parametrize("strategy,thr", [(0, 0.3), (0, 2.0), (1, 2.5), (1, 0.0)])
+def test_unmask_step_matches_host_loop(cuda_lib, strategy, thr):
+    """Rounds of the drafter's unmask loop on the device against the host loop: statistics to
+    float rounding of a double accumulation, selections / bytes / masks exactly."""
+    rng = np.random.default_rng(17 + strategy)
+    for B, V in ((1, 256), (4, 260), (16, 256), (32, 300)):
+        batch = 37
+        masked = (rng.random((batch, B)) < 0.8).astype(np.uint8)
+        masked[0] = 0                                   # nothing left to choose
+        masked[1] = 1
+        tokens = rng.integers(0, 256, (batch, B)).astype(np.uint8)
+        m_d, t_d = torch.from_numpy(masked.copy()).cuda(), torch.from_numpy(tokens.copy()).cuda()
+        for rnd in range(3):
+            sharp = rng.random((batch * B, 1)).astype(np.float32) * 6
+            logits = (rng.standard_normal((batch * B, V)).astype(np.float32) * sharp).astype(np.float32)
+            logits[3] = 0.25                            # uniform row: p_max = 1/V, entropy = ln V, argmax 0
+            want_sel, want_conf, want_ent = oracle_unmask_round(logits, masked, tokens, B, strategy, thr)
+            sel, conf, ent, left = ops.unmask_step(torch.from_numpy(logits).cuda(), m_d, t_d, strategy, thr)
+            np.testing.assert_allclose(conf.cpu().numpy(), want_conf, rtol=2e-6, atol=1e-9)
+            np.testing.assert_allclose(ent.cpu().numpy(), want_ent, rtol=2e-6, atol=1e-7)
+            assert (sel.cpu().numpy() == want_sel).all(), (B, V, rnd)
+            assert (m_d.cpu().numpy() == masked).all() and (t_d.cpu().numpy() == tokens).all()
+            assert (left.cpu().numpy() == masked.sum(axis=1)).all()

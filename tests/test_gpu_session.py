@@ -66,6 +66,23 @@ def test_session_decode_steps_and_rollback(cuda_lib):
     with pytest.raises(L.FbltError) as e:
         s.decode(4, 9, case.q, case.k_new, case.v_new, out, case.scale)
     assert e.value.status == L.ERR_CAPACITY
+    # per-sequence truncate: roll every sequence back by a different amount and decode again
+    for b in range(4):
+        case.k_cache[b, lens[b]] = case.k_new[b]
+        case.v_cache[b, lens[b]] = case.v_new[b]
+    lens = lens + 1 - np.array([0, 3, 50, 7], dtype=np.int32)
+    s.cache_truncate(lens)
+    assert (s.cache_lens(4) == lens).all()
+    case.base_len = lens.copy()
+    case.q, case.k_new, case.v_new = (rng.standard_normal((4, E)).astype(np.float32) for _ in range(3))
+    want, _ = oracle_decode(case)
+    s.decode(4, 1, case.q, case.k_new, case.v_new, out, case.scale, window=24)
+    assert_close(out, want, "session decode after truncate")
+    with pytest.raises(L.FbltError) as e:
+        s.cache_truncate([0, 0, 257, 0])
+    assert e.value.status == L.ERR_CAPACITY
+    s.cache_reset()
+    assert (s.cache_lens(4) == 0).all()
     s.close()
 
 
