@@ -218,9 +218,11 @@ def main():
     ap.add_argument("--cpu-prefill-seqs", type=int, default=512)
     ap.add_argument("--cpu-decode-seqs", type=int, default=128)
     ap.add_argument("--cpu-decode-steps", type=int, default=8)
-    ap.add_argument("--workload", default="scaled", choices=["scaled", "configs"],
+    ap.add_argument("--workload", default="scaled", choices=["scaled", "configs", "matmul"],
                     help="scaled = the headline job (one JSON line); configs = one line per small benchmark "
                          "configuration (byte self-attention, patch attention, cross-attention, cache decode)")
+    ap.add_argument("--matmul-small", action="store_true",
+                    help="matmul workload: only the decode-step shapes (8192 rows), for profiler captures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     args = ap.parse_args()
@@ -237,6 +239,9 @@ def main():
         return
     if args.workload == "configs":
         run_small_configs(args)
+        return
+    if args.workload == "matmul":
+        run_matmul(args)
         return
 
     import torch
@@ -479,6 +484,70 @@ def run_small_configs(args):
         want, cpu_s = oracle_decode(case)
         err = float(np.abs(out.cpu().numpy() - want).max())
         report(case.name, ms, case.algorithmic_bytes(), cpu_s, err, {"splits": int(d.splits)})
+
+
+def run_matmul(args):
+    """The projection GEMMs beside the attention operator (E = 1024: QKV [M,1024]x[1024,3072] and
+    output [M,1024]x[1024,1024]) at the row counts of the headline job: one line per shape and
+    precision with device time, TFLOP/s, the fraction of the tensor roofline, the same shape
+    through torch's fp32 matmul (cuBLAS SGEMM, what the reference calls on CUDA) and the
+    reference's CPU loop on a row sample."""
+    import torch
+    from fblt_b200 import lib as L
+    from fblt_b200 import ops
+    from oracle import binding as ob
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
+    bf16 = float(peaks.get("bf16_tflops", 1590.0))
+    torch.backends.cuda.matmul.allow_tf32 = False
+    g = torch.Generator(device="cuda").manual_seed(0)
+
+    def timed(fn):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = max(args.steps, 5)
+        torch.cuda.synchronize()
+        t0.record()
+        for _ in range(n):
+            fn()
+        t1.record()
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1) / n
+
+    shapes = (("qkv_prefill", 256508, 1024, 3072), ("proj_prefill", 256508, 1024, 1024),
+              ("qkv_decode_step", 8192, 1024, 3072), ("proj_decode_step", 8192, 1024, 1024))
+    for name, M, K, N in shapes[2:] if args.matmul_small else shapes:
+        a = torch.randn(M, K, device="cuda", generator=g)
+        b = torch.randn(K, N, device="cuda", generator=g) / 32.0
+        w = ops.PackedWeights(b)
+        out = torch.empty(M, N, device="cuda")
+        flops = 2.0 * M * K * N
+        ms_lib = timed(lambda: torch.matmul(a, b, out=out))
+        exact = (a[:64].double() @ b.double())
+        lib_err = float((out[:64].double() - exact).abs().max())
+        sample = a[:64].cpu().numpy()
+        t0 = time.perf_counter()
+        cpu_out = ob.matmul(sample, b.cpu().numpy(), use_ref=ob.have_ref())
+        cpu_s = time.perf_counter() - t0
+        for prec, tag, passes, rows_cta in ((L.PREC_FP32, "fp32 (3xTF32)", 3, 128), (L.PREC_FP32, "fp32 (3xTF32)", 3, 256),
+                                            (L.PREC_TF32, "tf32", 1, 128), (L.PREC_TF32, "tf32", 1, 256)):
+            L.load().fblt_matmul_set_rows_per_cta(rows_cta)
+            ms = timed(lambda: ops.matmul(a, w, out=out, precision=prec))
+            L.load().fblt_matmul_set_rows_per_cta(0)
+            assert L.load().fblt_tcgen05_error() == 0
+            err = float((out[:64].double() - exact).abs().max())
+            tf = flops / ms / 1e9
+            emit({"workload": f"matmul_{name}", "precision": tag, "rows_per_cta": rows_cta, "M": M, "K": K, "N": N, "ms": ms, "TFLOP/s": tf,
+                  "tensor_TFLOP/s": tf * passes,
+                  "frac_of_tf32_peak": tf * passes / (bf16 / 2.0),
+                  "tf32_peak_TFLOP/s": bf16 / 2.0, "peak_source": "measured bf16 cuBLAS figure / 2 (TF32 runs at half the bf16 rate)",
+                  "max_abs_err_vs_f64": err, "cublas_sgemm_ms": ms_lib, "cublas_sgemm_TFLOP/s": flops / ms_lib / 1e9,
+                  "cublas_sgemm_max_abs_err_vs_f64": lib_err,
+                  "cpu_reference": {"rows": 64, "seconds": cpu_s, "GFLOP/s": 2.0 * 64 * K * N / cpu_s / 1e9,
+                                    "max_abs_err_vs_f64": float(np.abs(cpu_out - exact.cpu().numpy()).max()), "cores": 1},
+                  "l2": "operands larger than L2 for the prefill shapes; decode-step shapes fit in L2"})
+        del a, b, w, out
 
 
 # dram bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in

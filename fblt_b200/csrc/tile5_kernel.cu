@@ -23,6 +23,7 @@
 // Every mbarrier wait is bounded: after kSpinLimit polls the CTA records an
 // error code, stops issuing work, frees its TMEM and returns.
 #include "common.cuh"
+#include "tc5.cuh"
 
 #include <atomic>
 #include <limits.h>
@@ -30,7 +31,6 @@
 namespace fblt {
 
 constexpr int kT5Rows = 128, kT5Keys = 64, kT5HD = 64, kT5Threads = 128;
-constexpr uint32_t kSpinLimit = 1u << 22; // x ~100 ns per poll: well under a second
 constexpr int kPlaneKV = kT5Keys * kT5HD * 4;   // 16 KB: one (hi or lo) plane of a K or V tile
 constexpr int kPlaneP = kT5Rows * kT5Keys * 4;  // 32 KB: one plane of P
 // shared memory map (bytes): [0,32K) K hi|lo, reused by P hi; [32K,64K) V hi|lo; [64K,96K) P lo
@@ -39,117 +39,6 @@ constexpr int kOffK = 0, kOffV = 2 * kPlaneKV, kOffPlo = 4 * kPlaneKV, kT5Smem =
 constexpr uint32_t kColQhi = 0, kColQlo = 64, kColS = 128, kColO = 192, kT5Cols = 256;
 
 __device__ unsigned int g_t5_error; // 0 = ok; otherwise (code << 24) | blockIdx.x of the first CTA that gave up
-
-// ---- PTX wrappers ------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-// Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-    const uint32_t addr = smem_u32(bar);
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        uint32_t done;
-        asm volatile("{\n\t.reg .pred p;\n\t"
-                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                     "selp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(done)
-                     : "r"(addr), "r"(parity)
-                     : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
-                 "r"(cols)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-// arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed
-__device__ __forceinline__ void tc_commit(uint64_t *bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem descriptor], TF32 inputs, fp32 accumulate
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
-                 : "memory");
-}
-// D[tmem] (+)= A[smem descriptor] * B[smem descriptor]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t acc) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-                 "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
-                 : "memory");
-}
-
-// 32 consecutive TMEM columns of this thread's lane -> registers / back
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
-                   "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
-                   "=r"(r[30]), "=r"(r[31])
-                 : "r"(taddr)
-                 : "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-                 "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-                 "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
-                 "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
-                 "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-                 : "memory");
-}
-
-__device__ __forceinline__ uint32_t t5_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return r;
-}
-__device__ __forceinline__ float t5_ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-// Shared-memory matrix descriptor, no swizzle: start address, leading-dimension
-// and stride byte offsets in 16-byte units, descriptor version 1 (bits 46-47).
-__device__ __forceinline__ uint64_t t5_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
-}
-
-// Instruction descriptor: fp32 accumulate (bits 4-5 = 1), A and B TF32 (bits 7-9, 10-12 = 2),
-// A K-major, B K-major or MN-major (bit 16), N / 8 at bits 17-22, M / 16 at bits 24-28.
-__host__ __device__ constexpr uint32_t t5_idesc(int m, int n, int b_mn_major) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(m >> 4) << 24);
-}
 
 // ---- the kernel -----------------------------------------------------------------
 
@@ -488,6 +377,8 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
     if (warp == 0) tmem_dealloc(tmem, kT5Cols);
 }
 
+int gemm5_take_error(); // gemm5_kernel.cu
+
 bool tile5_kernel_supports(const fblt_attn_desc &d, const char **why) {
     if (d.head_dim != 64) {
         *why = "tcgen05 kernel: head_dim must be 64";
@@ -541,5 +432,6 @@ extern "C" int fblt_tcgen05_error(void) {
     if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     if (cudaMemcpyFromSymbol(&v, fblt::g_t5_error, sizeof(v)) != cudaSuccess) return -1;
     if (v) cudaMemcpyToSymbol(fblt::g_t5_error, &zero, sizeof(zero));
-    return (int)v;
+    const int g = fblt::gemm5_take_error();
+    return v ? (int)v : g;
 }

@@ -110,6 +110,12 @@ SYMBOLS = {
     "fblt_unmask_step": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float,
                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "fblt_kv_common_patches": (C.c_size_t, [C.POINTER(PatchInfo), C.c_size_t, C.POINTER(PatchInfo), C.c_size_t]),
+    "fblt_matmul_packed_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
+    "fblt_matmul_pack_weights": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t,
+                                           C.c_void_p]),
+    "fblt_matmul": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+                              C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
+    "fblt_matmul_set_rows_per_cta": (C.c_int, [C.c_int32]),
     "fblt_session_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int32, C.c_int32]),
     "fblt_session_destroy": (None, [C.c_void_p]),

@@ -267,6 +267,30 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     return ids
 
 
+class PackedWeights:
+    """b [K, N] packed for fblt_matmul (device buffer + shape)."""
+
+    def __init__(self, b: torch.Tensor):
+        assert b.dim() == 2 and b.dtype == torch.float32 and b.is_cuda and b.stride(1) == 1
+        self.K, self.N = int(b.shape[0]), int(b.shape[1])
+        lib = L.load()
+        nbytes = lib.fblt_matmul_packed_bytes(self.K, self.N)
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=b.device)
+        L.check(lib.fblt_matmul_pack_weights(b.data_ptr(), b.stride(0), self.K, self.N, self.buf.data_ptr(), nbytes,
+                                             _stream_ptr(None)))
+
+
+def matmul(a: torch.Tensor, w: PackedWeights, out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+           precision: int = L.PREC_FP32) -> torch.Tensor:
+    """out = a @ b (+ bias) with b given as PackedWeights; a [M, K] float32 with unit column stride."""
+    assert a.dim() == 2 and a.dtype == torch.float32 and a.stride(1) == 1 and a.shape[1] == w.K
+    if out is None:
+        out = torch.empty(a.shape[0], w.N, dtype=torch.float32, device=a.device)
+    L.check(L.load().fblt_matmul(a.data_ptr(), a.stride(0), w.buf.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                 out.data_ptr(), out.stride(0), a.shape[0], w.K, w.N, precision, _stream_ptr(None)))
+    return out
+
+
 def unmask_step(logits: torch.Tensor, masked: torch.Tensor, tokens: torch.Tensor, strategy: int, threshold: float):
     """One unmask round over a batch of candidates. logits [batch*B, V] float32, masked/tokens
     [batch, B] uint8 (updated in place). Returns (sel [batch] int64 bit masks, conf [batch,B],

@@ -435,6 +435,30 @@ size_t fblt_kv_common_patches(const fblt_patch_info *cached, size_t num_cached, 
                               size_t num_patches);
 
 /* ------------------------------------------------------------------------ */
+/* projection GEMMs on both sides of the attention operator                 */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * out[M, N] = a[M, K] * b[K, N] (+ bias[N]), fp32 row-major: blt_matmul
+ * (ops/matmul.h:8; CPU loop ops/linalg_cpu.c:8-18, cublasSgemm call
+ * ops/linalg.cu:134-136) as used for the QKV and output projections
+ * (models/attention.c:156,206; models/cross_attention.c:139-141,154).
+ * The weight matrix is packed once -- split into TF32 (hi, lo) parts and
+ * laid out in the tile order the tensor-core kernel consumes -- and reused
+ * by every call; activations are split on the fly. FBLT_PREC_FP32 runs three
+ * TF32 products per term (lo*hi + hi*lo + hi*hi, fp32 accumulate: fp32-class
+ * accuracy), FBLT_PREC_TF32 one. K and lda must be multiples of 4 and `a`
+ * 16-byte aligned; M, N are arbitrary. All pointers device.
+ */
+size_t fblt_matmul_packed_bytes(int64_t K, int64_t N);
+int fblt_matmul_pack_weights(const float *b, int64_t ldb, int64_t K, int64_t N, void *packed, size_t packed_bytes,
+                             void *stream);
+int fblt_matmul(const float *a, int64_t lda, const void *packed_b, const float *bias, float *out, int64_t ldo,
+                int64_t M, int64_t K, int64_t N, int32_t precision, void *stream);
+/* Tuning knob: rows of `a` one CTA covers (128 or 256; 0 = chosen from M). Process-wide. */
+int fblt_matmul_set_rows_per_cta(int32_t rows);
+
+/* ------------------------------------------------------------------------ */
 /* host-buffer sessions (what a host-side caller with no device memory uses) */
 /* ------------------------------------------------------------------------ */
 
@@ -497,7 +521,7 @@ int fblt_session_cache_reset(fblt_session *s);
 int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch);
 
 /*
- * The tcgen05 kernel bounds every mbarrier wait; a CTA whose wait runs out records a code,
+ * The tcgen05 kernels (attention tile, matmul) bound every mbarrier wait; a CTA whose wait runs out records a code,
  * frees its TMEM and returns without writing its rows. This call synchronises the device,
  * returns that code (0 = none, -1 = CUDA error) and clears it.
  */

@@ -416,3 +416,16 @@ void oracle_rope_apply(const float *x, const float *cos_t, const float *sin_t, f
         }
     }
 }
+
+/* ---- projection matmul -------------------------------------------------------- */
+
+/* ops/linalg_cpu.c:8-18 */
+void oracle_matmul(const float *a, const float *b, float *out, size_t m, size_t k, size_t n) {
+    for (size_t i = 0; i < m; ++i) {
+        for (size_t j = 0; j < n; ++j) {
+            float acc = 0.0f;
+            for (size_t t = 0; t < k; ++t) acc += a[i * k + t] * b[t * n + j];
+            out[i * n + j] = acc;
+        }
+    }
+}

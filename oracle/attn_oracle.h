@@ -74,4 +74,8 @@ void oracle_rope_precompute(size_t max_seq_len, float theta, size_t head_dim, fl
 void oracle_rope_apply(const float *x, const float *cos_t, const float *sin_t, float *out, size_t rows, size_t heads,
                        size_t head_dim);
 
+/* ops/linalg_cpu.c:8-18: out[m, n] = a[m, k] * b[k, n], one fp32 accumulator per output,
+ * depth index ascending. */
+void oracle_matmul(const float *a, const float *b, float *out, size_t m, size_t k, size_t n);
+
 #endif

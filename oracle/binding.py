@@ -130,6 +130,18 @@ def rope_apply(x: np.ndarray, cos_rows: np.ndarray, sin_rows: np.ndarray, heads:
     return out
 
 
+def matmul(a: np.ndarray, b: np.ndarray, use_ref: bool = False) -> np.ndarray:
+    """out = a @ b the way blt_matmul's CPU branch computes it (sequential fp32 accumulation)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    out = np.empty((a.shape[0], b.shape[1]), dtype=np.float32)
+    fn = ref().ref_matmul if use_ref else oracle().oracle_matmul
+    fn.argtypes = [c_f_p, c_f_p, c_f_p, C.c_size_t, C.c_size_t, C.c_size_t]
+    fn.restype = None
+    fn(_fp(a), _fp(b), _fp(out), a.shape[0], a.shape[1], b.shape[1])
+    return out
+
+
 def host_cores() -> int:
     try:
         return len(os.sched_getaffinity(0))

@@ -26,6 +26,7 @@
 #include "models/patcher.h"
 #include "ops/attn_core.h"
 #include "ops/mask_builder.h"
+#include "ops/matmul.h"
 #include "ops/patch_pool.h"
 #include "ops/rope.h"
 
@@ -160,6 +161,15 @@ size_t ref_kv_common_patches(const blt_patch_info *cached, size_t num_cached, co
     cache.cached_patches = (blt_patch_info *)cached;
     cache.cross_num_patches = num_cached;
     return blt_kv_cache_common_patches(&cache, patches, num_patches);
+}
+
+/* out[m, n] = a[m, k] * b[k, n], the reference's CPU matmul. */
+void ref_matmul(const float *a, const float *b, float *out, size_t m, size_t k, size_t n) {
+    blt_tensor at, bt, ot;
+    blt_tensor_view_2d(&at, (void *)a, m, k, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&bt, (void *)b, k, n, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&ot, out, m, n, BLT_BACKEND_CPU);
+    blt_matmul(&at, &bt, &ot);
 }
 
 void ref_rope_precompute(size_t max_seq_len, float theta, size_t head_dim, float *cos_out, float *sin_out) {

@@ -185,3 +185,13 @@ def test_golden_fixtures():
             elif kind == "latent":
                 got = [ob.latent_at(g["bounds"], int(p), use_ref=ref) for p in g["pos"]]
                 assert got == list(g["latent"]), f.name
+
+
+def test_matmul_restatement_equals_reference():
+    if not ob.have_ref():
+        pytest.skip("reference object code not built")
+    rng = np.random.default_rng(5)
+    for m, k, n in ((1, 1, 1), (7, 33, 5), (64, 256, 96)):
+        a = rng.standard_normal((m, k)).astype(np.float32)
+        b = rng.standard_normal((k, n)).astype(np.float32)
+        assert ob.matmul(a, b).tobytes() == ob.matmul(a, b, use_ref=True).tobytes()
