@@ -530,15 +530,12 @@ def run_matmul(args):
         t0 = time.perf_counter()
         cpu_out = ob.matmul(sample, b.cpu().numpy(), use_ref=ob.have_ref())
         cpu_s = time.perf_counter() - t0
-        for prec, tag, passes, rows_cta in ((L.PREC_FP32, "fp32 (3xTF32)", 3, 128), (L.PREC_FP32, "fp32 (3xTF32)", 3, 256),
-                                            (L.PREC_TF32, "tf32", 1, 128), (L.PREC_TF32, "tf32", 1, 256)):
-            L.load().fblt_matmul_set_rows_per_cta(rows_cta)
+        for prec, tag, passes in ((L.PREC_FP32, "fp32 (3xTF32)", 3), (L.PREC_TF32, "tf32", 1)):
             ms = timed(lambda: ops.matmul(a, w, out=out, precision=prec))
-            L.load().fblt_matmul_set_rows_per_cta(0)
             assert L.load().fblt_tcgen05_error() == 0
             err = float((out[:64].double() - exact).abs().max())
             tf = flops / ms / 1e9
-            emit({"workload": f"matmul_{name}", "precision": tag, "rows_per_cta": rows_cta, "M": M, "K": K, "N": N, "ms": ms, "TFLOP/s": tf,
+            emit({"workload": f"matmul_{name}", "precision": tag, "M": M, "K": K, "N": N, "ms": ms, "TFLOP/s": tf,
                   "tensor_TFLOP/s": tf * passes,
                   "frac_of_tf32_peak": tf * passes / (bf16 / 2.0),
                   "tf32_peak_TFLOP/s": bf16 / 2.0, "peak_source": "measured bf16 cuBLAS figure / 2 (TF32 runs at half the bf16 rate)",

@@ -6,18 +6,24 @@
 //            parts and laid out tile by tile in the exact shared-memory image the MMA reads
 //            (no-swizzle K-major core matrices, [n][k] order), so one thread brings a
 //            128 x 32 weight tile in with one bulk copy that completes on an mbarrier.
-//   a      = 128 or 256 rows x 32 per step; eight producer warps load 16-byte pieces two
-//            steps ahead into registers, split them into (hi, lo) and store them in the same
-//            core-matrix layout, then arrive on the stage's mbarrier.
-//   MMA    = one thread; per step and 128-row sub-tile 4 x (lo*hi, hi*lo -> small-term
-//            accumulator; hi*hi -> main accumulator) tcgen05.mma of shape 128x128x8, fp32
-//            accumulate in TMEM; tcgen05.commit hands the stage back to the producers. The
-//            small terms are kept apart because the tensor core truncates when it adds into
-//            the accumulator: one addition per 8-deep slice into the main sum, not three.
+//   a      = one thread brings each raw 128 x 32 fp32 tile in with a tiled TMA load (128-byte
+//            swizzle, rows past M and depth past K filled with zeros by the copy engine).
+//            The A operand of the MMA lives in TMEM, not in shared memory: eight producer
+//            warps (thread = one row of the tile = one TMEM lane, warps w and w + 4 share a
+//            lane quarter and take 16 of the step's 32 depth values each) read their row
+//            from the swizzled tile without bank conflicts, split it into (hi, lo) and write
+//            both with tcgen05.st.
+//   MMA    = one thread; per 32-deep step 4 x (lo*hi, hi*lo -> small-term accumulator;
+//            hi*hi -> main accumulator) tcgen05.mma of shape 128x128x8 with A from TMEM, fp32
+//            accumulate in TMEM; tcgen05.commit hands the stage back. The small terms are
+//            kept apart because the tensor core truncates when it adds into the accumulator:
+//            one addition per 8-deep slice into the main sum, not three.
 //   out    = the producer warps read main + small accumulators (warp w: TMEM lanes
 //            32 (w & 3).., columns 64 (w >> 2)..), add the bias and store.
-//   No __syncthreads in the main loop: the three roles meet only on mbarriers
-//   (a ready, b ready, stage free, all done).
+//   No __syncthreads in the main loop: the four roles meet only on mbarriers (raw a landed,
+//   raw a read, a in TMEM, b landed, stage free, all done).
+//
+// TMEM columns: [0,128) main accumulator, [128,256) small terms, 256 + 64 stage: A hi | A lo.
 //
 // Every mbarrier wait is bounded and watches a CTA-wide abort word; a role that gives up
 // raises it, the CTA records an error code, waits (bounded) for its copies and MMAs in
@@ -26,23 +32,20 @@
 #include "tc5.cuh"
 
 #include <atomic>
+#include <cuda.h> // CUtensorMap and its enums only; the encoder is looked up at run time
 
 namespace fblt {
 
 constexpr int kGM = 128, kGN = 128, kGK = 32;
 constexpr int kGProducers = 256;               // warps 0-7: stage a, then run the epilogue
-constexpr int kGThreads = kGProducers + 64;    // warp 8: MMA issue (and TMEM owner); warp 9: weight copies
-constexpr int kGPlane = kGM * kGK * 4;         // 16 KB: one (hi or lo) plane of a 128 x 32 operand tile
-constexpr int kGPrefetch = 4;                  // steps of a held in registers ahead of the stores (covers the load latency)
-
-// MT = 128-row sub-tiles of a per CTA; they share the weight tile.
-template <int MT> struct GemmCfg {
-    static constexpr int kStageBytes = (2 * MT + 2) * kGPlane; // MT x (A hi | A lo), B hi | B lo
-    static constexpr int kStages = MT == 1 ? 3 : 2;
-    static constexpr int kSmem = kStages * kStageBytes;
-    static constexpr int kOffB = 2 * MT * kGPlane;
-    static constexpr uint32_t kCols = 2 * MT * 128;            // MT main + MT small-term accumulators
-};
+constexpr int kGThreads = kGProducers + 96;    // warp 8: MMA issue (and TMEM owner); warp 9: weight copies; warp 10: a tiles
+constexpr int kGPlane = kGN * kGK * 4;         // 16 KB: one (hi or lo) plane of a 128 x 32 weight tile
+constexpr int kGStages = 4;
+constexpr int kGStageBytes = 2 * kGPlane;      // B hi | B lo
+constexpr int kGRawBytes = kGM * kGK * 4;      // 16 KB: one raw fp32 tile of a (row = 128 bytes, 128-byte swizzle)
+constexpr int kGOffRaw = kGStages * kGStageBytes;
+constexpr int kGSmem = kGOffRaw + kGStages * kGRawBytes;
+constexpr uint32_t kGColSmall = 128, kGColA = 256, kGCols = 512;
 
 __device__ unsigned int g_gemm_error; // 0 = ok; otherwise (code << 24) | low bits of blockIdx.x
 
@@ -67,20 +70,19 @@ __global__ void __launch_bounds__(256) gemm5_pack_kernel(const float *b, int64_t
     *reinterpret_cast<float *>(packed + tile + kGPlane + off) = lo;
 }
 
-template <bool X3, int MT>
+template <bool X3>
 __global__ void __launch_bounds__(kGThreads, 1)
-    gemm5_kernel(const float *__restrict__ a, int64_t lda, const uint8_t *__restrict__ packed, const float *bias,
-                 float *__restrict__ out, int64_t ldo, int M, int K, int N, int ksteps, int ntn, int vec_out) {
-    using Cfg = GemmCfg<MT>;
-    constexpr int S = Cfg::kStages;
+    gemm5_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t *__restrict__ packed, const float *bias,
+                 float *__restrict__ out, int64_t ldo, int M, int N, int ksteps, int ntn, int vec_out) {
+    constexpr int S = kGStages;
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t bar_a[S], bar_b[S], bar_empty[S], bar_done;
+    __shared__ __align__(8) uint64_t bar_a[S], bar_b[S], bar_empty[S], bar_raw[S], bar_raw_free[S], bar_done;
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nt = blockIdx.x % ntn, mt = blockIdx.x / ntn; // column tiles fastest: neighbours share rows of a
-    const int row0 = mt * (kGM * MT);
+    const int row0 = mt * kGM;
     const uint32_t sbase = smem_u32(smem);
 
     if (tid == 0) {
@@ -89,13 +91,15 @@ __global__ void __launch_bounds__(kGThreads, 1)
             mbar_init(&bar_a[s], kGProducers / 32); // one arrival per producer warp
             mbar_init(&bar_b[s], 1);
             mbar_init(&bar_empty[s], 1);
+            mbar_init(&bar_raw[s], 1);
+            mbar_init(&bar_raw_free[s], kGProducers / 32);
         }
         mbar_init(&bar_done, 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 8) {
-        tmem_alloc(&tmem_slot, Cfg::kCols);
+        tmem_alloc(&tmem_slot, kGCols);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -105,61 +109,49 @@ __global__ void __launch_bounds__(kGThreads, 1)
     bool failed = false;
 
     if (warp < 8) {
-        // ---- producers: a tiles -> (hi, lo) planes ---------------------------------------------
-        constexpr int NP = 4 * MT; // 16-byte pieces per thread and step
-        float4 ar[kGPrefetch][NP];
-        auto load_a = [&](int s, float4 (&dst)[NP]) {
-#pragma unroll
-            for (int it = 0; it < NP; ++it) {
-                const int bid = it * 8 + warp; // 0 .. 32 MT - 1
-                const int r = (bid & (16 * MT - 1)) * 8 + (lane & 7), c = (bid / (16 * MT)) * 4 + (lane >> 3);
-                const int row = row0 + r, k = s * kGK + c * 4;
-                dst[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (row < M && k < K) dst[it] = __ldg(reinterpret_cast<const float4 *>(a + (int64_t)row * lda + k));
+        // ---- producers: a rows -> (hi, lo) TF32 parts in TMEM -------------------------------------
+        const int quarter = warp & 3, khalf = warp >> 2;
+        const int r = quarter * 32 + lane; // row of the tile = TMEM lane
+        const uint32_t tlane = tmem + ((uint32_t)(quarter * 32) << 16) + kGColA + khalf * 16;
+        for (int s = 0; s < ksteps; ++s) {
+            const int stage = s % S;
+            int ok = 1;
+            if (lane == 0) ok = mbar_wait_abort(&bar_raw[stage], (s / S) & 1, &s_abort); // one lane polls for the warp
+            if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                failed = true;
+                break;
             }
-        };
-        auto store_a = [&](int stage, const float4 (&src)[NP]) {
-            uint8_t *base = smem + stage * Cfg::kStageBytes;
+            // this row's 16 depth values: 16-byte piece c of row r sits at piece c ^ (r & 7)
+            const uint8_t *raw = smem + kGOffRaw + stage * kGRawBytes + r * 128;
+            float4 v[4];
 #pragma unroll
-            for (int it = 0; it < NP; ++it) {
-                const int bid = it * 8 + warp;
-                const int r = (bid & (16 * MT - 1)) * 8 + (lane & 7), c = (bid / (16 * MT)) * 4 + (lane >> 3);
-                const uint32_t off = (uint32_t)(r >> 7) * 2 * kGPlane + plane_offset(r & 127, c * 4);
-                const float e[4] = {src[it].x, src[it].y, src[it].z, src[it].w};
-                uint4 hi, lo;
-                uint32_t *h4 = &hi.x, *l4 = &lo.x;
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4 *>(raw + (((khalf * 4 + j) ^ (r & 7)) << 4));
+            uint32_t hi[16], lo[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    h4[x] = t5_tf32(e[x]);
-                    l4[x] = __float_as_uint(e[x] - __uint_as_float(h4[x]));
+                    hi[j * 4 + x] = t5_tf32(e[x]);
+                    lo[j * 4 + x] = __float_as_uint(e[x] - __uint_as_float(hi[j * 4 + x]));
                 }
-                *reinterpret_cast<uint4 *>(base + off) = hi;
-                if (X3) *reinterpret_cast<uint4 *>(base + kGPlane + off) = lo;
             }
-        };
-#pragma unroll
-        for (int u = 0; u < kGPrefetch; ++u)
-            if (u < ksteps) load_a(u, ar[u]);
-        for (int s0 = 0; s0 < ksteps && !failed; s0 += kGPrefetch) {
-#pragma unroll
-            for (int u = 0; u < kGPrefetch; ++u) {
-                const int s = s0 + u;
-                if (s >= ksteps) break;
-                const int stage = s % S;
-                if (s >= S) { // one lane polls for the warp
-                    int ok = 1;
-                    if (lane == 0) ok = mbar_wait_abort(&bar_empty[stage], ((s / S) - 1) & 1, &s_abort);
-                    if (!__shfl_sync(0xffffffffu, ok, 0)) {
-                        failed = true; // the MMAs of step s - S never released the stage
-                        break;
-                    }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_raw_free[stage]); // the raw tile may be overwritten
+            if (s >= S) {
+                if (lane == 0) ok = mbar_wait_abort(&bar_empty[stage], ((s / S) - 1) & 1, &s_abort);
+                if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                    failed = true; // the MMAs of step s - S never released the stage
+                    break;
                 }
-                store_a(stage, ar[u]);
-                if (s + kGPrefetch < ksteps) load_a(s + kGPrefetch, ar[u]);
-                fence_async_smem(); // every writer makes its stores visible to the tensor core ...
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_a[stage]); // ... then the warp arrives once
+                tc_fence_after();
             }
+            tmem_st16(tlane + stage * 64, hi);
+            if (X3) tmem_st16(tlane + stage * 64 + 32, lo);
+            tc_wait_st();
+            tc_fence_before(); // the TMEM stores are complete and ordered before ...
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_a[stage]); // ... the warp's arrival
         }
     } else if (warp == 8) {
         // ---- MMA issue ------------------------------------------------------------------------
@@ -173,28 +165,25 @@ __global__ void __launch_bounds__(kGThreads, 1)
                     break;
                 }
                 tc_fence_after();
-                const uint32_t sb = sbase + stage * Cfg::kStageBytes;
+                const uint32_t sb = sbase + stage * kGStageBytes;
+                const uint32_t ta = tmem + kGColA + stage * 64;
 #pragma unroll
                 for (int ks = 0; ks < kGK / 8; ++ks) {
-                    const uint64_t bh = t5_desc(sb + Cfg::kOffB + ks * 4096, 2048, 128);
-                    const uint64_t bl = t5_desc(sb + Cfg::kOffB + kGPlane + ks * 4096, 2048, 128);
+                    const uint64_t bh = t5_desc(sb + ks * 4096, 2048, 128);
+                    const uint64_t bl = t5_desc(sb + kGPlane + ks * 4096, 2048, 128);
+                    const uint32_t ah = ta + ks * 8, al = ta + 32 + ks * 8;
                     const uint32_t acc = (s > 0 || ks > 0) ? 1u : 0u;
-#pragma unroll
-                    for (int mi = 0; mi < MT; ++mi) {
-                        const uint64_t ah = t5_desc(sb + mi * 2 * kGPlane + ks * 4096, 2048, 128);
-                        const uint64_t al = t5_desc(sb + mi * 2 * kGPlane + kGPlane + ks * 4096, 2048, 128);
-                        if (X3) { // the two small products have an accumulator of their own
-                            mma_ss(tmem + (MT + mi) * 128, al, bh, kIdesc, acc);
-                            mma_ss(tmem + (MT + mi) * 128, ah, bl, kIdesc, 1);
-                        }
-                        mma_ss(tmem + mi * 128, ah, bh, kIdesc, acc);
+                    if (X3) { // the two small products have an accumulator of their own
+                        mma_ts(tmem + kGColSmall, al, bh, kIdesc, acc);
+                        mma_ts(tmem + kGColSmall, ah, bl, kIdesc, 1);
                     }
+                    mma_ts(tmem, ah, bh, kIdesc, acc);
                 }
                 tc_commit(&bar_empty[stage]);
             }
             tc_commit(&bar_done); // arrives when everything issued above has completed
         }
-    } else {
+    } else if (warp == 9) {
         // ---- weight tiles: one bulk copy per step ---------------------------------------------
         if (lane == 0) {
             const uint8_t *bsrc = packed + (int64_t)nt * ksteps * 2 * kGPlane;
@@ -207,12 +196,29 @@ __global__ void __launch_bounds__(kGThreads, 1)
                     break;
                 }
                 mbar_expect_tx(&bar_b[stage], kBBytes);
-                bulk_load(smem + stage * Cfg::kStageBytes + Cfg::kOffB, bsrc + (int64_t)s * 2 * kGPlane, kBBytes,
-                          &bar_b[stage]);
+                bulk_load(smem + stage * kGStageBytes, bsrc + (int64_t)s * 2 * kGPlane, kBBytes, &bar_b[stage]);
                 ++issued;
             }
             if (failed) { // copies still on their way into this CTA's shared memory
                 for (int x = issued > S ? issued - S : 0; x < issued; ++x) mbar_wait(&bar_b[x % S], (x / S) & 1);
+            }
+        }
+    } else {
+        // ---- raw a tiles: one tiled TMA load per step -----------------------------------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int s = 0; s < ksteps; ++s) {
+                const int stage = s % S;
+                if (s >= S && !mbar_wait_abort(&bar_raw_free[stage], ((s / S) - 1) & 1, &s_abort)) {
+                    failed = true;
+                    break;
+                }
+                mbar_expect_tx(&bar_raw[stage], kGRawBytes);
+                tma_load_2d(smem + kGOffRaw + stage * kGRawBytes, &a_map, s * kGK, row0, &bar_raw[stage]);
+                ++issued;
+            }
+            if (failed) {
+                for (int x = issued > S ? issued - S : 0; x < issued; ++x) mbar_wait(&bar_raw[x % S], (x / S) & 1);
             }
         }
     }
@@ -227,46 +233,43 @@ __global__ void __launch_bounds__(kGThreads, 1)
         tc_fence_after();
         const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const int chalf = (warp >> 2) * 64;
+        const int row = row0 + (warp & 3) * 32 + lane;
+        float *orow = out + (int64_t)(row < M ? row : 0) * ldo;
 #pragma unroll
-        for (int mi = 0; mi < MT; ++mi) {
-            const int row = row0 + mi * kGM + (warp & 3) * 32 + lane;
-            float *orow = out + (int64_t)(row < M ? row : 0) * ldo;
+        for (int q = 0; q < 2; ++q) {
+            float v[32];
+            if (!failed && ksteps > 0) { // uniform over the warp
+                tmem_ld32(trow + chalf + q * 32, v);
+                if (X3) {
+                    float w[32];
+                    tmem_ld32(trow + kGColSmall + chalf + q * 32, w);
+                    tc_wait_ld();
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                float v[32];
-                if (!failed && ksteps > 0) { // uniform over the warp
-                    tmem_ld32(trow + mi * 128 + chalf + q * 32, v);
-                    if (X3) {
-                        float w[32];
-                        tmem_ld32(trow + (MT + mi) * 128 + chalf + q * 32, w);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) v[c] += w[c];
-                    } else {
-                        tc_wait_ld();
-                    }
+                    for (int c = 0; c < 32; ++c) v[c] += w[c];
                 } else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] = 0.0f;
+                    tc_wait_ld();
                 }
-                if (row < M && !failed) {
-                    const int col0 = nt * kGN + chalf + q * 32;
+            } else {
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const int col = col0 + c * 4;
-                        float4 o = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
-                        if (vec_out && col + 3 < N) {
-                            if (bias) {
-                                const float4 bb = __ldg(reinterpret_cast<const float4 *>(bias + col));
-                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
-                            }
-                            *reinterpret_cast<float4 *>(orow + col) = o;
-                        } else {
-                            const float e[4] = {o.x, o.y, o.z, o.w};
+                for (int c = 0; c < 32; ++c) v[c] = 0.0f;
+            }
+            if (row < M && !failed) {
+                const int col0 = nt * kGN + chalf + q * 32;
 #pragma unroll
-                            for (int x = 0; x < 4; ++x)
-                                if (col + x < N) orow[col + x] = e[x] + (bias ? bias[col + x] : 0.0f);
+                for (int c = 0; c < 8; ++c) {
+                    const int col = col0 + c * 4;
+                    float4 o = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+                    if (vec_out && col + 3 < N) {
+                        if (bias) {
+                            const float4 bb = __ldg(reinterpret_cast<const float4 *>(bias + col));
+                            o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
                         }
+                        *reinterpret_cast<float4 *>(orow + col) = o;
+                    } else {
+                        const float e[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            if (col + x < N) orow[col + x] = e[x] + (bias ? bias[col + x] : 0.0f);
                     }
                 }
             }
@@ -277,7 +280,42 @@ __global__ void __launch_bounds__(kGThreads, 1)
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && s_abort) atomicCAS(&g_gemm_error, 0u, (2u << 24) | (blockIdx.x & 0xffffffu));
-    if (warp == 8) tmem_dealloc(tmem, Cfg::kCols);
+    if (warp == 8) tmem_dealloc(tmem, kGCols);
+}
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn tensor_map_encoder() {
+    static std::atomic<EncodeTiledFn> cached{nullptr};
+    EncodeTiledFn fn = cached.load(std::memory_order_acquire);
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = (EncodeTiledFn)p;
+        cached.store(fn, std::memory_order_release);
+    }
+    return fn;
+}
+
+// Map of a [M, K] (row stride lda) for 128-row x 32-column boxes, 128-byte swizzle, zero fill.
+static int make_a_map(CUtensorMap *map, const float *a, int64_t lda, int64_t M, int64_t K) {
+    EncodeTiledFn enc = tensor_map_encoder();
+    if (!enc) return fail(FBLT_ERR_CUDA, "matmul: cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)lda * sizeof(float)};
+    const cuuint32_t box[2] = {(cuuint32_t)kGK, (cuuint32_t)kGM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)a, dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(FBLT_ERR_CUDA, "matmul: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return FBLT_OK;
 }
 
 static int gemm5_configure() {
@@ -286,10 +324,8 @@ static int gemm5_configure() {
     FBLT_CUDA_TRY(cudaGetDevice(&dev));
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        FBLT_CUDA_TRY(cudaFuncSetAttribute(gemm5_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<1>::kSmem));
-        FBLT_CUDA_TRY(cudaFuncSetAttribute(gemm5_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<1>::kSmem));
-        FBLT_CUDA_TRY(cudaFuncSetAttribute(gemm5_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<2>::kSmem));
-        FBLT_CUDA_TRY(cudaFuncSetAttribute(gemm5_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<2>::kSmem));
+        FBLT_CUDA_TRY(cudaFuncSetAttribute(gemm5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGSmem));
+        FBLT_CUDA_TRY(cudaFuncSetAttribute(gemm5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGSmem));
         configured.fetch_or(bit, std::memory_order_release);
     }
     return FBLT_OK;
@@ -302,9 +338,6 @@ int gemm5_take_error() {
     if (v) cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(zero));
     return (int)v;
 }
-
-// 0 = choose by shape; 128 / 256 = rows of a per CTA (tuning knob, see fblt_matmul_set_rows_per_cta)
-static std::atomic<int> g_gemm_rows_per_cta{0};
 
 static inline int64_t ceil_div(int64_t x, int64_t y) { return (x + y - 1) / y; }
 
@@ -344,30 +377,20 @@ extern "C" int fblt_matmul(const float *a, int64_t lda, const void *packed_b, co
     if ((uintptr_t)packed_b & 15) return fail(FBLT_ERR_ARG, "matmul: packed weights must be 16-byte aligned");
     if (K > (1 << 24) || N > (1 << 24) || M > (int64_t)INT32_MAX) return fail(FBLT_ERR_LIMIT, "matmul: shape too large");
     const int ksteps = (int)ceil_div(K, kGK), ntn = (int)ceil_div(N, kGN);
-    const int mtile = (g_gemm_rows_per_cta == 128 || (g_gemm_rows_per_cta == 0 && M <= 128 * 148)) ? 1 : 2;
-    const int64_t tiles = ceil_div(M, kGM * mtile) * ntn;
+    const int64_t tiles = ceil_div(M, kGM) * ntn;
     if (tiles > (int64_t)INT32_MAX) return fail(FBLT_ERR_LIMIT, "matmul: too many tiles");
     const int st = gemm5_configure();
     if (st != FBLT_OK) return st;
     const int vec_out = !((ldo & 3) || ((uintptr_t)out & 15) || (bias && ((uintptr_t)bias & 15)));
-    const bool x3 = precision != FBLT_PREC_TF32;
-#define FBLT_GEMM_LAUNCH(X3_, MT_)                                                                              \
-    gemm5_kernel<X3_, MT_><<<(unsigned)tiles, kGThreads, GemmCfg<MT_>::kSmem, (cudaStream_t)stream>>>(          \
-        a, lda, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)K, (int)N, ksteps, ntn, vec_out)
-    if (mtile == 1) {
-        if (x3) FBLT_GEMM_LAUNCH(true, 1);
-        else FBLT_GEMM_LAUNCH(false, 1);
-    } else {
-        if (x3) FBLT_GEMM_LAUNCH(true, 2);
-        else FBLT_GEMM_LAUNCH(false, 2);
-    }
-#undef FBLT_GEMM_LAUNCH
+    CUtensorMap a_map;
+    const int mst = make_a_map(&a_map, a, lda, M, K);
+    if (mst != FBLT_OK) return mst;
+    if (precision != FBLT_PREC_TF32)
+        gemm5_kernel<true><<<(unsigned)tiles, kGThreads, kGSmem, (cudaStream_t)stream>>>(
+            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, vec_out);
+    else
+        gemm5_kernel<false><<<(unsigned)tiles, kGThreads, kGSmem, (cudaStream_t)stream>>>(
+            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, vec_out);
     count_launch();
     return check_launch("gemm5_kernel");
-}
-
-extern "C" int fblt_matmul_set_rows_per_cta(int32_t rows) {
-    if (rows != 0 && rows != 128 && rows != 256) return fblt::fail(FBLT_ERR_ARG, "matmul_set_rows_per_cta: 0, 128 or 256");
-    fblt::g_gemm_rows_per_cta.store(rows);
-    return FBLT_OK;
 }

@@ -115,7 +115,6 @@ SYMBOLS = {
                                            C.c_void_p]),
     "fblt_matmul": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                               C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
-    "fblt_matmul_set_rows_per_cta": (C.c_int, [C.c_int32]),
     "fblt_session_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int32, C.c_int32]),
     "fblt_session_destroy": (None, [C.c_void_p]),

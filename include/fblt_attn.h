@@ -455,8 +455,6 @@ int fblt_matmul_pack_weights(const float *b, int64_t ldb, int64_t K, int64_t N, 
                              void *stream);
 int fblt_matmul(const float *a, int64_t lda, const void *packed_b, const float *bias, float *out, int64_t ldo,
                 int64_t M, int64_t K, int64_t N, int32_t precision, void *stream);
-/* Tuning knob: rows of `a` one CTA covers (128 or 256; 0 = chosen from M). Process-wide. */
-int fblt_matmul_set_rows_per_cta(int32_t rows);
 
 /* ------------------------------------------------------------------------ */
 /* host-buffer sessions (what a host-side caller with no device memory uses) */
