@@ -36,9 +36,12 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
-    return r;
+    // Round to nearest, ties away from zero, to 10 mantissa bits -- the result of
+    // cvt.rna.tf32.f32 -- with integer instructions: the conversion instruction runs on the
+    // low-rate special-function pipe, which these kernels need for exp2. Inf / NaN pass through.
+    const uint32_t b = __float_as_uint(x);
+    const uint32_t r = (b + 0x1000u) & 0xFFFFE000u;
+    return (b & 0x7F800000u) == 0x7F800000u ? b : r;
 }
 // x = hi + lo with hi the TF32 rounding of x; lo is consumed by the tensor core
 // with its low mantissa bits ignored, which is below fp32 resolution of x.
