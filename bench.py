@@ -95,7 +95,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             f = [x.strip() for x in line.split(",")]
@@ -106,11 +106,15 @@ class ClockSampler:
                 mx.append(float(f[2]))
             except ValueError:
                 continue
+            try:
+                pw.append(float(f[3]))
+            except ValueError:
+                pass
             for name, val in zip(names, f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "power_w": statistics.median(pw) if pw else None}
 
 
 # ----------------------------------------------------------------------------- CPU reference legs
@@ -532,6 +536,15 @@ def run_matmul(args):
         cpu_s = time.perf_counter() - t0
         for prec, tag, passes in ((L.PREC_FP32, "fp32 (3xTF32)", 3), (L.PREC_TF32, "tf32", 1)):
             ms = timed(lambda: ops.matmul(a, w, out=out, precision=prec))
+            # clocks under this kernel: a second, longer loop with the sampler running
+            sampler = ClockSampler(torch.cuda.current_device())
+            sampler.start()
+            t_end = time.perf_counter() + 0.8
+            while time.perf_counter() < t_end:
+                for _ in range(8):
+                    ops.matmul(a, w, out=out, precision=prec)
+                torch.cuda.synchronize()
+            clocks = sampler.stop()
             assert L.load().fblt_tcgen05_error() == 0
             err = float((out[:64].double() - exact).abs().max())
             tf = flops / ms / 1e9
@@ -539,7 +552,7 @@ def run_matmul(args):
                   "tensor_TFLOP/s": tf * passes,
                   "frac_of_tf32_peak": tf * passes / (bf16 / 2.0),
                   "tf32_peak_TFLOP/s": bf16 / 2.0, "peak_source": "measured bf16 cuBLAS figure / 2 (TF32 runs at half the bf16 rate)",
-                  "max_abs_err_vs_f64": err, "cublas_sgemm_ms": ms_lib, "cublas_sgemm_TFLOP/s": flops / ms_lib / 1e9,
+                  "max_abs_err_vs_f64": err, "clocks": clocks, "cublas_sgemm_ms": ms_lib, "cublas_sgemm_TFLOP/s": flops / ms_lib / 1e9,
                   "cublas_sgemm_max_abs_err_vs_f64": lib_err,
                   "cpu_reference": {"rows": 64, "seconds": cpu_s, "GFLOP/s": 2.0 * 64 * K * N / cpu_s / 1e9,
                                     "max_abs_err_vs_f64": float(np.abs(cpu_out - exact.cpu().numpy()).max()), "cores": 1},
