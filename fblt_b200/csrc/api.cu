@@ -36,6 +36,7 @@ static int validate_desc(const fblt_attn_desc *d) {
     }
     if ((m.cu_doc == nullptr) != (m.doc_bounds == nullptr)) return fail(FBLT_ERR_ARG, "attn: cu_doc and doc_bounds go together");
     if ((d->rope_cos == nullptr) != (d->rope_sin == nullptr)) return fail(FBLT_ERR_ARG, "attn: rope_cos and rope_sin go together");
+    if (!d->rope_cos && (d->rope_q_pos || d->rope_k_pos)) return fail(FBLT_ERR_ARG, "attn: rotary positions without rotary tables");
     if (d->rope_cos && (d->head_dim & 1)) return fail(FBLT_ERR_ARG, "attn: rotary embedding needs an even head_dim");
     if (((uintptr_t)d->rope_cos | (uintptr_t)d->rope_sin) & 7) return fail(FBLT_ERR_ARG, "attn: rotary tables must be 8-byte aligned");
     return FBLT_OK;

@@ -130,7 +130,11 @@ template <class Search = ThreadSearch>
 __device__ __forceinline__ int query_group(const SeqMask &s, int i, const Search &srch = Search()) {
     if (s.group_rule == FBLT_GROUP_PATCH_ENC) return i / s.subtokens;
     if (s.group_rule == FBLT_GROUP_PATCH_DEC) {
-        if (s.trailing_closed && i == s.nq - 1) return s.P - 1;
+        // with num_clean (block-diffusion cross-attention, models/block_diffusion.c:164-186): rows past
+        // the clean prefix are the drafted block and read the last latent; the prefix ends at num_clean
+        if (s.num_clean >= 0 && i >= s.num_clean) return s.P - 1;
+        const int last = s.num_clean >= 0 ? s.num_clean - 1 : s.nq - 1;
+        if (s.trailing_closed && i == last) return s.P - 1;
         return latent_at(s, s.q_pos_off + i, srch);
     }
     return patch_of(s, s.q_pos_off + i, srch); // PATCH_LEQ
@@ -142,7 +146,7 @@ template <class Search = ThreadSearch>
 __device__ __forceinline__ void row_range(const SeqMask &s, int i, int &lo_out, int &hi_out,
                                           const Search &srch = Search()) {
     int lo = 0, hi = s.nk;
-    if (s.num_clean >= 0) {
+    if (s.num_clean >= 0 && s.group_rule == FBLT_GROUP_NONE) { // block-diffusion INFER self-attention
         if (i < s.num_clean) hi = min(hi, min(s.num_clean, i + 1));
     } else {
         if (s.is_causal) hi = min(hi, i + s.causal_off + 1);
@@ -189,7 +193,7 @@ __device__ __forceinline__ void row_range(const SeqMask &s, int i, int &lo_out, 
 // (ops/mask_builder_cpu.c:49-94, :125-135).
 __device__ __forceinline__ bool pair_allowed(const SeqMask &s, int i, int j) {
     bool ok = true;
-    if (s.num_clean >= 0) {
+    if (s.num_clean >= 0 && s.group_rule == FBLT_GROUP_NONE) {
         if (i < s.num_clean) ok = (j < s.num_clean) && (j <= i);
     } else {
         if (s.is_causal && j > i + s.causal_off) ok = false;

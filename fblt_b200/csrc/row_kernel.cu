@@ -53,7 +53,10 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
         acc[t] = 0.0f;
     }
     constexpr bool rope = ROPE; // a separate instantiation: the plain kernel keeps its register count
-    if constexpr (rope) rope_lanes<NT>(qv, d.rope_cos, d.rope_sin, i + s.causal_off, hd, lane);
+    const int32_t *kpos = rope ? d.rope_k_pos : nullptr; // optional gathered key positions of this sequence
+    if (kpos) kpos += k0;
+    if constexpr (rope)
+        rope_lanes<NT>(qv, d.rope_cos, d.rope_sin, d.rope_q_pos ? d.rope_q_pos[q0 + i] : i + s.causal_off, hd, lane);
 #pragma unroll
     for (int t = 0; t < NT; ++t) qv[t] *= qscale;
     float m = -INFINITY, l = 0.0f;
@@ -80,7 +83,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
                 kk[g][t] = (in_range && dd < hd) ? kj[dd] : 0.0f;
                 vv[g][t] = (in_range && dd < hd) ? vj[dd] : 0.0f;
             }
-            if constexpr (rope) rope_lanes<NT>(kk[g], d.rope_cos, d.rope_sin, in_range ? j : 0, hd, lane);
+            if constexpr (rope) rope_lanes<NT>(kk[g], d.rope_cos, d.rope_sin, in_range ? (kpos ? kpos[j] : j) : 0, hd, lane);
         }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
@@ -110,7 +113,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
             kloc[t] = dd < hd ? kj[dd] : 0.0f;
             vloc[t] = dd < hd ? vj[dd] : 0.0f;
         }
-        if constexpr (rope) rope_lanes<NT>(kloc, d.rope_cos, d.rope_sin, j, hd, lane);
+        if constexpr (rope) rope_lanes<NT>(kloc, d.rope_cos, d.rope_sin, kpos ? kpos[j] : j, hd, lane);
 #pragma unroll
         for (int t = 0; t < NT; ++t) part += qv[t] * kloc[t];
         part = warp_sum(part);

@@ -123,7 +123,9 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 kr[it] = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (j < nk) {
                     kr[it] = __ldg(reinterpret_cast<const float4 *>(kbase + (int64_t)j * d.k_stride + c * 4));
-                    if (d.rope_cos) kr[it] = rope_rotate4(kr[it], d.rope_cos, d.rope_sin, j, kT5HD / 2, c * 2);
+                    if (d.rope_cos)
+                        kr[it] = rope_rotate4(kr[it], d.rope_cos, d.rope_sin, d.rope_k_pos ? d.rope_k_pos[k0 + j] : j,
+                                              kT5HD / 2, c * 2);
                 }
             }
             {   // V: 16 keys x 2 pieces per warp step
@@ -195,7 +197,9 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 if (i < nq) {
                     v = __ldg(reinterpret_cast<const float4 *>(qrow + half * 32 + c * 4));
                     if (d.rope_cos)
-                        v = rope_rotate4(v, d.rope_cos, d.rope_sin, i + (d.mask.causal_offset ? d.mask.causal_offset[b] : 0),
+                        v = rope_rotate4(v, d.rope_cos, d.rope_sin,
+                                         d.rope_q_pos ? d.rope_q_pos[q0 + i]
+                                                      : i + (d.mask.causal_offset ? d.mask.causal_offset[b] : 0),
                                          kT5HD / 2, half * 16 + c * 2);
                 }
                 const float e[4] = {v.x * qscale, v.y * qscale, v.z * qscale, v.w * qscale};

@@ -173,7 +173,8 @@ __global__ void __launch_bounds__(kTileThreads, STAGES == 1 ? 4 : 2) tile_attn_k
                 const int r = c / CPR, cc = c - r * CPR;
                 if (j0 + r < nk) {
                     float4 *p4 = reinterpret_cast<float4 *>(rK + r * LDS + cc * 4);
-                    *p4 = rope_rotate4(*p4, d.rope_cos, d.rope_sin, j0 + r, HD / 2, cc * 2);
+                    *p4 = rope_rotate4(*p4, d.rope_cos, d.rope_sin, d.rope_k_pos ? d.rope_k_pos[k0 + j0 + r] : j0 + r,
+                                       HD / 2, cc * 2);
                 }
             }
             if (kt == kt_begin) {
@@ -182,7 +183,9 @@ __global__ void __launch_bounds__(kTileThreads, STAGES == 1 ? 4 : 2) tile_attn_k
                     const int r = c / CPR, cc = c - r * CPR;
                     if (qt * kBM + r < nq) {
                         float4 *p4 = reinterpret_cast<float4 *>(sQ + r * LDS + cc * 4);
-                        *p4 = rope_rotate4(*p4, d.rope_cos, d.rope_sin, qt * kBM + r + off, HD / 2, cc * 2);
+                        const int iq = qt * kBM + r;
+                        *p4 = rope_rotate4(*p4, d.rope_cos, d.rope_sin, d.rope_q_pos ? d.rope_q_pos[q0 + iq] : iq + off,
+                                           HD / 2, cc * 2);
                     }
                 }
             }

@@ -64,7 +64,7 @@ class AttnDesc(C.Structure):
         ("out", C.c_void_p), ("out_stride", C.c_int64),
         ("scale", C.c_float), ("reserved2", C.c_int32),
         ("mask", MaskDesc),
-        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p), ("rope_q_pos", C.c_void_p), ("rope_k_pos", C.c_void_p),
     ]
 
 

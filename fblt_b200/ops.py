@@ -161,7 +161,8 @@ class AttnBatch:
 def make_batch(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, cu_q: Sequence[int],
                cu_k: Sequence[int], num_heads: int, head_dim: int, scale: float,
                mask: Optional[MaskConfig] = None, impl: int = L.IMPL_AUTO, precision: int = L.PREC_FP32,
-               rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None) -> AttnBatch:
+               rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
+               rope_q_pos: Optional[torch.Tensor] = None, rope_k_pos: Optional[torch.Tensor] = None) -> AttnBatch:
     """q/k/v/out: 2-D fp32 CUDA views (rows packed over sequences, row stride = .stride(0),
     first column = head 0). cu_q / cu_k: row offsets [batch+1] (host)."""
     dev = q.device
@@ -193,6 +194,12 @@ def make_batch(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Ten
     if rope_cos is not None:
         d.rope_cos, d.rope_sin = rope_cos.data_ptr(), rope_sin.data_ptr()
         keep += [rope_cos, rope_sin]
+        if rope_q_pos is not None:
+            d.rope_q_pos = rope_q_pos.data_ptr()
+            keep.append(rope_q_pos)
+        if rope_k_pos is not None:
+            d.rope_k_pos = rope_k_pos.data_ptr()
+            keep.append(rope_k_pos)
     keep += [q, k, v, out]
     return AttnBatch(d, keep)
 

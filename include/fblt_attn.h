@@ -172,8 +172,13 @@ typedef enum {
  *                && group rule
  *                && (group rule == NONE || bidirectional_within_group || j <= i)
  *
- * and, when num_clean is given (block-diffusion INFER), the first two lines are
- * replaced by: i < N ? (j < N && j <= i) : true   (ops/mask_builder_cpu.c:127-135).
+ * and, when num_clean is given without a group rule (block-diffusion INFER
+ * self-attention), the first two lines are replaced by:
+ * i < N ? (j < N && j <= i) : true   (ops/mask_builder_cpu.c:127-135).
+ * With FBLT_GROUP_PATCH_DEC, num_clean describes the cross-attention of the
+ * same pass (models/block_diffusion.c:164-186): rows i < N use the decoder
+ * latent rule (trailing_closed applies to row N - 1), rows i >= N are the
+ * drafted block and read the last latent.
  *
  * All array members are device pointers to int32 (uint8 for trailing_closed);
  * NULL means "absent".
@@ -253,9 +258,15 @@ typedef struct {
      * [positions, head_dim/2] as blt_rope_precompute fills them. When given, q and k hold the
      * un-rotated QKV projection; query row i is rotated with position i + causal_offset[b]
      * and key row j with position j (interleaved pairs, ops/reductions_cpu.c:217-228)
-     * as they are loaded. NULL: q / k arrive rotated. head_dim must be even. */
+     * as they are loaded. NULL: q / k arrive rotated. head_dim must be even.
+     * rope_q_pos / rope_k_pos (optional, device int32, one entry per packed q / k row)
+     * replace those default positions: the gathered positions of the block-diffusion
+     * pass (models/block_diffusion.c:153-162 -- identity for clean rows, the recorded
+     * original position for block rows). Packed self-attention passes one array twice. */
     const float *rope_cos;
     const float *rope_sin;
+    const int32_t *rope_q_pos;
+    const int32_t *rope_k_pos;
 } fblt_attn_desc;
 
 int fblt_attn_forward(const fblt_attn_desc *desc, void *stream);

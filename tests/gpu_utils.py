@@ -21,12 +21,16 @@ def upload_case(case: ForwardCase):
 
 
 def forward_gpu(case: ForwardCase, impl: int = L.IMPL_AUTO, precision: int = L.PREC_FP32, fill: float = float("nan"),
-                rope=None):
-    """rope: optional (cos, sin) numpy tables [positions, head_dim/2]; the kernels then rotate Q and K."""
+                rope=None, rope_pos=None):
+    """rope: optional (cos, sin) numpy tables [positions, head_dim/2]; the kernels then rotate Q and K.
+    rope_pos: optional (q_pos, k_pos) int32 arrays, one position per packed row."""
     q, k, v = upload_case(case)
     rope_kw = {}
     if rope is not None:
         rope_kw = dict(rope_cos=torch.from_numpy(rope[0]).cuda(), rope_sin=torch.from_numpy(rope[1]).cuda())
+        if rope_pos is not None:
+            rope_kw.update(rope_q_pos=torch.from_numpy(np.ascontiguousarray(rope_pos[0], np.int32)).cuda(),
+                           rope_k_pos=torch.from_numpy(np.ascontiguousarray(rope_pos[1], np.int32)).cuda())
     out = torch.full((int(case.cu_q[-1]), case.embed), fill, dtype=torch.float32, device="cuda")
     batch = ops.make_batch(q, k, v, out, case.cu_q, case.cu_k, case.num_heads, case.head_dim, case.scale, case.mask,
                            impl=impl, precision=precision, **rope_kw)

@@ -44,7 +44,7 @@ def dense_masks(case: ForwardCase, ref: bool = False):
         off = int(m.causal_offset[b]) if m.causal_offset is not None else 0
         docs = m.doc_bounds[b] if m.doc_bounds is not None and len(m.doc_bounds[b]) else None
         k = m.subtokens
-        if m.num_clean is not None:
+        if m.num_clean is not None and m.group_rule == L.GROUP_NONE:
             mask, _ = ob.block_diffusion_mask(1, nq, int(m.num_clean[b]), use_ref=ref)
         elif m.group_rule == L.GROUP_NONE:
             mask, _ = ob.build_mask(nq, nk, window=m.sliding_window, doc_boundaries=docs, is_causal=m.is_causal,
@@ -66,8 +66,12 @@ def dense_masks(case: ForwardCase, ref: bool = False):
                                         bidirectional=m.bidirectional_within_group, use_ref=ref)
             elif m.group_rule == L.GROUP_PATCH_DEC:
                 qg = np.array([ob.latent_at(bounds, qpos + i, use_ref=ref) for i in range(nq)])
-                if m.trailing_closed is not None and m.trailing_closed[b]:
-                    qg[-1] = P - 1
+                # block-diffusion cross-attention (models/block_diffusion.c:164-186): the clean prefix ends
+                # at num_clean, the drafted rows behind it read the last latent
+                n_clean = int(m.num_clean[b]) if m.num_clean is not None else nq
+                qg[n_clean:] = P - 1
+                if m.trailing_closed is not None and m.trailing_closed[b] and n_clean > 0:
+                    qg[n_clean - 1] = P - 1
                 kg = np.arange(nk) // k
                 mask, _ = ob.build_mask(nq, nk, q_groups=qg, k_groups=kg,
                                         bidirectional=m.bidirectional_within_group, use_ref=ref)

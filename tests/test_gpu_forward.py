@@ -199,6 +199,34 @@ def test_fused_rotary_embedding(cuda_lib, hd):
             assert_close(got, want, f"rope hd={hd} impl={impl} prec={prec}", **tol)
 
 
+def test_block_diffusion_pass_gathered_positions_and_cross_rule(cuda_lib):
+    """The drafter's dense pass (models/block_diffusion.c:139-225): S = N + B rows, block rows carry
+    their recorded positions for the rotary embedding, self-attention under the INFER rule, and
+    cross-attention where clean rows read latent_at(i) and block rows the last latent."""
+    H, hd, B = 2, 64, 4
+    Ns = [60, 9, 130]
+    S = [n + B for n in Ns]
+    cu = np.concatenate([[0], np.cumsum(S)]).astype(np.int32)
+    cs, sn = ob.rope_tables(512, hd)
+    rng = np.random.default_rng(7)
+    pos = np.concatenate([np.concatenate([np.arange(n), n + rng.permutation(40)[:B]]) for n in Ns]).astype(np.int64)
+    raw = random_case(95, cu, cu, H, hd, MaskConfig(num_clean=Ns))
+    rotated = dataclasses.replace(raw, q=ob.rope_apply(raw.q, cs[pos], sn[pos], H, hd),
+                                  k=ob.rope_apply(raw.k, cs[pos], sn[pos], H, hd))
+    want, _, _ = oracle_forward(rotated)
+    for impl, prec in KERNELS + T5_KERNELS:
+        got, _ = forward_gpu(raw, impl, prec, rope=(cs, sn), rope_pos=(pos, pos))
+        tol = dict(atol=TF32_ATOL, rtol=TF32_RTOL) if prec == L.PREC_TF32 else {}
+        assert_close(got, want, f"diffusion self impl={impl} prec={prec}", **tol)
+    # cross-attention of the same pass: queries = the S rows, keys = P latents
+    bounds = [synth.bounds_from_lengths(synth.geometric_patches(31, b, n)) for b, n in enumerate(Ns)]
+    P = [len(x) - 1 for x in bounds]
+    cu_k = np.concatenate([[0], np.cumsum(P)]).astype(np.int32)
+    for trailing in ([0, 0, 0], [1, 0, 1]):
+        mask = MaskConfig(group_rule=L.GROUP_PATCH_DEC, patch_bounds=bounds, num_clean=Ns, trailing_closed=trailing)
+        check(random_case(96, cu, cu_k, H, hd, mask), kernels=[(L.IMPL_ROW, L.PREC_FP32), (L.IMPL_AUTO, L.PREC_FP32)])
+
+
 def test_rotary_tables_are_validated(cuda_lib):
     cs, sn = ob.rope_tables(64, 32)
     case = random_case(90, [0, 8], [0, 8], 1, 32, MaskConfig(is_causal=True))
