@@ -8,16 +8,20 @@
 //            128 x 32 weight tile in with one bulk copy that completes on an mbarrier.
 //   a      = one thread brings each raw 128 x 32 fp32 tile in with a tiled TMA load (128-byte
 //            swizzle, rows past M and depth past K filled with zeros by the copy engine).
-//            The A operand of the MMA lives in TMEM, not in shared memory: eight producer
-//            warps (thread = one row of the tile = one TMEM lane, warps w and w + 4 share a
-//            lane quarter and take 16 of the step's 32 depth values each) read their row
-//            from the swizzled tile without bank conflicts, split it into (hi, lo) and write
-//            both with tcgen05.st.
-//   MMA    = one thread; per 32-deep step 4 x (lo*hi, hi*lo -> small-term accumulator;
-//            hi*hi -> main accumulator) tcgen05.mma of shape 128x128x8 with A from TMEM, fp32
-//            accumulate in TMEM; tcgen05.commit hands the stage back. The small terms are
-//            kept apart because the tensor core truncates when it adds into the accumulator:
-//            one addition per 8-deep slice into the main sum, not three.
+//            The A operand of the MMA lives in TMEM, not in shared memory: a group of four
+//            producer warps (thread = one row of the tile = one TMEM lane) reads its rows
+//            from the swizzled tile without bank conflicts, splits them into (hi, lo) and
+//            writes both with tcgen05.st. Four such groups take the steps in turn: one
+//            conversion is a chain of waits, and the chains of consecutive steps overlap.
+//   MMA    = one thread; per 8-deep slice one tcgen05.mma of shape 128x256x8 (A hi from TMEM
+//            against the weight tile's high | low halves: hi*hi into the main accumulator,
+//            hi*lo into the small-term accumulator beside it) and one of shape 128x128x8
+//            (A lo * weight hi onto the small terms), fp32 accumulate in TMEM;
+//            tcgen05.commit hands the stage back. Issuing an MMA costs the thread about as
+//            long as the MMA runs, so fewer, wider instructions and one barrier per stage keep
+//            the tensor pipe fed. The small terms are kept apart because the tensor core
+//            truncates when it adds into the accumulator: one addition per 8-deep slice into
+//            the main sum, not three.
 //   out    = the producer warps read main + small accumulators (warp w: TMEM lanes
 //            32 (w & 3).., columns 64 (w >> 2)..), add the bias and store.
 //   No __syncthreads in the main loop: the four roles meet only on mbarriers (raw a landed,
@@ -37,8 +41,10 @@
 namespace fblt {
 
 constexpr int kGM = 128, kGN = 128, kGK = 32;
-constexpr int kGProducers = 256;               // warps 0-7: stage a, then run the epilogue
-constexpr int kGThreads = kGProducers + 96;    // warp 8: MMA issue (and TMEM owner); warp 9: weight copies; warp 10: a tiles
+constexpr int kGGroups = 4;                    // producer groups of four warps; group g converts steps g, g + 4, ...
+constexpr int kGProducers = kGGroups * 128;    // producer warps: stage a, then run the epilogue
+constexpr int kGThreads = kGProducers + 96;    // then: MMA issue (and TMEM owner); weight copies; a tiles
+constexpr int kGWarpMma = kGProducers / 32, kGWarpB = kGWarpMma + 1;
 constexpr int kGPlane = kGN * kGK * 4;         // 16 KB: one (hi or lo) plane of a 128 x 32 weight tile
 constexpr int kGStages = 4;
 constexpr int kGStageBytes = 2 * kGPlane;      // B hi | B lo
@@ -49,12 +55,15 @@ constexpr uint32_t kGColSmall = 128, kGColA = 256, kGCols = 512;
 
 __device__ unsigned int g_gemm_error; // 0 = ok; otherwise (code << 24) | low bits of blockIdx.x
 
-// byte offset of element (row r, depth k) inside a 128 x 32 plane
+// Byte offset of the high part of weight element (column r of the tile, depth k) inside a
+// 32 KB tile; the low part sits 2 KB further. Per 16-byte depth piece the tile holds 128 rows of
+// the high plane and then 128 rows of the low plane, so that the pair reads as one 256-row
+// K-major operand (high | low) and its first half as the 128-row high operand.
 __host__ __device__ constexpr uint32_t plane_offset(int r, int k) {
-    return (uint32_t)((k >> 2) * 2048 + (r >> 3) * 128 + (r & 7) * 16 + (k & 3) * 4);
+    return (uint32_t)((k >> 2) * 4096 + (r >> 3) * 128 + (r & 7) * 16 + (k & 3) * 4);
 }
 
-// b [K, N] row-major -> packed [n tile][k step][hi | lo][16 KB plane], zero padded.
+// b [K, N] row-major -> packed [n tile][k step][32 KB tile, see plane_offset], zero padded.
 __global__ void __launch_bounds__(256) gemm5_pack_kernel(const float *b, int64_t ldb, int K, int N, int ksteps,
                                                          int ntn, uint8_t *packed) {
     const int64_t np = (int64_t)ntn * kGN;
@@ -67,7 +76,7 @@ __global__ void __launch_bounds__(256) gemm5_pack_kernel(const float *b, int64_t
     const int64_t tile = ((int64_t)(n / kGN) * ksteps + k / kGK) * 2 * kGPlane;
     const uint32_t off = plane_offset(n % kGN, k % kGK);
     *reinterpret_cast<uint32_t *>(packed + tile + off) = hi;
-    *reinterpret_cast<float *>(packed + tile + kGPlane + off) = lo;
+    *reinterpret_cast<float *>(packed + tile + 2048 + off) = lo;
 }
 
 template <bool X3>
@@ -76,7 +85,8 @@ __global__ void __launch_bounds__(kGThreads, 1)
                  float *__restrict__ out, int64_t ldo, int M, int N, int ksteps, int ntn, int vec_out) {
     constexpr int S = kGStages;
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t bar_a[S], bar_b[S], bar_empty[S], bar_raw[S], bar_raw_free[S], bar_done;
+    // bar_full: A operand in TMEM (4 warp arrivals) and weight tile landed (1 arrival + bytes)
+    __shared__ __align__(8) uint64_t bar_full[S], bar_empty[S], bar_raw[S], bar_raw_free[S], bar_done;
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int s_abort;
 
@@ -88,17 +98,16 @@ __global__ void __launch_bounds__(kGThreads, 1)
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < S; ++s) {
-            mbar_init(&bar_a[s], kGProducers / 32); // one arrival per producer warp
-            mbar_init(&bar_b[s], 1);
+            mbar_init(&bar_full[s], 4 + 1);
             mbar_init(&bar_empty[s], 1);
             mbar_init(&bar_raw[s], 1);
-            mbar_init(&bar_raw_free[s], kGProducers / 32);
+            mbar_init(&bar_raw_free[s], 4);
         }
         mbar_init(&bar_done, 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 8) {
+    if (warp == kGWarpMma) {
         tmem_alloc(&tmem_slot, kGCols);
         tmem_relinquish();
     }
@@ -108,12 +117,14 @@ __global__ void __launch_bounds__(kGThreads, 1)
     const uint32_t tmem = tmem_slot;
     bool failed = false;
 
-    if (warp < 8) {
+    if (warp < kGWarpMma) {
         // ---- producers: a rows -> (hi, lo) TF32 parts in TMEM -------------------------------------
-        const int quarter = warp & 3, khalf = warp >> 2;
+        // The conversion of one step is a chain of waits (tile landed, stage free, TMEM store
+        // done); the groups take the steps in turn so that the chains overlap.
+        const int quarter = warp & 3, group = warp >> 2;
         const int r = quarter * 32 + lane; // row of the tile = TMEM lane
-        const uint32_t tlane = tmem + ((uint32_t)(quarter * 32) << 16) + kGColA + khalf * 16;
-        for (int s = 0; s < ksteps; ++s) {
+        const uint32_t tlane = tmem + ((uint32_t)(quarter * 32) << 16) + kGColA;
+        for (int s = group; s < ksteps; s += kGGroups) {
             const int stage = s % S;
             int ok = 1;
             if (lane == 0) ok = mbar_wait_abort(&bar_raw[stage], (s / S) & 1, &s_abort); // one lane polls for the warp
@@ -121,14 +132,14 @@ __global__ void __launch_bounds__(kGThreads, 1)
                 failed = true;
                 break;
             }
-            // this row's 16 depth values: 16-byte piece c of row r sits at piece c ^ (r & 7)
+            // this row's 32 depth values: 16-byte piece c of row r sits at piece c ^ (r & 7)
             const uint8_t *raw = smem + kGOffRaw + stage * kGRawBytes + r * 128;
-            float4 v[4];
+            float4 v[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float4 *>(raw + (((khalf * 4 + j) ^ (r & 7)) << 4));
-            uint32_t hi[16], lo[16];
+            for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const float4 *>(raw + ((j ^ (r & 7)) << 4));
+            uint32_t hi[32], lo[32];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < 8; ++j) {
                 const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
@@ -146,48 +157,50 @@ __global__ void __launch_bounds__(kGThreads, 1)
                 }
                 tc_fence_after();
             }
-            tmem_st16(tlane + stage * 64, hi);
-            if (X3) tmem_st16(tlane + stage * 64 + 32, lo);
+            tmem_st32(tlane + stage * 64, hi);
+            if (X3) tmem_st32(tlane + stage * 64 + 32, lo);
             tc_wait_st();
             tc_fence_before(); // the TMEM stores are complete and ordered before ...
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_a[stage]); // ... the warp's arrival
+            if (lane == 0) mbar_arrive(&bar_full[stage]); // ... the warp's arrival
         }
-    } else if (warp == 8) {
+    } else if (warp == kGWarpMma) {
         // ---- MMA issue ------------------------------------------------------------------------
         if (lane == 0) {
-            constexpr uint32_t kIdesc = t5_idesc(kGM, kGN, 0);
+            constexpr uint32_t kIdesc128 = t5_idesc(kGM, kGN, 0), kIdesc256 = t5_idesc(kGM, 2 * kGN, 0);
+            const uint64_t desc0 = t5_desc(sbase, 4096, 128); // + (byte offset >> 4) selects stage and depth slice
             for (int s = 0; s < ksteps; ++s) {
                 const int stage = s % S;
-                const uint32_t par = (s / S) & 1;
-                if (!mbar_wait_abort(&bar_a[stage], par, &s_abort) || !mbar_wait_abort(&bar_b[stage], par, &s_abort)) {
+                if (!mbar_wait_abort(&bar_full[stage], (s / S) & 1, &s_abort)) {
                     failed = true;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t sb = sbase + stage * kGStageBytes;
+                const uint64_t db = desc0 + (uint64_t)(stage * (kGStageBytes >> 4));
                 const uint32_t ta = tmem + kGColA + stage * 64;
 #pragma unroll
                 for (int ks = 0; ks < kGK / 8; ++ks) {
-                    const uint64_t bh = t5_desc(sb + ks * 4096, 2048, 128);
-                    const uint64_t bl = t5_desc(sb + kGPlane + ks * 4096, 2048, 128);
+                    const uint64_t bd = db + (uint64_t)(ks * (8192 >> 4));
                     const uint32_t ah = ta + ks * 8, al = ta + 32 + ks * 8;
                     const uint32_t acc = (s > 0 || ks > 0) ? 1u : 0u;
-                    if (X3) { // the two small products have an accumulator of their own
-                        mma_ts(tmem + kGColSmall, al, bh, kIdesc, acc);
-                        mma_ts(tmem + kGColSmall, ah, bl, kIdesc, 1);
+                    if (X3) {
+                        // one 256-wide MMA: columns [0,128) += hi*hi, columns [128,256) += hi*lo (the
+                        // small terms keep an accumulator of their own); then lo*hi onto the small terms
+                        mma_ts(tmem, ah, bd, kIdesc256, acc);
+                        mma_ts(tmem + kGColSmall, al, bd, kIdesc128, 1);
+                    } else {
+                        mma_ts(tmem, ah, bd, kIdesc128, acc);
                     }
-                    mma_ts(tmem, ah, bh, kIdesc, acc);
                 }
                 tc_commit(&bar_empty[stage]);
             }
             tc_commit(&bar_done); // arrives when everything issued above has completed
         }
-    } else if (warp == 9) {
+    } else if (warp == kGWarpB) {
         // ---- weight tiles: one bulk copy per step ---------------------------------------------
         if (lane == 0) {
             const uint8_t *bsrc = packed + (int64_t)nt * ksteps * 2 * kGPlane;
-            constexpr uint32_t kBBytes = X3 ? 2 * kGPlane : kGPlane; // hi and lo planes are adjacent
+            constexpr uint32_t kBBytes = X3 ? 2 * kGPlane : kGPlane;
             int issued = 0;
             for (int s = 0; s < ksteps; ++s) {
                 const int stage = s % S;
@@ -195,12 +208,19 @@ __global__ void __launch_bounds__(kGThreads, 1)
                     failed = true;
                     break;
                 }
-                mbar_expect_tx(&bar_b[stage], kBBytes);
-                bulk_load(smem + stage * kGStageBytes, bsrc + (int64_t)s * 2 * kGPlane, kBBytes, &bar_b[stage]);
+                mbar_expect_tx(&bar_full[stage], kBBytes);
+                if (X3) {
+                    bulk_load(smem + stage * kGStageBytes, bsrc + (int64_t)s * 2 * kGPlane, kBBytes, &bar_full[stage]);
+                } else { // single pass: only the high halves of the eight depth pieces
+#pragma unroll
+                    for (int pc = 0; pc < 8; ++pc)
+                        bulk_load(smem + stage * kGStageBytes + pc * 4096, bsrc + (int64_t)s * 2 * kGPlane + pc * 4096, 2048,
+                                  &bar_full[stage]);
+                }
                 ++issued;
             }
             if (failed) { // copies still on their way into this CTA's shared memory
-                for (int x = issued > S ? issued - S : 0; x < issued; ++x) mbar_wait(&bar_b[x % S], (x / S) & 1);
+                for (int x = issued > S ? issued - S : 0; x < issued; ++x) mbar_wait(&bar_full[x % S], (x / S) & 1);
             }
         }
     } else {
@@ -224,25 +244,26 @@ __global__ void __launch_bounds__(kGThreads, 1)
     }
     if (failed) s_abort = 1;
 
-    // ---- epilogue: warps 0-7 read the accumulators (warp w: lanes 32 (w & 3).., columns 64 (w >> 2)..) ----
-    if (warp < 8) {
+    // ---- epilogue: the producer warps read the accumulators (warp w: lanes 32 (w & 3).., group's columns) ----
+    if (warp < kGWarpMma) {
         bool ok = !failed && ksteps > 0 ? mbar_wait_abort(&bar_done, 0, &s_abort) : !failed;
         ok = __all_sync(0xffffffffu, ok); // the TMEM loads below are warp-wide
         failed = !ok;
         if (failed) s_abort = 1;
         tc_fence_after();
+        constexpr int kColsPerGroup = kGN / kGGroups;
         const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        const int chalf = (warp >> 2) * 64;
+        const int cbase = (warp >> 2) * kColsPerGroup;
         const int row = row0 + (warp & 3) * 32 + lane;
         float *orow = out + (int64_t)(row < M ? row : 0) * ldo;
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
+        for (int q = 0; q < kColsPerGroup / 32; ++q) {
             float v[32];
             if (!failed && ksteps > 0) { // uniform over the warp
-                tmem_ld32(trow + chalf + q * 32, v);
+                tmem_ld32(trow + cbase + q * 32, v);
                 if (X3) {
                     float w[32];
-                    tmem_ld32(trow + kGColSmall + chalf + q * 32, w);
+                    tmem_ld32(trow + kGColSmall + cbase + q * 32, w);
                     tc_wait_ld();
 #pragma unroll
                     for (int c = 0; c < 32; ++c) v[c] += w[c];
@@ -254,7 +275,7 @@ __global__ void __launch_bounds__(kGThreads, 1)
                 for (int c = 0; c < 32; ++c) v[c] = 0.0f;
             }
             if (row < M && !failed) {
-                const int col0 = nt * kGN + chalf + q * 32;
+                const int col0 = nt * kGN + cbase + q * 32;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     const int col = col0 + c * 4;
@@ -274,13 +295,13 @@ __global__ void __launch_bounds__(kGThreads, 1)
                 }
             }
         }
-    } else if (warp == 8 && lane == 0 && failed) {
+    } else if (warp == kGWarpMma && lane == 0 && failed) {
         mbar_wait(&bar_done, 0); // bounded: let the MMAs in flight finish before the TMEM goes back
     }
     tc_fence_before();
     __syncthreads();
     if (tid == 0 && s_abort) atomicCAS(&g_gemm_error, 0u, (2u << 24) | (blockIdx.x & 0xffffffu));
-    if (warp == 8) tmem_dealloc(tmem, kGCols);
+    if (warp == kGWarpMma) tmem_dealloc(tmem, kGCols);
 }
 
 // cuTensorMapEncodeTiled, looked up through the runtime so that the library does not link libcuda.
