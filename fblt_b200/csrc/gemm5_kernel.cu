@@ -41,10 +41,10 @@
 namespace fblt {
 
 constexpr int kGM = 128, kGN = 128, kGK = 32;
-constexpr int kGGroups = 4;                    // producer groups of four warps; group g converts steps g, g + 4, ...
-constexpr int kGProducers = kGGroups * 128;    // producer warps: stage a, then run the epilogue
-constexpr int kGThreads = kGProducers + 96;    // then: MMA issue (and TMEM owner); weight copies; a tiles
-constexpr int kGWarpMma = kGProducers / 32, kGWarpB = kGWarpMma + 1;
+constexpr int kGGroups = 2;                    // producer groups of four warps; group g converts steps g, g + 2, ...
+constexpr int kGWarpEpi = kGGroups * 4;        // four epilogue warps follow the producer warps
+constexpr int kGWarpMma = kGWarpEpi + 4, kGWarpB = kGWarpMma + 1; // MMA issue (and TMEM owner); weight copies; a tiles
+constexpr int kGThreads = (kGWarpB + 2) * 32;
 constexpr int kGPlane = kGN * kGK * 4;         // 16 KB: one (hi or lo) plane of a 128 x 32 weight tile
 constexpr int kGStages = 4;
 constexpr int kGStageBytes = 2 * kGPlane;      // B hi | B lo
@@ -82,17 +82,16 @@ __global__ void __launch_bounds__(256) gemm5_pack_kernel(const float *b, int64_t
 template <bool X3>
 __global__ void __launch_bounds__(kGThreads, 1)
     gemm5_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t *__restrict__ packed, const float *bias,
-                 float *__restrict__ out, int64_t ldo, int M, int N, int ksteps, int ntn, int vec_out) {
+                 float *__restrict__ out, int64_t ldo, int M, int N, int ksteps, int ntn, int tiles, int vec_out) {
     constexpr int S = kGStages;
     extern __shared__ __align__(1024) uint8_t smem[];
-    // bar_full: A operand in TMEM (4 warp arrivals) and weight tile landed (1 arrival + bytes)
-    __shared__ __align__(8) uint64_t bar_full[S], bar_empty[S], bar_raw[S], bar_raw_free[S], bar_done;
+    // bar_full: A operand in TMEM (4 warp arrivals) and weight tile landed (1 arrival + bytes);
+    // bar_done: a tile's MMAs are complete; bar_acc_free: the epilogue has read the accumulators
+    __shared__ __align__(8) uint64_t bar_full[S], bar_empty[S], bar_raw[S], bar_raw_free[S], bar_done, bar_acc_free;
     __shared__ uint32_t tmem_slot;
     __shared__ volatile int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nt = blockIdx.x % ntn, mt = blockIdx.x / ntn; // column tiles fastest: neighbours share rows of a
-    const int row0 = mt * kGM;
     const uint32_t sbase = smem_u32(smem);
 
     if (tid == 0) {
@@ -104,6 +103,7 @@ __global__ void __launch_bounds__(kGThreads, 1)
             mbar_init(&bar_raw_free[s], 4);
         }
         mbar_init(&bar_done, 1);
+        mbar_init(&bar_acc_free, 4);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -117,107 +117,184 @@ __global__ void __launch_bounds__(kGThreads, 1)
     const uint32_t tmem = tmem_slot;
     bool failed = false;
 
-    if (warp < kGWarpMma) {
+    // The CTA is persistent: it takes tiles blockIdx.x, blockIdx.x + gridDim.x, ... (column tiles
+    // fastest, so CTAs running together share rows of a). Every role walks the same tile list
+    // with a running step count g, which also gives ring stage and barrier parity.
+    if (warp < kGWarpEpi) {
         // ---- producers: a rows -> (hi, lo) TF32 parts in TMEM -------------------------------------
         // The conversion of one step is a chain of waits (tile landed, stage free, TMEM store
         // done); the groups take the steps in turn so that the chains overlap.
         const int quarter = warp & 3, group = warp >> 2;
         const int r = quarter * 32 + lane; // row of the tile = TMEM lane
         const uint32_t tlane = tmem + ((uint32_t)(quarter * 32) << 16) + kGColA;
-        for (int s = group; s < ksteps; s += kGGroups) {
-            const int stage = s % S;
+        int g0 = 0;
+        for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x, g0 += ksteps) {
+            for (int s = 0; s < ksteps; ++s) {
+                const int g = g0 + s;
+                if (g % kGGroups != group) continue;
+                const int stage = g % S;
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait_abort(&bar_raw[stage], (g / S) & 1, &s_abort); // one lane polls for the warp
+                if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                    failed = true;
+                    break;
+                }
+                __syncwarp(); // lane 0's acquire of the barrier orders every lane's reads below
+                // this row's 32 depth values: 16-byte piece c of row r sits at piece c ^ (r & 7)
+                const uint8_t *raw = smem + kGOffRaw + stage * kGRawBytes + r * 128;
+                float4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const float4 *>(raw + ((j ^ (r & 7)) << 4));
+                uint32_t hi[32], lo[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        hi[j * 4 + x] = t5_tf32(e[x]);
+                        lo[j * 4 + x] = __float_as_uint(e[x] - __uint_as_float(hi[j * 4 + x]));
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_raw_free[stage]); // the raw tile may be overwritten
+                if (g >= S) {
+                    if (lane == 0) ok = mbar_wait_abort(&bar_empty[stage], ((g / S) - 1) & 1, &s_abort);
+                    if (!__shfl_sync(0xffffffffu, ok, 0)) {
+                        failed = true; // the MMAs of step g - S never released the stage
+                        break;
+                    }
+                    tc_fence_after();
+                }
+                tmem_st32(tlane + stage * 64, hi);
+                if (X3) tmem_st32(tlane + stage * 64 + 32, lo);
+                tc_wait_st();
+                tc_fence_before(); // the TMEM stores are complete and ordered before ...
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_full[stage]); // ... the warp's arrival
+            }
+        }
+    } else if (warp < kGWarpMma) {
+        // ---- epilogue: warp q reads TMEM lanes 32 q .. (one output row per thread) ------------------
+        const int quarter = warp - kGWarpEpi;
+        const uint32_t trow = tmem + ((uint32_t)(quarter * 32) << 16);
+        int it = 0;
+        for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x, ++it) {
+            const int nt = tile % ntn, mt = tile / ntn;
             int ok = 1;
-            if (lane == 0) ok = mbar_wait_abort(&bar_raw[stage], (s / S) & 1, &s_abort); // one lane polls for the warp
+            if (lane == 0) ok = mbar_wait_abort(&bar_done, it & 1, &s_abort);
             if (!__shfl_sync(0xffffffffu, ok, 0)) {
                 failed = true;
                 break;
             }
-            // this row's 32 depth values: 16-byte piece c of row r sits at piece c ^ (r & 7)
-            const uint8_t *raw = smem + kGOffRaw + stage * kGRawBytes + r * 128;
-            float4 v[8];
+            tc_fence_after();
+            const int row = mt * kGM + quarter * 32 + lane;
+            float *orow = out + (int64_t)(row < M ? row : 0) * ldo;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = *reinterpret_cast<const float4 *>(raw + ((j ^ (r & 7)) << 4));
-            uint32_t hi[32], lo[32];
+            for (int q = 0; q < kGN / 32; ++q) {
+                float v[32];
+                tmem_ld32(trow + q * 32, v);
+                if (X3) {
+                    float w[32];
+                    tmem_ld32(trow + kGColSmall + q * 32, w);
+                    tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                const float e[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                    for (int c = 0; c < 32; ++c) v[c] += w[c];
+                } else {
+                    tc_wait_ld();
+                }
+                if (q == kGN / 32 - 1) { // everything is in registers: the next tile may overwrite the accumulators
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bar_acc_free);
+                }
+                if (row < M) {
+                    const int col0 = nt * kGN + q * 32;
 #pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    hi[j * 4 + x] = t5_tf32(e[x]);
-                    lo[j * 4 + x] = __float_as_uint(e[x] - __uint_as_float(hi[j * 4 + x]));
+                    for (int c = 0; c < 8; ++c) {
+                        const int col = col0 + c * 4;
+                        float4 o = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+                        if (vec_out && col + 3 < N) {
+                            if (bias) {
+                                const float4 bb = __ldg(reinterpret_cast<const float4 *>(bias + col));
+                                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+                            }
+                            *reinterpret_cast<float4 *>(orow + col) = o;
+                        } else {
+                            const float e[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                            for (int x = 0; x < 4; ++x)
+                                if (col + x < N) orow[col + x] = e[x] + (bias ? bias[col + x] : 0.0f);
+                        }
+                    }
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_raw_free[stage]); // the raw tile may be overwritten
-            if (s >= S) {
-                if (lane == 0) ok = mbar_wait_abort(&bar_empty[stage], ((s / S) - 1) & 1, &s_abort);
-                if (!__shfl_sync(0xffffffffu, ok, 0)) {
-                    failed = true; // the MMAs of step s - S never released the stage
-                    break;
-                }
-                tc_fence_after();
-            }
-            tmem_st32(tlane + stage * 64, hi);
-            if (X3) tmem_st32(tlane + stage * 64 + 32, lo);
-            tc_wait_st();
-            tc_fence_before(); // the TMEM stores are complete and ordered before ...
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_full[stage]); // ... the warp's arrival
         }
     } else if (warp == kGWarpMma) {
         // ---- MMA issue ------------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t kIdesc128 = t5_idesc(kGM, kGN, 0), kIdesc256 = t5_idesc(kGM, 2 * kGN, 0);
             const uint64_t desc0 = t5_desc(sbase, 4096, 128); // + (byte offset >> 4) selects stage and depth slice
-            for (int s = 0; s < ksteps; ++s) {
-                const int stage = s % S;
-                if (!mbar_wait_abort(&bar_full[stage], (s / S) & 1, &s_abort)) {
-                    failed = true;
-                    break;
-                }
-                tc_fence_after();
-                const uint64_t db = desc0 + (uint64_t)(stage * (kGStageBytes >> 4));
-                const uint32_t ta = tmem + kGColA + stage * 64;
-#pragma unroll
-                for (int ks = 0; ks < kGK / 8; ++ks) {
-                    const uint64_t bd = db + (uint64_t)(ks * (8192 >> 4));
-                    const uint32_t ah = ta + ks * 8, al = ta + 32 + ks * 8;
-                    const uint32_t acc = (s > 0 || ks > 0) ? 1u : 0u;
-                    if (X3) {
-                        // one 256-wide MMA: columns [0,128) += hi*hi, columns [128,256) += hi*lo (the
-                        // small terms keep an accumulator of their own); then lo*hi onto the small terms
-                        mma_ts(tmem, ah, bd, kIdesc256, acc);
-                        mma_ts(tmem + kGColSmall, al, bd, kIdesc128, 1);
-                    } else {
-                        mma_ts(tmem, ah, bd, kIdesc128, acc);
+            int g = 0, it = 0;
+            for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x, ++it) {
+                if (it > 0) { // the previous tile's accumulators must have been read out
+                    if (!mbar_wait_abort(&bar_acc_free, (it - 1) & 1, &s_abort)) {
+                        failed = true;
+                        break;
                     }
+                    tc_fence_after();
                 }
-                tc_commit(&bar_empty[stage]);
+                for (int s = 0; s < ksteps; ++s, ++g) {
+                    const int stage = g % S;
+                    if (!mbar_wait_abort(&bar_full[stage], (g / S) & 1, &s_abort)) {
+                        failed = true;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t db = desc0 + (uint64_t)(stage * (kGStageBytes >> 4));
+                    const uint32_t ta = tmem + kGColA + stage * 64;
+#pragma unroll
+                    for (int ks = 0; ks < kGK / 8; ++ks) {
+                        const uint64_t bd = db + (uint64_t)(ks * (8192 >> 4));
+                        const uint32_t ah = ta + ks * 8, al = ta + 32 + ks * 8;
+                        const uint32_t acc = (s > 0 || ks > 0) ? 1u : 0u;
+                        if (X3) {
+                            // one 256-wide MMA: columns [0,128) += hi*hi, columns [128,256) += hi*lo (the
+                            // small terms keep an accumulator of their own); then lo*hi onto the small terms
+                            mma_ts(tmem, ah, bd, kIdesc256, acc);
+                            mma_ts(tmem + kGColSmall, al, bd, kIdesc128, 1);
+                        } else {
+                            mma_ts(tmem, ah, bd, kIdesc128, acc);
+                        }
+                    }
+                    tc_commit(&bar_empty[stage]);
+                }
+                if (!failed) tc_commit(&bar_done); // arrives when this tile's MMAs have completed
             }
-            tc_commit(&bar_done); // arrives when everything issued above has completed
         }
     } else if (warp == kGWarpB) {
         // ---- weight tiles: one bulk copy per step ---------------------------------------------
         if (lane == 0) {
-            const uint8_t *bsrc = packed + (int64_t)nt * ksteps * 2 * kGPlane;
             constexpr uint32_t kBBytes = X3 ? 2 * kGPlane : kGPlane;
-            int issued = 0;
-            for (int s = 0; s < ksteps; ++s) {
-                const int stage = s % S;
-                if (s >= S && !mbar_wait_abort(&bar_empty[stage], ((s / S) - 1) & 1, &s_abort)) {
-                    failed = true;
-                    break;
-                }
-                mbar_expect_tx(&bar_full[stage], kBBytes);
-                if (X3) {
-                    bulk_load(smem + stage * kGStageBytes, bsrc + (int64_t)s * 2 * kGPlane, kBBytes, &bar_full[stage]);
-                } else { // single pass: only the high halves of the eight depth pieces
+            int g = 0, issued = 0;
+            for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x) {
+                const uint8_t *bsrc = packed + (int64_t)(tile % ntn) * ksteps * 2 * kGPlane;
+                for (int s = 0; s < ksteps; ++s, ++g) {
+                    const int stage = g % S;
+                    if (g >= S && !mbar_wait_abort(&bar_empty[stage], ((g / S) - 1) & 1, &s_abort)) {
+                        failed = true;
+                        break;
+                    }
+                    mbar_expect_tx(&bar_full[stage], kBBytes);
+                    if (X3) {
+                        bulk_load(smem + stage * kGStageBytes, bsrc + (int64_t)s * 2 * kGPlane, kBBytes, &bar_full[stage]);
+                    } else { // single pass: only the high halves of the eight depth pieces
 #pragma unroll
-                    for (int pc = 0; pc < 8; ++pc)
-                        bulk_load(smem + stage * kGStageBytes + pc * 4096, bsrc + (int64_t)s * 2 * kGPlane + pc * 4096, 2048,
-                                  &bar_full[stage]);
+                        for (int pc = 0; pc < 8; ++pc)
+                            bulk_load(smem + stage * kGStageBytes + pc * 4096, bsrc + (int64_t)s * 2 * kGPlane + pc * 4096,
+                                      2048, &bar_full[stage]);
+                    }
+                    ++issued;
                 }
-                ++issued;
             }
             if (failed) { // copies still on their way into this CTA's shared memory
                 for (int x = issued > S ? issued - S : 0; x < issued; ++x) mbar_wait(&bar_full[x % S], (x / S) & 1);
@@ -226,16 +303,19 @@ __global__ void __launch_bounds__(kGThreads, 1)
     } else {
         // ---- raw a tiles: one tiled TMA load per step -----------------------------------------
         if (lane == 0) {
-            int issued = 0;
-            for (int s = 0; s < ksteps; ++s) {
-                const int stage = s % S;
-                if (s >= S && !mbar_wait_abort(&bar_raw_free[stage], ((s / S) - 1) & 1, &s_abort)) {
-                    failed = true;
-                    break;
+            int g = 0, issued = 0;
+            for (int tile = blockIdx.x; tile < tiles && !failed; tile += gridDim.x) {
+                const int row0 = (tile / ntn) * kGM;
+                for (int s = 0; s < ksteps; ++s, ++g) {
+                    const int stage = g % S;
+                    if (g >= S && !mbar_wait_abort(&bar_raw_free[stage], ((g / S) - 1) & 1, &s_abort)) {
+                        failed = true;
+                        break;
+                    }
+                    mbar_expect_tx(&bar_raw[stage], kGRawBytes);
+                    tma_load_2d(smem + kGOffRaw + stage * kGRawBytes, &a_map, s * kGK, row0, &bar_raw[stage]);
+                    ++issued;
                 }
-                mbar_expect_tx(&bar_raw[stage], kGRawBytes);
-                tma_load_2d(smem + kGOffRaw + stage * kGRawBytes, &a_map, s * kGK, row0, &bar_raw[stage]);
-                ++issued;
             }
             if (failed) {
                 for (int x = issued > S ? issued - S : 0; x < issued; ++x) mbar_wait(&bar_raw[x % S], (x / S) & 1);
@@ -243,60 +323,10 @@ __global__ void __launch_bounds__(kGThreads, 1)
         }
     }
     if (failed) s_abort = 1;
-
-    // ---- epilogue: the producer warps read the accumulators (warp w: lanes 32 (w & 3).., group's columns) ----
-    if (warp < kGWarpMma) {
-        bool ok = !failed && ksteps > 0 ? mbar_wait_abort(&bar_done, 0, &s_abort) : !failed;
-        ok = __all_sync(0xffffffffu, ok); // the TMEM loads below are warp-wide
-        failed = !ok;
-        if (failed) s_abort = 1;
-        tc_fence_after();
-        constexpr int kColsPerGroup = kGN / kGGroups;
-        const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        const int cbase = (warp >> 2) * kColsPerGroup;
-        const int row = row0 + (warp & 3) * 32 + lane;
-        float *orow = out + (int64_t)(row < M ? row : 0) * ldo;
-#pragma unroll
-        for (int q = 0; q < kColsPerGroup / 32; ++q) {
-            float v[32];
-            if (!failed && ksteps > 0) { // uniform over the warp
-                tmem_ld32(trow + cbase + q * 32, v);
-                if (X3) {
-                    float w[32];
-                    tmem_ld32(trow + kGColSmall + cbase + q * 32, w);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) v[c] += w[c];
-                } else {
-                    tc_wait_ld();
-                }
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) v[c] = 0.0f;
-            }
-            if (row < M && !failed) {
-                const int col0 = nt * kGN + cbase + q * 32;
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int col = col0 + c * 4;
-                    float4 o = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
-                    if (vec_out && col + 3 < N) {
-                        if (bias) {
-                            const float4 bb = __ldg(reinterpret_cast<const float4 *>(bias + col));
-                            o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
-                        }
-                        *reinterpret_cast<float4 *>(orow + col) = o;
-                    } else {
-                        const float e[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                        for (int x = 0; x < 4; ++x)
-                            if (col + x < N) orow[col + x] = e[x] + (bias ? bias[col + x] : 0.0f);
-                    }
-                }
-            }
-        }
-    } else if (warp == kGWarpMma && lane == 0 && failed) {
+    if (warp == kGWarpMma && lane == 0 && failed) {
+        tc_commit(&bar_done);
         mbar_wait(&bar_done, 0); // bounded: let the MMAs in flight finish before the TMEM goes back
+        mbar_wait(&bar_done, 1);
     }
     tc_fence_before();
     __syncthreads();
@@ -406,12 +436,16 @@ extern "C" int fblt_matmul(const float *a, int64_t lda, const void *packed_b, co
     CUtensorMap a_map;
     const int mst = make_a_map(&a_map, a, lda, M, K);
     if (mst != FBLT_OK) return mst;
+    int dev = 0, sms = 0;
+    FBLT_CUDA_TRY(cudaGetDevice(&dev));
+    FBLT_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const unsigned grid = (unsigned)(tiles < sms ? tiles : sms); // one persistent CTA per SM
     if (precision != FBLT_PREC_TF32)
-        gemm5_kernel<true><<<(unsigned)tiles, kGThreads, kGSmem, (cudaStream_t)stream>>>(
-            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, vec_out);
+        gemm5_kernel<true><<<grid, kGThreads, kGSmem, (cudaStream_t)stream>>>(
+            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, (int)tiles, vec_out);
     else
-        gemm5_kernel<false><<<(unsigned)tiles, kGThreads, kGSmem, (cudaStream_t)stream>>>(
-            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, vec_out);
+        gemm5_kernel<false><<<grid, kGThreads, kGSmem, (cudaStream_t)stream>>>(
+            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, (int)tiles, vec_out);
     count_launch();
     return check_launch("gemm5_kernel");
 }
