@@ -1,0 +1,50 @@
+// Multi-head self-attention block over a batch of packed sequences: the work of
+// blt_multihead_attention (models/attention.c:130-207) -- QKV projection, rotary embedding of
+// Q and K, per-head masked attention, output projection -- as three launches: the tcgen05
+// matmul, the batched attention kernel with the rotation fused into its loads and the mask
+// evaluated from the descriptor, and the matmul again. The reference runs, per sequence and
+// layer, two GEMMs, 2 x heads rotary launches, a mask build and one attention launch per head.
+#include "common.cuh"
+
+#include <math.h>
+
+extern "C" int fblt_mha_forward(const fblt_mha_desc *d, void *stream) {
+    using namespace fblt;
+    if (!d) return fail(FBLT_ERR_ARG, "mha: NULL descriptor");
+    if (d->batch < 0 || d->num_heads <= 0 || d->head_dim <= 0 || d->total_rows < 0 || d->max_len < 0)
+        return fail(FBLT_ERR_ARG, "mha: bad sizes");
+    if (d->total_rows == 0 || d->batch == 0) return FBLT_OK;
+    const int64_t E = (int64_t)d->num_heads * d->head_dim;
+    if (!d->input || !d->output || !d->packed_qkv || !d->packed_proj || !d->qkv_work || !d->combined_work || !d->cu_rows)
+        return fail(FBLT_ERR_ARG, "mha: buffers must not be NULL");
+    if (d->input_stride < E || d->output_stride < E) return fail(FBLT_ERR_ARG, "mha: row strides below embed_dim");
+
+    int st = fblt_matmul(d->input, d->input_stride, d->packed_qkv, nullptr, d->qkv_work, 3 * E, d->total_rows, E, 3 * E,
+                         d->precision, stream);
+    if (st != FBLT_OK) return st;
+
+    fblt_attn_desc a;
+    memset(&a, 0, sizeof(a));
+    a.batch = d->batch;
+    a.num_heads = d->num_heads;
+    a.head_dim = d->head_dim;
+    a.max_q = a.max_k = d->max_len;
+    a.impl = FBLT_IMPL_AUTO;
+    a.precision = d->precision;
+    a.cu_q = a.cu_k = d->cu_rows;
+    a.q = d->qkv_work;
+    a.k = d->qkv_work + E;
+    a.v = d->qkv_work + 2 * E;
+    a.q_stride = a.k_stride = a.v_stride = 3 * E;
+    a.out = d->combined_work;
+    a.out_stride = E;
+    a.scale = 1.0f / sqrtf((float)d->head_dim); // models/attention.c:137
+    a.mask = d->mask;
+    a.rope_cos = d->rope_cos;
+    a.rope_sin = d->rope_sin;
+    st = fblt_attn_forward(&a, stream);
+    if (st != FBLT_OK) return st;
+
+    return fblt_matmul(d->combined_work, E, d->packed_proj, nullptr, d->output, d->output_stride, d->total_rows, E, E,
+                       d->precision, stream);
+}

@@ -52,6 +52,20 @@ class MaskDesc(C.Structure):
     ]
 
 
+class MhaDesc(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32), ("max_len", C.c_int32),
+        ("total_rows", C.c_int64), ("cu_rows", C.c_void_p),
+        ("input", C.c_void_p), ("input_stride", C.c_int64),
+        ("packed_qkv", C.c_void_p), ("packed_proj", C.c_void_p),
+        ("output", C.c_void_p), ("output_stride", C.c_int64),
+        ("qkv_work", C.c_void_p), ("combined_work", C.c_void_p),
+        ("mask", MaskDesc),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("precision", C.c_int32), ("reserved", C.c_int32),
+    ]
+
+
 class AttnDesc(C.Structure):
     _fields_ = [
         ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32),
@@ -115,6 +129,7 @@ SYMBOLS = {
                                            C.c_void_p]),
     "fblt_matmul": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                               C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
+    "fblt_mha_forward": (C.c_int, [C.POINTER(MhaDesc), C.c_void_p]),
     "fblt_session_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int32, C.c_int32]),
     "fblt_session_destroy": (None, [C.c_void_p]),
@@ -159,7 +174,7 @@ def load() -> C.CDLL:
         fn.argtypes = args
     sizes = (C.c_size_t * 8)()
     n = lib.fblt_abi_sizes(sizes, 8)
-    want = [C.sizeof(HeadArgs), C.sizeof(PatchInfo), C.sizeof(MaskDesc), C.sizeof(AttnDesc), C.sizeof(DecodeDesc)]
+    want = [C.sizeof(HeadArgs), C.sizeof(PatchInfo), C.sizeof(MaskDesc), C.sizeof(AttnDesc), C.sizeof(DecodeDesc), C.sizeof(MhaDesc)]
     if list(sizes[:n]) != want:
         raise ImportError(f"ABI mismatch between lib.py and libfblt_attn.so: {list(sizes[:n])} vs {want}")
     _lib = lib

@@ -298,6 +298,44 @@ def matmul(a: torch.Tensor, w: PackedWeights, out: Optional[torch.Tensor] = None
     return out
 
 
+def mha_forward(x: torch.Tensor, w_qkv: PackedWeights, w_proj: PackedWeights, cu_rows: Sequence[int], num_heads: int,
+                mask: Optional[MaskConfig] = None, rope_cos: Optional[torch.Tensor] = None,
+                rope_sin: Optional[torch.Tensor] = None, precision: int = L.PREC_FP32) -> torch.Tensor:
+    """The multi-head self-attention block over packed sequences (x [rows, E]); returns [rows, E]."""
+    rows, E = int(x.shape[0]), int(x.shape[1])
+    dev = x.device
+    cu_h = np.asarray(cu_rows, dtype=np.int32)
+    batch = len(cu_h) - 1
+    mask = mask or MaskConfig()
+    d = L.MhaDesc()
+    d.batch, d.num_heads, d.head_dim = batch, num_heads, E // num_heads
+    d.max_len = int(np.max(np.diff(cu_h))) if batch else 0
+    d.total_rows = rows
+    keep = []
+
+    def dev_i32(a):
+        t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+        keep.append(t)
+        return t
+
+    d.cu_rows = dev_i32(cu_h).data_ptr()
+    out = torch.empty(rows, E, dtype=torch.float32, device=dev)
+    qkv = torch.empty(rows, 3 * E, dtype=torch.float32, device=dev)
+    comb = torch.empty(rows, E, dtype=torch.float32, device=dev)
+    d.input, d.input_stride = x.data_ptr(), x.stride(0)
+    d.packed_qkv, d.packed_proj = w_qkv.buf.data_ptr(), w_proj.buf.data_ptr()
+    d.output, d.output_stride = out.data_ptr(), out.stride(0)
+    d.qkv_work, d.combined_work = qkv.data_ptr(), comb.data_ptr()
+    tables = {name: dev_i32(arr) for name, arr in mask.host_tables(batch).items()}
+    mask.fill(d.mask, tables)
+    if rope_cos is not None:
+        d.rope_cos, d.rope_sin = rope_cos.data_ptr(), rope_sin.data_ptr()
+    d.precision = precision
+    L.check(L.load().fblt_mha_forward(C.byref(d), _stream_ptr(None)))
+    torch.cuda.current_stream().synchronize()   # the scratch tensors above die with this call
+    return out
+
+
 def unmask_step(logits: torch.Tensor, masked: torch.Tensor, tokens: torch.Tensor, strategy: int, threshold: float):
     """One unmask round over a batch of candidates. logits [batch*B, V] float32, masked/tokens
     [batch, B] uint8 (updated in place). Returns (sel [batch] int64 bit masks, conf [batch,B],

@@ -467,6 +467,39 @@ int fblt_matmul_pack_weights(const float *b, int64_t ldb, int64_t K, int64_t N, 
 int fblt_matmul(const float *a, int64_t lda, const void *packed_b, const float *bias, float *out, int64_t ldo,
                 int64_t M, int64_t K, int64_t N, int32_t precision, void *stream);
 
+/*
+ * The multi-head self-attention block of blt_multihead_attention
+ * (models/attention.h:12-26, models/attention.c:130-207) for a batch of packed
+ * sequences: qkv = input * weight_qkv; Q, K rotated when rope tables are given
+ * (position = row index within the sequence); per-head attention under `mask`
+ * with scale 1/sqrt(head_dim); output = combined * weight_proj. Weights are the
+ * fblt_matmul_pack_weights images of weight_qkv [E, 3E] and weight_proj [E, E].
+ * qkv_work [total_rows, 3E] and combined_work [total_rows, E] are caller-provided
+ * scratch (qkv_work holds the un-rotated projection afterwards). Three launches.
+ * total_rows is the host copy of cu_rows[batch]; max_len bounds the sequence
+ * lengths. All pointers device.
+ */
+typedef struct {
+    int32_t batch, num_heads, head_dim, max_len;
+    int64_t total_rows;
+    const int32_t *cu_rows; /* [batch + 1] */
+    const float *input;
+    int64_t input_stride;
+    const void *packed_qkv;
+    const void *packed_proj;
+    float *output;
+    int64_t output_stride;
+    float *qkv_work;
+    float *combined_work;
+    fblt_mask_desc mask; /* is_causal / sliding_window / documents of blt_attention_config.mask_config */
+    const float *rope_cos; /* NULL: no rotary embedding (use_rope = false) */
+    const float *rope_sin;
+    int32_t precision; /* FBLT_PREC_FP32 or FBLT_PREC_TF32, for the matmuls and the attention */
+    int32_t reserved;
+} fblt_mha_desc;
+
+int fblt_mha_forward(const fblt_mha_desc *desc, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* host-buffer sessions (what a host-side caller with no device memory uses) */
 /* ------------------------------------------------------------------------ */
@@ -539,7 +572,7 @@ int fblt_tcgen05_error(void);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t fblt_launch_count(void);
 /* sizeof of {fblt_head_args, fblt_patch_info, fblt_mask_desc, fblt_attn_desc,
- * fblt_decode_desc}, for bindings that re-declare the structs. Returns the count. */
+ * fblt_decode_desc, fblt_mha_desc}, for bindings that re-declare the structs. Returns the count. */
 size_t fblt_abi_sizes(size_t *out, size_t cap);
 
 #ifdef __cplusplus

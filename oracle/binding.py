@@ -142,6 +142,23 @@ def matmul(a: np.ndarray, b: np.ndarray, use_ref: bool = False) -> np.ndarray:
     return out
 
 
+def ref_multihead_attention(x: np.ndarray, w_qkv: np.ndarray, w_proj: np.ndarray, num_heads: int, *, is_causal: bool,
+                            use_rope: bool, theta: float = 500000.0, window: int = 0, doc_boundaries=None) -> np.ndarray:
+    """blt_multihead_attention of the reference on the CPU, one sequence x [T, E]."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w_qkv = np.ascontiguousarray(w_qkv, dtype=np.float32)
+    w_proj = np.ascontiguousarray(w_proj, dtype=np.float32)
+    out = np.empty_like(x)
+    docs = np.ascontiguousarray(doc_boundaries, dtype=np.uint64) if doc_boundaries is not None and len(doc_boundaries) else None
+    fn = ref().ref_multihead_attention
+    fn.argtypes = [c_f_p, c_f_p, c_f_p, c_f_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_float,
+                   C.c_size_t, c_sz_p, C.c_size_t]
+    fn.restype = None
+    fn(_fp(x), _fp(w_qkv), _fp(w_proj), _fp(out), x.shape[0], x.shape[1], num_heads, int(is_causal), int(use_rope),
+       theta, window, docs.ctypes.data_as(c_sz_p) if docs is not None else None, 0 if docs is None else len(docs) + 1)
+    return out
+
+
 def host_cores() -> int:
     try:
         return len(os.sched_getaffinity(0))

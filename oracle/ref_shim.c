@@ -23,6 +23,7 @@
 #include "infer/block_generation.h"
 #include "infer/kv_cache.h"
 #include "infer/self_speculation.h"
+#include "models/attention.h"
 #include "models/patcher.h"
 #include "ops/attn_core.h"
 #include "ops/mask_builder.h"
@@ -170,6 +171,40 @@ void ref_matmul(const float *a, const float *b, float *out, size_t m, size_t k, 
     blt_tensor_view_2d(&bt, (void *)b, k, n, BLT_BACKEND_CPU);
     blt_tensor_view_2d(&ot, out, m, n, BLT_BACKEND_CPU);
     blt_matmul(&at, &bt, &ot);
+}
+
+/* The reference's multi-head attention block on the CPU for one sequence. window > 0 or
+ * num_docs > 0 go through a blt_mask_config (which then carries is_causal), as the callers in
+ * models/local_common.c do. */
+void ref_multihead_attention(const float *input, const float *w_qkv, const float *w_proj, float *output, size_t seq_len,
+                             size_t embed_dim, size_t num_heads, int is_causal, int use_rope, float rope_theta,
+                             size_t window, const size_t *doc_boundaries, size_t num_docs) {
+    const size_t work = seq_len * (4 * embed_dim + 2 * seq_len + 8 * (embed_dim / num_heads) + 64) * sizeof(float) +
+                        seq_len * seq_len * sizeof(float) + (1u << 20);
+    blt_arena *arena = blt_arena_create(work, BLT_BACKEND_CPU);
+    blt_tensor in, wq, wp, out;
+    blt_tensor_view_2d(&in, (void *)input, seq_len, embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&wq, (void *)w_qkv, embed_dim, 3 * embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&wp, (void *)w_proj, embed_dim, embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&out, output, seq_len, embed_dim, BLT_BACKEND_CPU);
+    blt_mask_config mc;
+    memset(&mc, 0, sizeof(mc));
+    mc.seq_len_q = mc.seq_len_kv = seq_len;
+    mc.sliding_window = window;
+    mc.doc_boundaries = doc_boundaries;
+    mc.num_docs = num_docs;
+    mc.is_causal = is_causal != 0;
+    blt_attention_config cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.embed_dim = embed_dim;
+    cfg.num_heads = num_heads;
+    cfg.head_dim = embed_dim / num_heads;
+    cfg.is_causal = is_causal != 0;
+    cfg.use_rope = use_rope != 0;
+    cfg.rope_theta = rope_theta;
+    cfg.mask_config = (window > 0 || num_docs > 0) ? &mc : NULL;
+    blt_multihead_attention(&in, &wq, &wp, &out, &cfg, arena);
+    blt_arena_destroy(arena);
 }
 
 void ref_rope_precompute(size_t max_seq_len, float theta, size_t head_dim, float *cos_out, float *sin_out) {
