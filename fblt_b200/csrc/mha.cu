@@ -48,3 +48,53 @@ extern "C" int fblt_mha_forward(const fblt_mha_desc *d, void *stream) {
     return fblt_matmul(d->combined_work, E, d->packed_proj, nullptr, d->output, d->output_stride, d->total_rows, E, E,
                        d->precision, stream);
 }
+
+// The cross-attention block of blt_cross_attention_forward (models/cross_attention.c:98-157):
+// Q from query_in, K and V from kv_in (one matmul against [weight_k | weight_v]), masked
+// attention under the patch rule of the descriptor, output projection. Four launches.
+extern "C" int fblt_cross_attention_forward(const fblt_cross_desc *d, void *stream) {
+    using namespace fblt;
+    if (!d) return fail(FBLT_ERR_ARG, "cross: NULL descriptor");
+    if (d->batch < 0 || d->num_heads <= 0 || d->head_dim <= 0 || d->total_q_rows < 0 || d->total_k_rows < 0)
+        return fail(FBLT_ERR_ARG, "cross: bad sizes");
+    if (d->total_q_rows == 0 || d->batch == 0) return FBLT_OK;
+    const int64_t E = (int64_t)d->num_heads * d->head_dim;
+    if (!d->query_in || !d->kv_in || !d->output || !d->packed_q || !d->packed_kv || !d->packed_proj || !d->q_work ||
+        !d->kv_work || !d->combined_work || !d->cu_q || !d->cu_k)
+        return fail(FBLT_ERR_ARG, "cross: buffers must not be NULL");
+    if (d->query_stride < E || d->kv_stride < E || d->output_stride < E)
+        return fail(FBLT_ERR_ARG, "cross: row strides below embed_dim");
+
+    int st = fblt_matmul(d->query_in, d->query_stride, d->packed_q, nullptr, d->q_work, E, d->total_q_rows, E, E, d->precision,
+                         stream);
+    if (st != FBLT_OK) return st;
+    st = fblt_matmul(d->kv_in, d->kv_stride, d->packed_kv, nullptr, d->kv_work, 2 * E, d->total_k_rows, E, 2 * E,
+                     d->precision, stream);
+    if (st != FBLT_OK) return st;
+
+    fblt_attn_desc a;
+    memset(&a, 0, sizeof(a));
+    a.batch = d->batch;
+    a.num_heads = d->num_heads;
+    a.head_dim = d->head_dim;
+    a.max_q = d->max_q;
+    a.max_k = d->max_k;
+    a.impl = FBLT_IMPL_AUTO;
+    a.precision = d->precision;
+    a.cu_q = d->cu_q;
+    a.cu_k = d->cu_k;
+    a.q = d->q_work;
+    a.q_stride = E;
+    a.k = d->kv_work;
+    a.v = d->kv_work + E;
+    a.k_stride = a.v_stride = 2 * E;
+    a.out = d->combined_work;
+    a.out_stride = E;
+    a.scale = 1.0f / sqrtf((float)d->head_dim); // models/cross_attention.c:112
+    a.mask = d->mask;
+    st = fblt_attn_forward(&a, stream);
+    if (st != FBLT_OK) return st;
+
+    return fblt_matmul(d->combined_work, E, d->packed_proj, nullptr, d->output, d->output_stride, d->total_q_rows, E, E,
+                       d->precision, stream);
+}

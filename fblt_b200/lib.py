@@ -66,6 +66,21 @@ class MhaDesc(C.Structure):
     ]
 
 
+class CrossDesc(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32), ("max_q", C.c_int32),
+        ("max_k", C.c_int32), ("precision", C.c_int32),
+        ("total_q_rows", C.c_int64), ("total_k_rows", C.c_int64),
+        ("cu_q", C.c_void_p), ("cu_k", C.c_void_p),
+        ("query_in", C.c_void_p), ("query_stride", C.c_int64),
+        ("kv_in", C.c_void_p), ("kv_stride", C.c_int64),
+        ("packed_q", C.c_void_p), ("packed_kv", C.c_void_p), ("packed_proj", C.c_void_p),
+        ("output", C.c_void_p), ("output_stride", C.c_int64),
+        ("q_work", C.c_void_p), ("kv_work", C.c_void_p), ("combined_work", C.c_void_p),
+        ("mask", MaskDesc),
+    ]
+
+
 class AttnDesc(C.Structure):
     _fields_ = [
         ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32),
@@ -130,6 +145,7 @@ SYMBOLS = {
     "fblt_matmul": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                               C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "fblt_mha_forward": (C.c_int, [C.POINTER(MhaDesc), C.c_void_p]),
+    "fblt_cross_attention_forward": (C.c_int, [C.POINTER(CrossDesc), C.c_void_p]),
     "fblt_session_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int32, C.c_int32]),
     "fblt_session_destroy": (None, [C.c_void_p]),
@@ -174,7 +190,7 @@ def load() -> C.CDLL:
         fn.argtypes = args
     sizes = (C.c_size_t * 8)()
     n = lib.fblt_abi_sizes(sizes, 8)
-    want = [C.sizeof(HeadArgs), C.sizeof(PatchInfo), C.sizeof(MaskDesc), C.sizeof(AttnDesc), C.sizeof(DecodeDesc), C.sizeof(MhaDesc)]
+    want = [C.sizeof(HeadArgs), C.sizeof(PatchInfo), C.sizeof(MaskDesc), C.sizeof(AttnDesc), C.sizeof(DecodeDesc), C.sizeof(MhaDesc), C.sizeof(CrossDesc)]
     if list(sizes[:n]) != want:
         raise ImportError(f"ABI mismatch between lib.py and libfblt_attn.so: {list(sizes[:n])} vs {want}")
     _lib = lib

@@ -336,6 +336,44 @@ def mha_forward(x: torch.Tensor, w_qkv: PackedWeights, w_proj: PackedWeights, cu
     return out
 
 
+def cross_attention_forward(query_in: torch.Tensor, kv_in: torch.Tensor, w_q: PackedWeights, w_kv: PackedWeights,
+                            w_proj: PackedWeights, cu_q: Sequence[int], cu_k: Sequence[int], num_heads: int,
+                            mask: MaskConfig, precision: int = L.PREC_FP32) -> torch.Tensor:
+    """The cross-attention block over packed sequences; w_kv packs [weight_k | weight_v] ([E, 2E])."""
+    E = int(query_in.shape[1])
+    dev = query_in.device
+    cu_q_h, cu_k_h = np.asarray(cu_q, dtype=np.int32), np.asarray(cu_k, dtype=np.int32)
+    batch = len(cu_q_h) - 1
+    d = L.CrossDesc()
+    d.batch, d.num_heads, d.head_dim = batch, num_heads, E // num_heads
+    d.max_q = int(np.max(np.diff(cu_q_h))) if batch else 0
+    d.max_k = int(np.max(np.diff(cu_k_h))) if batch else 0
+    d.precision = precision
+    d.total_q_rows, d.total_k_rows = int(query_in.shape[0]), int(kv_in.shape[0])
+    keep = []
+
+    def dev_i32(a):
+        t = torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+        keep.append(t)
+        return t
+
+    d.cu_q, d.cu_k = dev_i32(cu_q_h).data_ptr(), dev_i32(cu_k_h).data_ptr()
+    out = torch.empty(d.total_q_rows, E, dtype=torch.float32, device=dev)
+    qw = torch.empty(d.total_q_rows, E, dtype=torch.float32, device=dev)
+    kvw = torch.empty(d.total_k_rows, 2 * E, dtype=torch.float32, device=dev)
+    comb = torch.empty(d.total_q_rows, E, dtype=torch.float32, device=dev)
+    d.query_in, d.query_stride = query_in.data_ptr(), query_in.stride(0)
+    d.kv_in, d.kv_stride = kv_in.data_ptr(), kv_in.stride(0)
+    d.packed_q, d.packed_kv, d.packed_proj = w_q.buf.data_ptr(), w_kv.buf.data_ptr(), w_proj.buf.data_ptr()
+    d.output, d.output_stride = out.data_ptr(), out.stride(0)
+    d.q_work, d.kv_work, d.combined_work = qw.data_ptr(), kvw.data_ptr(), comb.data_ptr()
+    tables = {name: dev_i32(arr) for name, arr in mask.host_tables(batch).items()}
+    mask.fill(d.mask, tables)
+    L.check(L.load().fblt_cross_attention_forward(C.byref(d), _stream_ptr(None)))
+    torch.cuda.current_stream().synchronize()   # the scratch tensors above die with this call
+    return out
+
+
 def unmask_step(logits: torch.Tensor, masked: torch.Tensor, tokens: torch.Tensor, strategy: int, threshold: float):
     """One unmask round over a batch of candidates. logits [batch*B, V] float32, masked/tokens
     [batch, B] uint8 (updated in place). Returns (sel [batch] int64 bit masks, conf [batch,B],

@@ -500,6 +500,42 @@ typedef struct {
 
 int fblt_mha_forward(const fblt_mha_desc *desc, void *stream);
 
+/*
+ * The cross-attention block of blt_cross_attention_forward
+ * (models/cross_attention.h:54-56, models/cross_attention.c:98-157) for a batch:
+ * Q = query_in * weight_q; K, V = kv_in * [weight_k | weight_v]; attention under
+ * `mask` (the patch rules FBLT_GROUP_PATCH_ENC / _DEC replace the group-id
+ * arrays), no rotary embedding; output = combined * weight_proj. query_in and
+ * kv_in are the split-form views [rows, E] the reference builds for its split
+ * modes. packed_kv is one buffer of fblt_matmul_packed_bytes(E, 2E) bytes: the
+ * packed weight_k followed by the packed weight_v (packing [E, E] twice into
+ * the two halves equals packing the concatenation). Scratch: q_work
+ * [total_q_rows, E], kv_work [total_k_rows, 2E], combined_work [total_q_rows, E].
+ * All pointers device.
+ */
+typedef struct {
+    int32_t batch, num_heads, head_dim, max_q, max_k;
+    int32_t precision;
+    int64_t total_q_rows, total_k_rows;
+    const int32_t *cu_q; /* [batch + 1] */
+    const int32_t *cu_k;
+    const float *query_in;
+    int64_t query_stride;
+    const float *kv_in;
+    int64_t kv_stride;
+    const void *packed_q;
+    const void *packed_kv;
+    const void *packed_proj;
+    float *output;
+    int64_t output_stride;
+    float *q_work;
+    float *kv_work;
+    float *combined_work;
+    fblt_mask_desc mask;
+} fblt_cross_desc;
+
+int fblt_cross_attention_forward(const fblt_cross_desc *desc, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* host-buffer sessions (what a host-side caller with no device memory uses) */
 /* ------------------------------------------------------------------------ */
@@ -572,7 +608,7 @@ int fblt_tcgen05_error(void);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t fblt_launch_count(void);
 /* sizeof of {fblt_head_args, fblt_patch_info, fblt_mask_desc, fblt_attn_desc,
- * fblt_decode_desc, fblt_mha_desc}, for bindings that re-declare the structs. Returns the count. */
+ * fblt_decode_desc, fblt_mha_desc, fblt_cross_desc}, for bindings that re-declare the structs. Returns the count. */
 size_t fblt_abi_sizes(size_t *out, size_t cap);
 
 #ifdef __cplusplus

@@ -159,6 +159,18 @@ def ref_multihead_attention(x: np.ndarray, w_qkv: np.ndarray, w_proj: np.ndarray
     return out
 
 
+def ref_cross_attention(query_in, kv_in, wq, wk, wv, wp, num_heads: int, q_groups, k_groups) -> np.ndarray:
+    """blt_cross_attention_forward of the reference on the CPU, one sequence, group-id mask."""
+    arrs = [np.ascontiguousarray(a, dtype=np.float32) for a in (query_in, kv_in, wq, wk, wv, wp)]
+    out = np.empty_like(arrs[0])
+    qg, kg = _sz(q_groups), _sz(k_groups)
+    fn = ref().ref_cross_attention
+    fn.argtypes = [c_f_p] * 7 + [C.c_size_t] * 4 + [c_sz_p, c_sz_p]
+    fn.restype = None
+    fn(*[_fp(a) for a in arrs], _fp(out), arrs[0].shape[0], arrs[1].shape[0], arrs[0].shape[1], num_heads, _szp(qg), _szp(kg))
+    return out
+
+
 def host_cores() -> int:
     try:
         return len(os.sched_getaffinity(0))

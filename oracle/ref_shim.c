@@ -24,6 +24,7 @@
 #include "infer/kv_cache.h"
 #include "infer/self_speculation.h"
 #include "models/attention.h"
+#include "models/cross_attention.h"
 #include "models/patcher.h"
 #include "ops/attn_core.h"
 #include "ops/mask_builder.h"
@@ -204,6 +205,38 @@ void ref_multihead_attention(const float *input, const float *w_qkv, const float
     cfg.rope_theta = rope_theta;
     cfg.mask_config = (window > 0 || num_docs > 0) ? &mc : NULL;
     blt_multihead_attention(&in, &wq, &wp, &out, &cfg, arena);
+    blt_arena_destroy(arena);
+}
+
+/* The reference's cross-attention block on the CPU for one sequence, no split (views already
+ * in split form), group-id mask as its callers build it. */
+void ref_cross_attention(const float *query_in, const float *kv_in, const float *wq, const float *wk, const float *wv,
+                         const float *wp, float *output, size_t nq, size_t nk, size_t embed_dim, size_t num_heads,
+                         const size_t *q_groups, const size_t *k_groups) {
+    const size_t work = (2 * nq + 2 * nk) * embed_dim * sizeof(float) + 3 * nq * nk * sizeof(float) + (1u << 20);
+    blt_arena *arena = blt_arena_create(work, BLT_BACKEND_CPU);
+    blt_tensor q, kv, tq, tk, tv, tp, out;
+    blt_tensor_view_2d(&q, (void *)query_in, nq, embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&kv, (void *)kv_in, nk, embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&tq, (void *)wq, embed_dim, embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&tk, (void *)wk, embed_dim, embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&tv, (void *)wv, embed_dim, embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&tp, (void *)wp, embed_dim, embed_dim, BLT_BACKEND_CPU);
+    blt_tensor_view_2d(&out, output, nq, embed_dim, BLT_BACKEND_CPU);
+    blt_cross_attention_weights w = {&tq, &tk, &tv, &tp};
+    blt_mask_config mc;
+    memset(&mc, 0, sizeof(mc));
+    mc.seq_len_q = nq;
+    mc.seq_len_kv = nk;
+    mc.query_group_ids = q_groups;
+    mc.kv_group_ids = k_groups;
+    mc.bidirectional_within_group = true;
+    blt_cross_attention_config cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.embed_dim = embed_dim;
+    cfg.num_heads = num_heads;
+    cfg.mask_config = &mc;
+    blt_cross_attention_forward(&q, &kv, &w, &out, &cfg, arena);
     blt_arena_destroy(arena);
 }
 

@@ -54,3 +54,51 @@ def test_mha_block_matches_reference(cuda_lib):
 def test_mha_block_tf32_mode(cuda_lib):
     got, want = run_case(256, 4, [128, 77], 4, use_rope=True, precision=L.PREC_TF32)
     assert_close(got, want, "mha tf32", atol=5e-3, rtol=2e-2)     # single-pass TF32 in all three stages
+
+
+def packed_kv(wk: np.ndarray, wv: np.ndarray) -> ops.PackedWeights:
+    """[weight_k | weight_v] as one packed [E, 2E] weight."""
+    return ops.PackedWeights(torch.from_numpy(np.ascontiguousarray(np.concatenate([wk, wv], axis=1))).cuda())
+
+
+@pytest.mark.parametrize("direction", ["enc", "dec"])
+def test_cross_attention_block_matches_reference(cuda_lib, direction):
+    """Encoder (patch queries over their own bytes) and decoder (byte queries over their latent)
+    cross-attention blocks against blt_cross_attention_forward run on the CPU with the
+    group-id arrays its callers build (models/local_encoder.c:70-74, models/local_decoder.c:82-94)."""
+    if not ob.have_ref():
+        pytest.skip("reference object code not built")
+    from fblt_b200 import synth
+    E, H = 256, 4
+    rng = np.random.default_rng(21)
+    nbytes = [200, 64, 17]
+    bounds = [synth.bounds_from_lengths(synth.geometric_patches(41, b, n)) for b, n in enumerate(nbytes)]
+    P = [len(x) - 1 for x in bounds]
+    wq, wk, wv, wp = ((rng.standard_normal((E, E)) / np.sqrt(E)).astype(np.float32) for _ in range(4))
+    if direction == "enc":
+        q_rows, k_rows = P, nbytes
+        mask = MaskConfig(group_rule=L.GROUP_PATCH_ENC, patch_bounds=bounds)
+    else:
+        q_rows, k_rows = nbytes, P
+        mask = MaskConfig(group_rule=L.GROUP_PATCH_DEC, patch_bounds=bounds, trailing_closed=[1, 0, 1])
+    cu_q = np.concatenate([[0], np.cumsum(q_rows)]).astype(np.int32)
+    cu_k = np.concatenate([[0], np.cumsum(k_rows)]).astype(np.int32)
+    xq = rng.standard_normal((int(cu_q[-1]), E)).astype(np.float32)
+    xk = rng.standard_normal((int(cu_k[-1]), E)).astype(np.float32)
+    want = np.zeros_like(xq)
+    for b in range(len(nbytes)):
+        _, byte_patch = ob.patch_group_ids(bounds[b], use_ref=True)
+        if direction == "enc":
+            qg, kg = np.arange(P[b]), byte_patch[:nbytes[b]]
+        else:
+            qg = np.array([ob.latent_at(bounds[b], i, use_ref=True) for i in range(nbytes[b])])
+            if mask.trailing_closed[b]:
+                qg[-1] = P[b] - 1
+            kg = np.arange(P[b])
+        want[cu_q[b]:cu_q[b + 1]] = ob.ref_cross_attention(xq[cu_q[b]:cu_q[b + 1]], xk[cu_k[b]:cu_k[b + 1]], wq, wk, wv, wp,
+                                                           H, qg, kg)
+    got = ops.cross_attention_forward(torch.from_numpy(xq).cuda(), torch.from_numpy(xk).cuda(),
+                                      ops.PackedWeights(torch.from_numpy(wq).cuda()), packed_kv(wk, wv),
+                                      ops.PackedWeights(torch.from_numpy(wp).cuda()), cu_q, cu_k, H, mask)
+    assert L.load().fblt_tcgen05_error() == 0
+    assert_close(got.cpu().numpy(), want, f"cross block {direction}")
