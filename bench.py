@@ -222,7 +222,7 @@ def main():
     ap.add_argument("--cpu-prefill-seqs", type=int, default=512)
     ap.add_argument("--cpu-decode-seqs", type=int, default=128)
     ap.add_argument("--cpu-decode-steps", type=int, default=8)
-    ap.add_argument("--workload", default="scaled", choices=["scaled", "configs", "matmul"],
+    ap.add_argument("--workload", default="scaled", choices=["scaled", "configs", "matmul", "blocks"],
                     help="scaled = the headline job (one JSON line); configs = one line per small benchmark "
                          "configuration (byte self-attention, patch attention, cross-attention, cache decode)")
     ap.add_argument("--matmul-small", action="store_true",
@@ -246,6 +246,9 @@ def main():
         return
     if args.workload == "matmul":
         run_matmul(args)
+        return
+    if args.workload == "blocks":
+        run_blocks(args)
         return
 
     import torch
@@ -558,6 +561,60 @@ def run_matmul(args):
                                     "max_abs_err_vs_f64": float(np.abs(cpu_out - exact.cpu().numpy()).max()), "cores": 1},
                   "l2": "operands larger than L2 for the prefill shapes; decode-step shapes fit in L2"})
         del a, b, w, out
+
+
+def run_blocks(args):
+    """The whole multi-head self-attention block (QKV matmul, rotary attention, output matmul;
+    fblt_mha_forward) on the patch-transformer shape of the headline job: 2048 sequences with the
+    config-5 patch structure, E = 1024, 16 heads. One line with the device time of the three
+    launches, and the reference's own blt_multihead_attention on the CPU for a few sequences."""
+    import torch
+    from fblt_b200 import lib as L
+    from fblt_b200 import ops, workloads
+    from fblt_b200.ops import MaskConfig
+    from oracle import binding as ob
+    H, hd = 16, 64
+    E = H * hd
+    case = workloads.patch_self_attention(4, args.batch, H, "c5_prefill", with_tensors=False)
+    cu = case.cu_q
+    rows = int(cu[-1])
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(rows, E, device="cuda", generator=g)
+    w_qkv = torch.randn(E, 3 * E, device="cuda", generator=g) / 32.0
+    w_proj = torch.randn(E, E, device="cuda", generator=g) / 32.0
+    pq, pp = ops.PackedWeights(w_qkv), ops.PackedWeights(w_proj)
+    cs, sn = ob.rope_tables(int(np.max(np.diff(cu))), hd, use_ref=ob.have_ref())
+    cs_d, sn_d = torch.from_numpy(cs).cuda(), torch.from_numpy(sn).cuda()
+    mask = MaskConfig(is_causal=True)
+    fn = lambda: ops.mha_forward(x, pq, pp, cu, H, mask, rope_cos=cs_d, rope_sin=sn_d)
+    for _ in range(max(3, args.warmup)):
+        out = fn()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = max(args.steps, 5)
+    torch.cuda.synchronize()
+    t0.record()
+    for _ in range(n):
+        out = fn()
+    t1.record()
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1) / n
+    assert L.load().fblt_tcgen05_error() == 0
+    flops = 2.0 * rows * E * 3 * E + 2.0 * rows * E * E
+    line = {"workload": "mha_block_c5_prefill", "sequences": args.batch, "rows": rows, "embed": E, "heads": H,
+            "ms": ms, "rows_per_s": rows / ms * 1e3, "matmul_TFLOP/s_equivalent": flops / ms / 1e9,
+            "launches": 3, "l2": "operands larger than L2"}
+    if ob.have_ref():
+        nseq = 4
+        xs, wq, wp = x[: int(cu[nseq])].cpu().numpy(), w_qkv.cpu().numpy(), w_proj.cpu().numpy()
+        t = time.perf_counter()
+        err = 0.0
+        for b in range(nseq):
+            want = ob.ref_multihead_attention(xs[cu[b]:cu[b + 1]], wq, wp, H, is_causal=True, use_rope=True)
+            err = max(err, float(np.abs(out[cu[b]:cu[b + 1]].cpu().numpy() - want).max()))
+        cpu_s = time.perf_counter() - t
+        line["cpu_reference"] = {"sequences": nseq, "rows": int(cu[nseq]), "seconds": cpu_s,
+                                 "rows_per_s": int(cu[nseq]) / cpu_s, "cores": 1, "max_abs_err_vs_gpu": err}
+    emit(line)
 
 
 # dram bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in
