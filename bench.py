@@ -264,6 +264,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # one process per GPU: keep each rank and its pinned host buffers on the GPU's own NUMA node
+    # (the CPU baseline leg of a single-GPU run gets the full affinity mask back)
+    full_affinity = os.sched_getaffinity(0)
+    numa = shard.bind_to_device_numa_node(local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
@@ -411,6 +415,7 @@ def main():
 
     # ---- CPU baseline on a bounded sample of the same tensors (rank 0, one GPU) ----
     cpu = None
+    os.sched_setaffinity(0, full_affinity)
     if rank == 0 and world == 1 and not args.no_cpu:
         cpu = run_cpu_baseline(args, torch, qkv, cu, kc, vc, qn, kn, vn, out_p,
                                out_d2[(args.warmup + args.steps - 1) % len(out_d2)], total_rows)
@@ -420,7 +425,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(args, total_rows),
-            "roofline": roofline, "prefill": prefill, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "roofline": roofline, "prefill": prefill, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "host_binding": numa,
             "job_bytes": total_bytes,
         }
         emit(line)

@@ -7,7 +7,9 @@ helpers are backend-agnostic (NCCL on GPUs, gloo in the CPU tests).
 """
 from __future__ import annotations
 
-from typing import List, Tuple
+import os
+import subprocess
+from typing import List, Optional, Set, Tuple
 
 import torch
 import torch.distributed as dist
@@ -52,3 +54,56 @@ def gather_rows(local: torch.Tensor, rows_per_rank: List[int], group=None, padde
 def unpad(gathered: torch.Tensor, rows_per_rank: List[int]) -> torch.Tensor:
     """Concatenate the valid rows of a gather_rows() result in rank order."""
     return torch.cat([gathered[r, :n] for r, n in enumerate(rows_per_rank)], dim=0)
+
+
+def parse_cpulist(text: str) -> Set[int]:
+    """'0-3,8,10-11' -> {0, 1, 2, 3, 8, 10, 11} (the format of /sys/devices/system/node/*/cpulist)."""
+    cpus: Set[int] = set()
+    for part in text.strip().split(","):
+        part = part.strip()
+        if not part:
+            continue
+        if "-" in part:
+            lo, hi = part.split("-", 1)
+            cpus.update(range(int(lo), int(hi) + 1))
+        else:
+            cpus.add(int(part))
+    return cpus
+
+
+def _pci_address(device_index: int) -> Optional[str]:
+    props = torch.cuda.get_device_properties(device_index)
+    if all(hasattr(props, a) for a in ("pci_domain_id", "pci_bus_id", "pci_device_id")):
+        return f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+    try:
+        out = subprocess.run(["nvidia-smi", f"--id={device_index}", "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip()
+        return out[-12:].lower() if out else None  # '00000000:1B:00.0' -> '0000:1b:00.0'
+    except (OSError, subprocess.SubprocessError):
+        return None
+
+
+def bind_to_device_numa_node(device_index: int) -> dict:
+    """Restrict this process to the CPUs of the NUMA node its GPU is attached to.
+
+    Pinned host buffers allocated afterwards are first touched on that node, and the thread that
+    issues the copies runs there, so host<->device traffic of a rank does not cross the socket
+    interconnect. Every rank of a one-process-per-GPU job calls this before it allocates host
+    memory. Returns what was done; does nothing when the topology is not exposed."""
+    info = {"numa_node": None, "cpus": None}
+    try:
+        addr = _pci_address(device_index)
+        if not addr:
+            return info
+        node = int(open(f"/sys/bus/pci/devices/{addr}/numa_node").read().strip())
+        if node < 0:
+            return info
+        cpus = parse_cpulist(open(f"/sys/devices/system/node/node{node}/cpulist").read())
+        target = cpus & os.sched_getaffinity(0)
+        if not target:
+            return info
+        os.sched_setaffinity(0, target)
+        info.update(numa_node=node, cpus=len(target))
+    except (OSError, ValueError):
+        pass
+    return info

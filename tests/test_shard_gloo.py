@@ -59,3 +59,10 @@ def test_gather_rows_world_size_2():
         assert p.exitcode == 0
     assert all(ok for _, ok, _ in results)
     assert results[0][2] == results[1][2] and len(set(results[0][2])) == 2   # unequal blocks were exercised
+
+
+def test_parse_cpulist():
+    from fblt_b200 import shard
+    assert shard.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert shard.parse_cpulist("5") == {5}
+    assert shard.parse_cpulist("") == set()
