@@ -309,7 +309,12 @@ def main():
         max_rows = max(rows_per_rank)
         pad_p = torch.zeros((max_rows, E), device=dev)
         gath_p = torch.empty((world, max_rows, E), device=dev)
-        gath_d = torch.empty((world, args.decode_steps * B * N_NEW, E), device=dev)
+        # the decode rows of a step travel in chunks of a quarter of the decode launches, so that
+        # only the last chunk's gather is still under way when the step's compute ends
+        n_chunks = 4 if args.decode_steps % 4 == 0 else 1
+        chunk_steps = args.decode_steps // n_chunks
+        gath_d = [torch.empty((world, chunk_steps * B * N_NEW, E), device=dev) for _ in range(n_chunks)]
+        ev_chunk = [torch.cuda.Event() for _ in range(n_chunks)]
         equal = len({e - b for b, e in ranges}) == 1
         assert equal, "decode gather assumes equal sequence counts per rank"
 
@@ -340,13 +345,16 @@ def main():
             dec_t0[it].record(main_stream)
             for t in range(args.decode_steps):
                 ops.attn_decode(dec2[buf][t], ws, main_stream)
+                if world > 1 and (t + 1) % chunk_steps == 0:   # this chunk's rows travel while decode goes on
+                    c = t // chunk_steps
+                    ev_chunk[c].record(main_stream)
+                    comm_stream.wait_event(ev_chunk[c])
+                    with torch.cuda.stream(comm_stream):
+                        dist.all_gather_into_tensor(gath_d[c].view(-1, E),
+                                                    out_d2[buf][c * chunk_steps:(c + 1) * chunk_steps].view(-1, E))
+                        if c == n_chunks - 1:
+                            ev_gathered[buf].record(comm_stream)
             dec_t1[it].record(main_stream)
-            if world > 1:   # decode rows travel while the next step computes
-                ev_dec_done[buf].record(main_stream)
-                comm_stream.wait_event(ev_dec_done[buf])
-                with torch.cuda.stream(comm_stream):
-                    dist.all_gather_into_tensor(gath_d.view(-1, E), out_d2[buf].view(-1, E))
-                    ev_gathered[buf].record(comm_stream)
 
     def barrier():
         if world > 1:
