@@ -185,7 +185,8 @@ extern "C" int32_t fblt_patch_latent_at(const int32_t *bounds, int32_t num_patch
 // sizeof of every ABI struct, for bindings that re-declare them (ctypes, cgo).
 extern "C" size_t fblt_abi_sizes(size_t *out, size_t cap) {
     const size_t v[] = {sizeof(fblt_head_args), sizeof(fblt_patch_info), sizeof(fblt_mask_desc), sizeof(fblt_attn_desc),
-                        sizeof(fblt_decode_desc), sizeof(fblt_mha_desc), sizeof(fblt_cross_desc)};
+                        sizeof(fblt_decode_desc), sizeof(fblt_mha_desc), sizeof(fblt_cross_desc),
+                        sizeof(fblt_kv_step_desc)};
     const size_t n = sizeof(v) / sizeof(v[0]);
     for (size_t i = 0; i < n && i < cap; ++i) out[i] = v[i];
     return n;

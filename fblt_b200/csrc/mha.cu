@@ -98,3 +98,57 @@ extern "C" int fblt_cross_attention_forward(const fblt_cross_desc *d, void *stre
     return fblt_matmul(d->combined_work, E, d->packed_proj, nullptr, d->output, d->output_stride, d->total_q_rows, E, E,
                        d->precision, stream);
 }
+
+// The self-attention part of one cache-aware decode step (infer/kv_cache.c:338-396) for a batch:
+// qkv = rows * weight_qkv; Q and K rotated with position base + r; K / V written through to the
+// cache at rows base .. base + n; attention of the n new rows over the cache; output projection.
+// The reference does this per layer with 5 strided copies and 2 rotary launches per head and one
+// operator launch per head; here it is the matmul, the decode kernel (rotation and write-through
+// fused) and the matmul again.
+extern "C" int fblt_kv_self_attention_step(const fblt_kv_step_desc *d, void *stream) {
+    using namespace fblt;
+    if (!d) return fail(FBLT_ERR_ARG, "kv step: NULL descriptor");
+    if (d->batch < 0 || d->num_heads <= 0 || d->head_dim <= 0 || d->n_new < 1)
+        return fail(FBLT_ERR_ARG, "kv step: bad sizes");
+    if (d->batch == 0) return FBLT_OK;
+    const int64_t E = (int64_t)d->num_heads * d->head_dim, rows = (int64_t)d->batch * d->n_new;
+    if (!d->input || !d->output || !d->packed_qkv || !d->packed_proj || !d->qkv_work || !d->combined_work)
+        return fail(FBLT_ERR_ARG, "kv step: buffers must not be NULL");
+    if (d->input_stride < E || d->output_stride < E) return fail(FBLT_ERR_ARG, "kv step: row strides below embed_dim");
+
+    int st = fblt_matmul(d->input, d->input_stride, d->packed_qkv, nullptr, d->qkv_work, 3 * E, rows, E, 3 * E, d->precision,
+                         stream);
+    if (st != FBLT_OK) return st;
+
+    fblt_decode_desc a;
+    memset(&a, 0, sizeof(a));
+    a.batch = d->batch;
+    a.num_heads = d->num_heads;
+    a.head_dim = d->head_dim;
+    a.n_new = d->n_new;
+    a.block_mode = d->block_mode;
+    a.window = d->window;
+    a.max_len = d->max_len;
+    a.base_len = d->base_len;
+    a.k_cache = d->k_cache;
+    a.v_cache = d->v_cache;
+    a.cache_seq_stride = d->cache_seq_stride;
+    a.cache_row_stride = d->cache_row_stride;
+    a.q = d->qkv_work;
+    a.q_stride = 3 * E;
+    a.k_new = d->qkv_work + E;
+    a.v_new = d->qkv_work + 2 * E;
+    a.kv_new_stride = 3 * E;
+    a.out = d->combined_work;
+    a.out_stride = E;
+    a.scale = 1.0f / sqrtf((float)d->head_dim); // infer/kv_cache.c:258
+    a.rope_cos = d->rope_cos;
+    a.rope_sin = d->rope_sin;
+    const size_t need = fblt_attn_decode_workspace(&a);
+    if (need > d->workspace_bytes) a.splits = 1; // no room for split-K partials: one pass per (sequence, head)
+    st = fblt_attn_decode(&a, d->workspace, d->workspace_bytes, stream);
+    if (st != FBLT_OK) return st;
+
+    return fblt_matmul(d->combined_work, E, d->packed_proj, nullptr, d->output, d->output_stride, rows, E, E, d->precision,
+                       stream);
+}

@@ -81,6 +81,21 @@ class CrossDesc(C.Structure):
     ]
 
 
+class KvStepDesc(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32), ("n_new", C.c_int32),
+        ("block_mode", C.c_int32), ("window", C.c_int32), ("max_len", C.c_int32), ("precision", C.c_int32),
+        ("base_len", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p),
+        ("cache_seq_stride", C.c_int64), ("cache_row_stride", C.c_int64),
+        ("input", C.c_void_p), ("input_stride", C.c_int64),
+        ("packed_qkv", C.c_void_p), ("packed_proj", C.c_void_p),
+        ("output", C.c_void_p), ("output_stride", C.c_int64),
+        ("qkv_work", C.c_void_p), ("combined_work", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+    ]
+
+
 class AttnDesc(C.Structure):
     _fields_ = [
         ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32),
@@ -146,6 +161,7 @@ SYMBOLS = {
                               C.c_int64, C.c_int64, C.c_int32, C.c_void_p]),
     "fblt_mha_forward": (C.c_int, [C.POINTER(MhaDesc), C.c_void_p]),
     "fblt_cross_attention_forward": (C.c_int, [C.POINTER(CrossDesc), C.c_void_p]),
+    "fblt_kv_self_attention_step": (C.c_int, [C.POINTER(KvStepDesc), C.c_void_p]),
     "fblt_session_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                       C.c_int32, C.c_int32]),
     "fblt_session_destroy": (None, [C.c_void_p]),
@@ -188,9 +204,9 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
         fn.restype = res
         fn.argtypes = args
-    sizes = (C.c_size_t * 8)()
-    n = lib.fblt_abi_sizes(sizes, 8)
-    want = [C.sizeof(HeadArgs), C.sizeof(PatchInfo), C.sizeof(MaskDesc), C.sizeof(AttnDesc), C.sizeof(DecodeDesc), C.sizeof(MhaDesc), C.sizeof(CrossDesc)]
+    sizes = (C.c_size_t * 16)()
+    n = lib.fblt_abi_sizes(sizes, 16)
+    want = [C.sizeof(HeadArgs), C.sizeof(PatchInfo), C.sizeof(MaskDesc), C.sizeof(AttnDesc), C.sizeof(DecodeDesc), C.sizeof(MhaDesc), C.sizeof(CrossDesc), C.sizeof(KvStepDesc)]
     if list(sizes[:n]) != want:
         raise ImportError(f"ABI mismatch between lib.py and libfblt_attn.so: {list(sizes[:n])} vs {want}")
     _lib = lib

@@ -374,6 +374,38 @@ def cross_attention_forward(query_in: torch.Tensor, kv_in: torch.Tensor, w_q: Pa
     return out
 
 
+def kv_self_attention_step(x: torch.Tensor, w_qkv: PackedWeights, w_proj: PackedWeights, k_cache: torch.Tensor,
+                           v_cache: torch.Tensor, base_len: torch.Tensor, num_heads: int, n_new: int, *,
+                           rope_cos: Optional[torch.Tensor] = None, rope_sin: Optional[torch.Tensor] = None,
+                           block_mode: bool = False, window: int = 0, max_len: int = 0,
+                           precision: int = L.PREC_FP32) -> torch.Tensor:
+    """Self-attention part of a decode step: x [batch*n_new, E] rows -> [batch*n_new, E]; K/V rows are
+    written into the caches ([batch, rows, E]) at base_len .. base_len + n_new."""
+    rows, E = int(x.shape[0]), int(x.shape[1])
+    dev = x.device
+    d = L.KvStepDesc()
+    d.batch, d.num_heads, d.head_dim, d.n_new = rows // n_new, num_heads, E // num_heads, n_new
+    d.block_mode, d.window, d.precision = int(block_mode), window, precision
+    d.max_len = max_len or int(k_cache.shape[1])
+    d.base_len = base_len.data_ptr()
+    d.k_cache, d.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+    d.cache_seq_stride, d.cache_row_stride = k_cache.stride(0), k_cache.stride(1)
+    out = torch.empty(rows, E, dtype=torch.float32, device=dev)
+    qkv = torch.empty(rows, 3 * E, dtype=torch.float32, device=dev)
+    comb = torch.empty(rows, E, dtype=torch.float32, device=dev)
+    ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
+    d.input, d.input_stride = x.data_ptr(), x.stride(0)
+    d.packed_qkv, d.packed_proj = w_qkv.buf.data_ptr(), w_proj.buf.data_ptr()
+    d.output, d.output_stride = out.data_ptr(), out.stride(0)
+    d.qkv_work, d.combined_work = qkv.data_ptr(), comb.data_ptr()
+    d.workspace, d.workspace_bytes = ws.data_ptr(), ws.numel()
+    if rope_cos is not None:
+        d.rope_cos, d.rope_sin = rope_cos.data_ptr(), rope_sin.data_ptr()
+    L.check(L.load().fblt_kv_self_attention_step(C.byref(d), _stream_ptr(None)))
+    torch.cuda.current_stream().synchronize()   # the scratch tensors above die with this call
+    return out
+
+
 def unmask_step(logits: torch.Tensor, masked: torch.Tensor, tokens: torch.Tensor, strategy: int, threshold: float):
     """One unmask round over a batch of candidates. logits [batch*B, V] float32, masked/tokens
     [batch, B] uint8 (updated in place). Returns (sel [batch] int64 bit masks, conf [batch,B],

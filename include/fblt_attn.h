@@ -536,6 +536,41 @@ typedef struct {
 
 int fblt_cross_attention_forward(const fblt_cross_desc *desc, void *stream);
 
+/*
+ * The self-attention part of one cache-aware decode step, blt_kv_decode_step
+ * (infer/kv_cache.c:338-396), for a batch of sequences with their own cache
+ * lengths: qkv = input * weight_qkv for the batch * n_new new rows (row
+ * b * n_new + r = sequence b, absolute position base_len[b] + r); Q and K
+ * rotated with that position when rope tables are given; K and V written
+ * through to cache rows base .. base + n_new; attention of the new rows over
+ * the cache (causal inside the new rows, or all-visible with block_mode; optional
+ * window); output = combined * weight_proj. Cache layout and the other fields as
+ * in fblt_decode_desc. workspace may be NULL (then the key range is not split).
+ * Does not advance base_len. All pointers device.
+ */
+typedef struct {
+    int32_t batch, num_heads, head_dim, n_new;
+    int32_t block_mode, window, max_len, precision;
+    const int32_t *base_len;
+    float *k_cache;
+    float *v_cache;
+    int64_t cache_seq_stride, cache_row_stride;
+    const float *input;
+    int64_t input_stride;
+    const void *packed_qkv;
+    const void *packed_proj;
+    float *output;
+    int64_t output_stride;
+    float *qkv_work;      /* [batch * n_new, 3E] */
+    float *combined_work; /* [batch * n_new, E] */
+    void *workspace;
+    size_t workspace_bytes;
+    const float *rope_cos;
+    const float *rope_sin;
+} fblt_kv_step_desc;
+
+int fblt_kv_self_attention_step(const fblt_kv_step_desc *desc, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* host-buffer sessions (what a host-side caller with no device memory uses) */
 /* ------------------------------------------------------------------------ */
@@ -608,7 +643,7 @@ int fblt_tcgen05_error(void);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t fblt_launch_count(void);
 /* sizeof of {fblt_head_args, fblt_patch_info, fblt_mask_desc, fblt_attn_desc,
- * fblt_decode_desc, fblt_mha_desc, fblt_cross_desc}, for bindings that re-declare the structs. Returns the count. */
+ * fblt_decode_desc, fblt_mha_desc, fblt_cross_desc, fblt_kv_step_desc}, for bindings that re-declare the structs. Returns the count. */
 size_t fblt_abi_sizes(size_t *out, size_t cap);
 
 #ifdef __cplusplus

@@ -102,3 +102,46 @@ def test_cross_attention_block_matches_reference(cuda_lib, direction):
                                       ops.PackedWeights(torch.from_numpy(wp).cuda()), cu_q, cu_k, H, mask)
     assert L.load().fblt_tcgen05_error() == 0
     assert_close(got.cpu().numpy(), want, f"cross block {direction}")
+
+
+@pytest.mark.parametrize("block_mode,window", [(False, 0), (True, 0), (False, 24)])
+def test_kv_decode_step_self_attention_block(cuda_lib, block_mode, window):
+    """fblt_kv_self_attention_step against the same chain built from the reference's CPU pieces in
+    the order of infer/kv_cache.c:338-396: matmul, rotary embedding at position base + r, rows
+    written through to the cache, the head operator over the cache, matmul."""
+    if not ob.have_ref():
+        pytest.skip("reference object code not built")
+    from fblt_b200 import workloads
+    from helpers import oracle_decode
+    H, hd, n, batch, cache_rows = 4, 64, 4, 5, 256
+    E = H * hd
+    rng = np.random.default_rng(33)
+    base = np.array([10, 64, 200, 33, 0], dtype=np.int32)
+    case = workloads.decode_case(130, batch, H, n, block_mode, lens=base, cache_rows=cache_rows)
+    case.window = window
+    x = rng.standard_normal((batch * n, E)).astype(np.float32)
+    w_qkv = (rng.standard_normal((E, 3 * E)) / np.sqrt(E)).astype(np.float32)
+    w_proj = (rng.standard_normal((E, E)) / np.sqrt(E)).astype(np.float32)
+    cs, sn = ob.rope_tables(cache_rows, hd, use_ref=True)
+    # reference chain
+    qkv = ob.matmul(x, w_qkv, use_ref=True)
+    pos = (base[:, None] + np.arange(n)[None, :]).reshape(-1)
+    case.q = ob.rope_apply(qkv[:, :E], cs[pos], sn[pos], H, hd, use_ref=True)
+    case.k_new = ob.rope_apply(qkv[:, E:2 * E], cs[pos], sn[pos], H, hd, use_ref=True)
+    case.v_new = np.ascontiguousarray(qkv[:, 2 * E:])
+    combined, _ = oracle_decode(case)
+    want = ob.matmul(combined, w_proj, use_ref=True)
+    # device
+    kc, vc = torch.from_numpy(case.k_cache).cuda(), torch.from_numpy(case.v_cache).cuda()
+    got = ops.kv_self_attention_step(torch.from_numpy(x).cuda(), ops.PackedWeights(torch.from_numpy(w_qkv).cuda()),
+                                     ops.PackedWeights(torch.from_numpy(w_proj).cuda()), kc, vc,
+                                     torch.from_numpy(base).cuda(), H, n, rope_cos=torch.from_numpy(cs).cuda(),
+                                     rope_sin=torch.from_numpy(sn).cuda(), block_mode=block_mode, window=window,
+                                     max_len=int(base.max()) + n)
+    assert L.load().fblt_tcgen05_error() == 0
+    assert_close(got.cpu().numpy(), want, f"kv step block_mode={block_mode} window={window}")
+    # write-through: the cache rows base .. base + n now hold the rotated K and the V rows
+    for b in range(batch):
+        rows = slice(int(base[b]), int(base[b]) + n)
+        assert_close(kc[b, rows].cpu().numpy(), case.k_new[b * n:(b + 1) * n], f"cache K rows of sequence {b}")
+        assert_close(vc[b, rows].cpu().numpy(), case.v_new[b * n:(b + 1) * n], f"cache V rows of sequence {b}")
