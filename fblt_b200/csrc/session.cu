@@ -25,6 +25,10 @@ struct fblt_session {
     cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_kernel[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
     void *ws = nullptr;
     size_t ws_bytes = 0;
+    // download stream and events of the non-blocking forward call
+    cudaStream_t fwd_out = nullptr;
+    cudaEvent_t ev_fwd_kernel = nullptr, ev_fwd_out = nullptr;
+    bool fwd_pending = false;
 };
 
 namespace fblt {
@@ -50,6 +54,9 @@ static void session_free(fblt_session *s) {
         if (s->ev_kernel[i]) cudaEventDestroy(s->ev_kernel[i]);
         if (s->ev_out[i]) cudaEventDestroy(s->ev_out[i]);
     }
+    if (s->ev_fwd_kernel) cudaEventDestroy(s->ev_fwd_kernel);
+    if (s->ev_fwd_out) cudaEventDestroy(s->ev_fwd_out);
+    if (s->fwd_out) cudaStreamDestroy(s->fwd_out);
     if (s->copy_in) cudaStreamDestroy(s->copy_in);
     if (s->copy_out) cudaStreamDestroy(s->copy_out);
     cudaFree(s->ws);
@@ -107,6 +114,9 @@ extern "C" int fblt_session_create(fblt_session **out, int32_t max_batch, int32_
         }                                                                                    \
     } while (0)
     S_TRY(cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking));
+    S_TRY(cudaStreamCreateWithFlags(&s->fwd_out, cudaStreamNonBlocking));
+    S_TRY(cudaEventCreateWithFlags(&s->ev_fwd_kernel, cudaEventDisableTiming));
+    S_TRY(cudaEventCreateWithFlags(&s->ev_fwd_out, cudaEventDisableTiming));
     const size_t fE = (size_t)s->E * sizeof(float);
     if (max_q_rows > 0) S_TRY(cudaMalloc(&s->d_out, (size_t)max_q_rows * fE));
     if (max_q_rows + max_k_rows > 0) S_TRY(cudaMalloc(&s->d_in, (size_t)(max_q_rows + 2 * max_k_rows) * fE));
@@ -150,8 +160,35 @@ extern "C" int fblt_session_create(fblt_session **out, int32_t max_batch, int32_
 
 extern "C" void fblt_session_destroy(fblt_session *s) { fblt::session_free(s); }
 
+namespace fblt {
+static int session_forward_impl(fblt_session *s, const fblt_attn_desc *hd, bool blocking);
+}
+
 extern "C" int fblt_session_forward(fblt_session *s, const fblt_attn_desc *hd) {
+    return fblt::session_forward_impl(s, hd, true);
+}
+
+extern "C" int fblt_session_forward_async(fblt_session *s, const fblt_attn_desc *hd) {
+    return fblt::session_forward_impl(s, hd, false);
+}
+
+extern "C" int fblt_session_wait(fblt_session *s) {
     using namespace fblt;
+    if (!s) return fail(FBLT_ERR_ARG, "session_wait: NULL session");
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
+    FBLT_CUDA_TRY(cudaStreamSynchronize(s->fwd_out));
+    if (s->copy_in) FBLT_CUDA_TRY(cudaStreamSynchronize(s->copy_in));
+    if (s->copy_out) FBLT_CUDA_TRY(cudaStreamSynchronize(s->copy_out));
+    const bool had_forward = s->fwd_pending;
+    s->fwd_pending = false;
+    if (had_forward) {
+        if (const int code = fblt_tcgen05_error())
+            return fail(FBLT_ERR_CUDA, "session_wait: a tcgen05 CTA gave up on a bounded wait (code 0x%x)", code);
+    }
+    return FBLT_OK;
+}
+
+static int fblt::session_forward_impl(fblt_session *s, const fblt_attn_desc *hd, bool blocking) {
     if (!s || !hd) return fail(FBLT_ERR_ARG, "session_forward: NULL argument");
     if (hd->batch < 0 || hd->batch > s->max_batch) return fail(FBLT_ERR_CAPACITY, "session_forward: batch %d > %d", hd->batch, s->max_batch);
     if (hd->num_heads != s->H || hd->head_dim != s->hd) return fail(FBLT_ERR_ARG, "session_forward: heads/head_dim differ from the session");
@@ -211,13 +248,18 @@ extern "C" int fblt_session_forward(fblt_session *s, const fblt_attn_desc *hd) {
     d.out = s->d_out;
     d.q_stride = d.k_stride = d.v_stride = dstride;
     d.out_stride = E;
+    // the previous non-blocking call's rows must have left d_out before this kernel overwrites them
+    if (s->fwd_pending) FBLT_CUDA_TRY(cudaStreamWaitEvent(s->stream, s->ev_fwd_out, 0));
     int st = fblt_attn_forward(&d, s->stream);
     if (st != FBLT_OK) return st;
-    FBLT_CUDA_TRY(cudaMemcpy2DAsync(hd->out, (size_t)hd->out_stride * 4, s->d_out, wb, wb, (size_t)tq, cudaMemcpyDeviceToHost, s->stream));
-    FBLT_CUDA_TRY(cudaStreamSynchronize(s->stream));
-    if (const int code = fblt_tcgen05_error())
-        return fail(FBLT_ERR_CUDA, "session_forward: a tcgen05 CTA gave up on a bounded wait (code 0x%x)", code);
-    return FBLT_OK;
+    // the rows go home on a stream of their own, so that whatever the caller enqueues next on the
+    // session (a cache load, decode steps) overlaps with the download
+    FBLT_CUDA_TRY(cudaEventRecord(s->ev_fwd_kernel, s->stream));
+    FBLT_CUDA_TRY(cudaStreamWaitEvent(s->fwd_out, s->ev_fwd_kernel, 0));
+    FBLT_CUDA_TRY(cudaMemcpy2DAsync(hd->out, (size_t)hd->out_stride * 4, s->d_out, wb, wb, (size_t)tq, cudaMemcpyDeviceToHost, s->fwd_out));
+    FBLT_CUDA_TRY(cudaEventRecord(s->ev_fwd_out, s->fwd_out));
+    s->fwd_pending = true;
+    return blocking ? fblt_session_wait(s) : FBLT_OK;
 }
 
 extern "C" int fblt_session_cache_load(fblt_session *s, int32_t batch, const int32_t *lens, const float *k_host,

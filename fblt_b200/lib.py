@@ -166,6 +166,8 @@ SYMBOLS = {
                                       C.c_int32, C.c_int32]),
     "fblt_session_destroy": (None, [C.c_void_p]),
     "fblt_session_forward": (C.c_int, [C.c_void_p, C.POINTER(AttnDesc)]),
+    "fblt_session_forward_async": (C.c_int, [C.c_void_p, C.POINTER(AttnDesc)]),
+    "fblt_session_wait": (C.c_int, [C.c_void_p]),
     "fblt_session_cache_load": (C.c_int, [C.c_void_p, C.c_int32, c_i32_p, C.c_void_p, C.c_void_p, C.c_int64]),
     "fblt_session_decode": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_float, C.c_void_p,
                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32]),

@@ -460,8 +460,10 @@ class Session:
 
     def forward(self, q, k, v, out, cu_q, cu_k, scale: float, mask: Optional[MaskConfig] = None, *,
                 q_stride=None, k_stride=None, v_stride=None, out_stride=None, impl: int = L.IMPL_AUTO,
-                precision: int = L.PREC_FP32) -> None:
-        """q/k/v/out: host arrays; strides in elements (default: the arrays' own row stride)."""
+                precision: int = L.PREC_FP32, wait: bool = True) -> None:
+        """q/k/v/out: host arrays; strides in elements (default: the arrays' own row stride).
+        wait=False returns once the work is enqueued (the rows come home beside whatever is called
+        next on the session); `out` may be read after wait()."""
         def rs(a, s):
             if s is not None:
                 return s
@@ -483,7 +485,11 @@ class Session:
         d.scale = float(scale)
         tables = mask.host_tables(batch)
         mask.fill(d.mask, tables)
-        L.check(self._lib.fblt_session_forward(self._h, C.byref(d)))
+        fn = self._lib.fblt_session_forward if wait else self._lib.fblt_session_forward_async
+        L.check(fn(self._h, C.byref(d)))
+
+    def wait(self) -> None:
+        L.check(self._lib.fblt_session_wait(self._h))
 
     def cache_load(self, lens, k_host, v_host, host_seq_stride_rows: int) -> None:
         lens_h = np.ascontiguousarray(np.asarray(lens, dtype=np.int32))

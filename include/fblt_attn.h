@@ -596,6 +596,16 @@ void fblt_session_destroy(fblt_session *s);
  * mask.q_group_ids / k_group_ids are not supported here.
  */
 int fblt_session_forward(fblt_session *s, const fblt_attn_desc *host_desc);
+/*
+ * The same call without the final wait: the output rows travel home on a stream of their own
+ * while the caller goes on (fblt_session_cache_load, fblt_session_decode_steps, ... on the same
+ * session run beside the download). Every host buffer and table of `host_desc` must stay valid
+ * and `out` must not be read until fblt_session_wait() has returned.
+ */
+int fblt_session_forward_async(fblt_session *s, const fblt_attn_desc *host_desc);
+/* Returns when everything enqueued on the session has completed (and reports a tcgen05 bounded-
+ * wait failure of a forward call, if any). */
+int fblt_session_wait(fblt_session *s);
 
 /* Loads `lens[b]` rows of host K/V ([batch, rows_stride_rows, E] with the
  * given per-sequence stride in rows) into the session cache and sets the

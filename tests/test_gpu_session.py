@@ -114,3 +114,25 @@ def test_session_decode_steps_pipeline_equals_single_steps(cuda_lib):
     case.q, case.k_new, case.v_new = q_all[0], k_all[0], v_all[0]
     want, _ = oracle_decode(case)
     assert_close(outs[1][0], want, "pipelined step 0")
+
+
+def test_session_forward_async_equals_blocking(cuda_lib):
+    """The non-blocking forward call followed by other session work and wait() returns the same rows."""
+    case = workloads.c5_prefill(batch=6)
+    E = case.embed
+    lens = np.array([5, 9, 0, 33, 64, 7], dtype=np.int32)
+    dcase = workloads.decode_case(140, 6, case.num_heads, 4, True, lens=lens, cache_rows=128)
+    outs = []
+    for wait in (True, False):
+        s = ops.Session(6, case.num_heads, 64, max_q_rows=case.q.shape[0], max_k_rows=case.k.shape[0], cache_rows=128,
+                        max_new=4)
+        out = np.full((case.q.shape[0], E), np.nan, dtype=np.float32)
+        s.forward(case.q, case.k, case.v, out, case.cu_q, case.cu_k, case.scale, case.mask, wait=wait)
+        s.cache_load(lens, dcase.k_cache, dcase.v_cache, 128)        # runs beside the download when wait=False
+        s.wait()
+        assert np.isfinite(out).all()
+        outs.append(out)
+        s.close()
+    assert outs[0].tobytes() == outs[1].tobytes()
+    want, _, _ = oracle_forward(case)
+    assert_close(outs[1], want, "async session forward")
