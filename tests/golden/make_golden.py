@@ -44,8 +44,36 @@ def mask_case(name, nq, nk, **kw):
     np.savez_compressed(HERE / f"{name}.npz", **d)
 
 
+def block_cases():
+    """Projection matmul and the two attention blocks (models/attention.c:130-207,
+    models/cross_attention.c:98-157) run by the reference on the CPU."""
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal((37, 52)).astype(np.float32)
+    b = rng.standard_normal((52, 45)).astype(np.float32)
+    np.savez_compressed(HERE / "matmul_37x52x45.npz", kind="matmul", a=a, b=b, out=ob.matmul(a, b, use_ref=True))
+    E, H, T = 64, 2, 21
+    x = rng.standard_normal((T, E)).astype(np.float32)
+    w_qkv = (rng.standard_normal((E, 3 * E)) / np.sqrt(E)).astype(np.float32)
+    w_proj = (rng.standard_normal((E, E)) / np.sqrt(E)).astype(np.float32)
+    for name, kw in (("mha_block_rope_causal", dict(use_rope=True, window=0)),
+                     ("mha_block_window", dict(use_rope=False, window=6))):
+        out = ob.ref_multihead_attention(x, w_qkv, w_proj, H, is_causal=True, **kw)
+        np.savez_compressed(HERE / f"{name}.npz", kind="mha", x=x, w_qkv=w_qkv, w_proj=w_proj, num_heads=H,
+                            use_rope=kw["use_rope"], window=kw["window"], out=out)
+    bounds = synth.bounds_from_lengths(synth.geometric_patches(12, 0, 40))
+    P = len(bounds) - 1
+    _, byte_patch = ob.patch_group_ids(bounds, use_ref=True)
+    xq = rng.standard_normal((P, E)).astype(np.float32)
+    xk = rng.standard_normal((40, E)).astype(np.float32)
+    ws = [(rng.standard_normal((E, E)) / np.sqrt(E)).astype(np.float32) for _ in range(4)]
+    out = ob.ref_cross_attention(xq, xk, *ws, H, np.arange(P), byte_patch[:40])
+    np.savez_compressed(HERE / "cross_block_encoder.npz", kind="cross", xq=xq, xk=xk, wq=ws[0], wk=ws[1], wv=ws[2],
+                        wp=ws[3], num_heads=H, bounds=bounds, out=out)
+
+
 def main():
     assert ob.have_ref(), "build oracle/_ref first (make -C oracle)"
+    block_cases()
     # shape of tests/parity/parity_transformer.c:19-61 (T=6, E=16, H=4, causal)
     head_case("head_causal_t6_h4", 101, 6, 6, 4, 4, 0.5, is_causal=True)
     # ragged sizes around warp / tile edges, non-causal, arbitrary additive mask values

@@ -118,3 +118,35 @@ def oracle_decode(case: DecodeCase, nthreads: int = 0, ref: bool | None = None, 
                      scale=case.scale, mask=mask, nq=n, nk=base + n, q_row=b * n, k_row=0)
     secs = jobs.run(nthreads, ref)
     return out, secs
+
+
+# ---- the attention blocks composed from the oracle's pieces --------------------------------------
+
+def oracle_mha_block(x, w_qkv, w_proj, num_heads, *, use_rope, window=0, theta=500000.0, ref=False):
+    """blt_multihead_attention (models/attention.c:130-207) as a chain of oracle functions: matmul,
+    rotary embedding of Q and K at position = row, dense causal (+ window) mask, the head operator per
+    head, matmul. Every piece is the restatement (ref=False) or the reference's own object code."""
+    T, E = x.shape
+    hd = E // num_heads
+    qkv = ob.matmul(x, w_qkv, use_ref=ref)
+    q, k, v = (np.ascontiguousarray(qkv[:, i * E:(i + 1) * E]) for i in range(3))
+    if use_rope:
+        cs, sn = ob.rope_tables(T, hd, theta, use_ref=ref)
+        q, k = ob.rope_apply(q, cs, sn, num_heads, hd, use_ref=ref), ob.rope_apply(k, cs, sn, num_heads, hd, use_ref=ref)
+    mask = None
+    if window > 0:
+        mask, _ = ob.build_mask(T, T, window=window, is_causal=True, use_ref=ref)
+    comb, _ = ob.batched_attention(q, k, v, [0, T], [0, T], num_heads, hd, 1.0 / np.sqrt(np.float32(hd)), [mask],
+                                   is_causal=True, use_ref=ref, nthreads=1)
+    return ob.matmul(comb, w_proj, use_ref=ref)
+
+
+def oracle_cross_block(xq, xk, wq, wk, wv, wp, num_heads, q_groups, k_groups, ref=False):
+    """blt_cross_attention_forward (models/cross_attention.c:98-157) as a chain of oracle functions."""
+    E = xq.shape[1]
+    hd = E // num_heads
+    q, k, v = ob.matmul(xq, wq, use_ref=ref), ob.matmul(xk, wk, use_ref=ref), ob.matmul(xk, wv, use_ref=ref)
+    mask, _ = ob.build_mask(xq.shape[0], xk.shape[0], q_groups=q_groups, k_groups=k_groups, use_ref=ref)
+    comb, _ = ob.batched_attention(q, k, v, [0, xq.shape[0]], [0, xk.shape[0]], num_heads, hd,
+                                   1.0 / np.sqrt(np.float32(hd)), [mask], use_ref=ref, nthreads=1)
+    return ob.matmul(comb, wp, use_ref=ref)

@@ -145,3 +145,41 @@ def test_kv_decode_step_self_attention_block(cuda_lib, block_mode, window):
         rows = slice(int(base[b]), int(base[b]) + n)
         assert_close(kc[b, rows].cpu().numpy(), case.k_new[b * n:(b + 1) * n], f"cache K rows of sequence {b}")
         assert_close(vc[b, rows].cpu().numpy(), case.v_new[b * n:(b + 1) * n], f"cache V rows of sequence {b}")
+
+
+def test_blocks_against_committed_fixtures(cuda_lib):
+    """The committed outputs of the reference's own CPU code (tests/golden/make_golden.py) for the
+    projection matmul and the two attention blocks: no reference object code needed at run time."""
+    from pathlib import Path
+    golden = Path(__file__).resolve().parent / "golden"
+    seen = set()
+    for f in sorted(golden.glob("*.npz")):
+        g = np.load(f)
+        kind = str(g["kind"])
+        if kind == "matmul":
+            w = ops.PackedWeights(torch.from_numpy(g["b"]).cuda())
+            a = np.zeros((g["a"].shape[0], 52), np.float32)
+            a[:, :g["a"].shape[1]] = g["a"]
+            got = ops.matmul(torch.from_numpy(a).cuda()[:, :g["a"].shape[1]], w).cpu().numpy()
+        elif kind == "mha":
+            H, T, E = int(g["num_heads"]), g["x"].shape[0], g["x"].shape[1]
+            rope = {}
+            if bool(g["use_rope"]):
+                cs, sn = ob.rope_tables(T, E // H)
+                rope = dict(rope_cos=torch.from_numpy(cs).cuda(), rope_sin=torch.from_numpy(sn).cuda())
+            got = ops.mha_forward(torch.from_numpy(g["x"]).cuda(), ops.PackedWeights(torch.from_numpy(g["w_qkv"]).cuda()),
+                                  ops.PackedWeights(torch.from_numpy(g["w_proj"]).cuda()), [0, T], H,
+                                  MaskConfig(is_causal=True, sliding_window=int(g["window"])), **rope).cpu().numpy()
+        elif kind == "cross":
+            H, bounds = int(g["num_heads"]), g["bounds"]
+            got = ops.cross_attention_forward(
+                torch.from_numpy(g["xq"]).cuda(), torch.from_numpy(g["xk"]).cuda(),
+                ops.PackedWeights(torch.from_numpy(g["wq"]).cuda()), packed_kv(g["wk"], g["wv"]),
+                ops.PackedWeights(torch.from_numpy(g["wp"]).cuda()), [0, g["xq"].shape[0]], [0, g["xk"].shape[0]], H,
+                MaskConfig(group_rule=L.GROUP_PATCH_ENC, patch_bounds=[bounds])).cpu().numpy()
+        else:
+            continue
+        seen.add(kind)
+        assert L.load().fblt_tcgen05_error() == 0
+        assert_close(got, g["out"], f.name)
+    assert seen == {"matmul", "mha", "cross"}

@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 from fblt_b200 import synth
+from helpers import oracle_cross_block, oracle_mha_block
 from oracle import binding as ob
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
@@ -185,6 +186,21 @@ def test_golden_fixtures():
             elif kind == "latent":
                 got = [ob.latent_at(g["bounds"], int(p), use_ref=ref) for p in g["pos"]]
                 assert got == list(g["latent"]), f.name
+            elif kind == "matmul":
+                assert ob.matmul(g["a"], g["b"], use_ref=ref).tobytes() == g["out"].tobytes(), f.name
+            elif kind == "mha":
+                # the block is exactly the chain of its pieces, in either oracle flavour
+                out = oracle_mha_block(g["x"], g["w_qkv"], g["w_proj"], int(g["num_heads"]), use_rope=bool(g["use_rope"]),
+                                       window=int(g["window"]), ref=ref)
+                assert out.tobytes() == g["out"].tobytes(), f.name
+            elif kind == "cross":
+                bounds = g["bounds"]
+                _, byte_patch = ob.patch_group_ids(bounds, use_ref=ref)
+                out = oracle_cross_block(g["xq"], g["xk"], g["wq"], g["wk"], g["wv"], g["wp"], int(g["num_heads"]),
+                                         np.arange(len(bounds) - 1), byte_patch[:g["xk"].shape[0]], ref=ref)
+                assert out.tobytes() == g["out"].tobytes(), f.name
+            else:
+                raise AssertionError(f"unknown fixture kind {kind}")
 
 
 def test_matmul_restatement_equals_reference():
