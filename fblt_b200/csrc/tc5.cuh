@@ -132,6 +132,8 @@ __device__ __forceinline__ uint32_t t5_tf32(float x) {
     const uint32_t r = (b + 0x1000u) & 0xFFFFE000u;
     return (b & 0x7F800000u) == 0x7F800000u ? b : r;
 }
+// The same rounding for values known to be finite (probabilities): two integer instructions.
+__device__ __forceinline__ uint32_t t5_tf32_finite(float x) { return (__float_as_uint(x) + 0x1000u) & 0xFFFFE000u; }
 __device__ __forceinline__ float t5_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

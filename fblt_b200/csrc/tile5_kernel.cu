@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 for (int x = 0; x < 4; ++x) {
                     const float p = t5_ex2(s[kc * 4 + x] - ref);
                     rs += p;
-                    h4[x] = t5_tf32(p);
+                    h4[x] = t5_tf32_finite(p); // p is in [0, 1]
                     l4[x] = __float_as_uint(p - __uint_as_float(h4[x]));
                 }
                 *reinterpret_cast<uint4 *>(smem + kOffK + kc * 2048 + prow) = ph; // K tile space, S is complete
@@ -367,12 +367,11 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 for (int c = 0; c < 32; ++c) o[c] = 0.0f;
             }
             if (i < nq) {
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f; // rows without keys give zeros
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (l > 0.0f) v = make_float4(o[c * 4] / l, o[c * 4 + 1] / l, o[c * 4 + 2] / l, o[c * 4 + 3] / l);
-                    *reinterpret_cast<float4 *>(orow + half * 32 + c * 4) = v;
-                }
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<float4 *>(orow + half * 32 + c * 4) =
+                        make_float4(o[c * 4] * inv, o[c * 4 + 1] * inv, o[c * 4 + 2] * inv, o[c * 4 + 3] * inv);
             }
         }
     }
