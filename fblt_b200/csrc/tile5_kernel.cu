@@ -42,6 +42,14 @@ __device__ unsigned int g_t5_error; // 0 = ok; otherwise (code << 24) | blockIdx
 
 // ---- the kernel -----------------------------------------------------------------
 
+// Rounding of an input element. With the low part present (three-pass mode) a NaN or an infinity in
+// the element reaches the score through hi or through lo = x - hi whatever the rounding does to
+// the bit pattern, so the pass-through test of t5_tf32 is only needed in single-pass mode.
+template <bool X3>
+__device__ __forceinline__ uint32_t t5_round_in(float x) {
+    return X3 ? t5_tf32_finite(x) : t5_tf32(x);
+}
+
 template <bool X3>
 __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_desc d) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -148,7 +156,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 uint32_t *kh = &khi.x, *kl = &klo.x;
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    kh[x] = t5_tf32(ke[x]);
+                    kh[x] = t5_round_in<X3>(ke[x]);
                     kl[x] = __float_as_uint(ke[x] - __uint_as_float(kh[x]));
                 }
                 *reinterpret_cast<uint4 *>(smem + kOffK + koff) = khi;
@@ -174,7 +182,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 for (int st = 0; st < 4; ++st) {
                     const int n = c * 4 + ((st + v_xo) & 3);
                     const uint32_t o = vbase_off + (n >> 3) * 128 + (n & 7) * 16;
-                    const uint32_t vh = t5_tf32(ve[st]);
+                    const uint32_t vh = t5_round_in<X3>(ve[st]);
                     *reinterpret_cast<uint32_t *>(smem + kOffV + o) = vh;
                     if (X3) *reinterpret_cast<uint32_t *>(smem + kOffV + kPlaneKV + o) = __float_as_uint(ve[st] - __uint_as_float(vh));
                 }
@@ -205,7 +213,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
                 const float e[4] = {v.x * qscale, v.y * qscale, v.z * qscale, v.w * qscale};
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    qh[c * 4 + x] = t5_tf32(e[x]);
+                    qh[c * 4 + x] = t5_round_in<X3>(e[x]);
                     ql[c * 4 + x] = __float_as_uint(e[x] - __uint_as_float(qh[c * 4 + x]));
                 }
             }

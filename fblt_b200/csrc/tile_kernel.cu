@@ -45,8 +45,13 @@ __device__ __forceinline__ uint32_t to_tf32(float x) {
 }
 // x = hi + lo with hi the TF32 rounding of x; lo is consumed by the tensor core
 // with its low mantissa bits ignored, which is below fp32 resolution of x.
+// With the low part in use (three-pass mode) the rounding needs no Inf / NaN pass-through:
+// whatever it does to such a bit pattern, the low part x - hi is then not finite, so the score
+// still is not. In single-pass mode only hi reaches the tensor core, so Q and K keep the test.
+// Probabilities and V rows (finite by contract) never need it.
+template <bool CHECKED>
 __device__ __forceinline__ void split_tf32(float x, uint32_t &hi, uint32_t &lo) {
-    hi = to_tf32(x);
+    hi = CHECKED ? to_tf32(x) : ((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
     lo = __float_as_uint(x - __uint_as_float(hi));
 }
 __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -207,16 +212,16 @@ __global__ void __launch_bounds__(kTileThreads, STAGES == 1 ? 4 : 2) tile_attn_k
 #pragma unroll
             for (int ks = 0; ks < KS_S; ++ks) {
                 uint32_t ahi[4], alo[4];
-                split_tf32(sQ[(wr + g) * LDS + ks * 8 + t] * qscale, ahi[0], alo[0]);
-                split_tf32(sQ[(wr + g + 8) * LDS + ks * 8 + t] * qscale, ahi[1], alo[1]);
-                split_tf32(sQ[(wr + g) * LDS + ks * 8 + t + 4] * qscale, ahi[2], alo[2]);
-                split_tf32(sQ[(wr + g + 8) * LDS + ks * 8 + t + 4] * qscale, ahi[3], alo[3]);
+                split_tf32<!X3>(sQ[(wr + g) * LDS + ks * 8 + t] * qscale, ahi[0], alo[0]);
+                split_tf32<!X3>(sQ[(wr + g + 8) * LDS + ks * 8 + t] * qscale, ahi[1], alo[1]);
+                split_tf32<!X3>(sQ[(wr + g) * LDS + ks * 8 + t + 4] * qscale, ahi[2], alo[2]);
+                split_tf32<!X3>(sQ[(wr + g + 8) * LDS + ks * 8 + t + 4] * qscale, ahi[3], alo[3]);
 #pragma unroll
                 for (int n = 0; n < 8; ++n) {
                     if (n < nlo || n >= nhi) continue; // scores stay 0 and are masked below
                     uint32_t bhi[2], blo[2];
-                    split_tf32(tK[(n * 8 + g) * LDS + ks * 8 + t], bhi[0], blo[0]);
-                    split_tf32(tK[(n * 8 + g) * LDS + ks * 8 + t + 4], bhi[1], blo[1]);
+                    split_tf32<!X3>(tK[(n * 8 + g) * LDS + ks * 8 + t], bhi[0], blo[0]);
+                    split_tf32<!X3>(tK[(n * 8 + g) * LDS + ks * 8 + t + 4], bhi[1], blo[1]);
                     if (X3) {
                         mma_tf32(sacc[n], alo, bhi);
                         mma_tf32(sacc[n], ahi, blo);
@@ -277,15 +282,15 @@ __global__ void __launch_bounds__(kTileThreads, STAGES == 1 ? 4 : 2) tile_attn_k
             for (int ks = 0; ks < 8; ++ks) {
                 if (ks < nlo || ks >= nhi) continue; // every probability in this block is 0
                 uint32_t ahi[4], alo[4];
-                split_tf32(sacc[ks][0], ahi[0], alo[0]); // row g,   key 2t
-                split_tf32(sacc[ks][2], ahi[1], alo[1]); // row g+8, key 2t
-                split_tf32(sacc[ks][1], ahi[2], alo[2]); // row g,   key 2t+1
-                split_tf32(sacc[ks][3], ahi[3], alo[3]); // row g+8, key 2t+1
+                split_tf32<false>(sacc[ks][0], ahi[0], alo[0]); // row g,   key 2t
+                split_tf32<false>(sacc[ks][2], ahi[1], alo[1]); // row g+8, key 2t
+                split_tf32<false>(sacc[ks][1], ahi[2], alo[2]); // row g,   key 2t+1
+                split_tf32<false>(sacc[ks][3], ahi[3], alo[3]); // row g+8, key 2t+1
 #pragma unroll
                 for (int n = 0; n < NT_O; ++n) {
                     uint32_t bhi[2], blo[2];
-                    split_tf32(tV[(ks * 8 + 2 * t) * LDS + n * 8 + g], bhi[0], blo[0]);
-                    split_tf32(tV[(ks * 8 + 2 * t + 1) * LDS + n * 8 + g], bhi[1], blo[1]);
+                    split_tf32<false>(tV[(ks * 8 + 2 * t) * LDS + n * 8 + g], bhi[0], blo[0]);
+                    split_tf32<false>(tV[(ks * 8 + 2 * t + 1) * LDS + n * 8 + g], bhi[1], blo[1]);
                     if (X3) {
                         mma_tf32(oacc[n], alo, bhi);
                         mma_tf32(oacc[n], ahi, blo);

@@ -120,6 +120,14 @@ def test_common_patches_matches_reference_or_definition():
             assert ob.ref().ref_kv_common_patches(a, ncached, b, nb) == want
 
 
+def test_matmul_packed_size():
+    """One 32 KB (hi | lo) tile per 128 output columns and 32 of depth, both rounded up."""
+    lib = L.load()
+    for K, N in ((1024, 3072), (1024, 1024), (4, 1), (33, 129), (100, 130)):
+        assert lib.fblt_matmul_packed_bytes(K, N) == -(-N // 128) * -(-K // 32) * 32768
+    assert lib.fblt_matmul_packed_bytes(0, 8) == 0 and lib.fblt_matmul_packed_bytes(8, -1) == 0
+
+
 def test_synth_is_deterministic_and_sliceable():
     a = synth.normal(5, synth.TAG_Q, 1000)
     b = synth.normal(5, synth.TAG_Q, 400, start=333)

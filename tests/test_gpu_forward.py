@@ -237,3 +237,25 @@ def test_rotary_tables_are_validated(cuda_lib):
     batch.desc.rope_sin = None                  # one table without the other
     with pytest.raises(L.FbltError):
         ops.attn_forward(batch)
+
+
+def test_non_finite_scores_weigh_zero(cuda_lib):
+    """A key whose score is not finite (infinity or any NaN bit pattern in its K row) carries weight
+    0 for every query, as in ops/vecmath_cpu.c:33-52; the other keys are unaffected."""
+    cu = np.array([0, 150], dtype=np.int32)
+    case = random_case(77, cu, cu, 2, 64, MaskConfig(is_causal=True))
+    k = case.k.copy()
+    k[5, 3] = np.inf
+    k[17, 64 + 9] = -np.inf
+    k[40, 20] = np.nan
+    kv = k.view(np.uint32)
+    kv[66, 1] = 0x7FFFFFFF            # NaN with every payload bit set
+    kv[101, 70] = 0xFFFFF001          # negative NaN, large payload
+    case = dataclasses.replace(case, k=k)
+    want, _, _ = oracle_forward(case)
+    assert np.isfinite(want).all()
+    for impl, prec in KERNELS + T5_KERNELS:
+        got, _ = forward_gpu(case, impl, prec)
+        assert np.isfinite(got).all(), (impl, prec)
+        tol = dict(atol=TF32_ATOL, rtol=TF32_RTOL) if prec == L.PREC_TF32 else {}
+        assert_close(got, want, f"non-finite keys impl={impl} prec={prec}", **tol)
