@@ -199,14 +199,17 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
         const int idx = dl / REP;        // the score this lane owns
         const int q_own = idx % NQ;
         float m_own = -INFINITY, l_own = 0.0f;
-        for (int c = warp; c < nchunks; c += kDecWarps) {
-            const int jb = F0 + c * CH + grp;
+        // running row pointers: the chunk loop adds one precomputed stride instead of redoing the
+        // 64-bit row arithmetic for every load
+        const int64_t ustep = (int64_t)KPW * p.row_stride, cstep = (int64_t)kDecWarps * CH * p.row_stride;
+        const float *kp = kc + (int64_t)(F0 + warp * CH + grp) * p.row_stride;
+        const float *vp = vc + (int64_t)(F0 + warp * CH + grp) * p.row_stride;
+        for (int c = warp; c < nchunks; c += kDecWarps, kp += cstep, vp += cstep) {
             float4 kk[U], vv[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int64_t off = (int64_t)(jb + u * KPW) * p.row_stride;
-                kk[u] = ld4(kc + off);
-                vv[u] = ld4(vc + off);
+                kk[u] = ld4(kp + u * ustep);
+                vv[u] = ld4(vp + u * ustep);
             }
             float s[V];
 #pragma unroll
@@ -219,19 +222,29 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
             float cmax = sv;
 #pragma unroll
             for (int o = NQ * REP; o < LPK; o <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, o));
-            const float mn = fmaxf(m_own, cmax);
+            // m_own is the reference the exponentials are taken against. It follows the running
+            // maximum only when a chunk's maximum is more than 2^8 above it (or at the first finite
+            // score): the rescale of the accumulators -- a shuffle and four multiplies per query row
+            // and chunk -- then happens a few times per sequence instead of every chunk, and the
+            // probabilities stay below 2^8.
+            const bool move = cmax > m_own + 8.0f || m_own == -INFINITY;
+            const float mn = move ? cmax : m_own;
             const float mref = mn == -INFINITY ? 0.0f : mn;
-            const float corr_own = fast_exp2(m_own - mref);
             const float pe_own = fast_exp2(sv - mref);
             float psum = pe_own;
 #pragma unroll
             for (int o = NQ * REP; o < LPK; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
-            l_own = l_own * corr_own + psum;
+            if (__any_sync(0xffffffffu, move)) {
+                const float corr_own = move ? fast_exp2(m_own - mref) : 1.0f;
+                l_own = l_own * corr_own + psum;
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) scale4(acc[q], __shfl_sync(0xffffffffu, corr_own, q * REP, LPK));
+            } else {
+                l_own += psum;
+            }
             m_own = mn;
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
-                const float corr = __shfl_sync(0xffffffffu, corr_own, q * REP, LPK);
-                scale4(acc[q], corr);
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const float pe = __shfl_sync(0xffffffffu, pe_own, (u * NQ + q) * REP, LPK);
