@@ -11,7 +11,7 @@
 //            The A operand of the MMA lives in TMEM, not in shared memory: a group of four
 //            producer warps (thread = one row of the tile = one TMEM lane) reads its rows
 //            from the swizzled tile without bank conflicts, splits them into (hi, lo) and
-//            writes both with tcgen05.st. Four such groups take the steps in turn: one
+//            writes both with tcgen05.st. Two such groups take the steps in turn: one
 //            conversion is a chain of waits, and the chains of consecutive steps overlap.
 //   MMA    = one thread; per 8-deep slice one tcgen05.mma of shape 128x256x8 (A hi from TMEM
 //            against the weight tile's high | low halves: hi*hi into the main accumulator,
@@ -22,10 +22,11 @@
 //            the tensor pipe fed. The small terms are kept apart because the tensor core
 //            truncates when it adds into the accumulator: one addition per 8-deep slice into
 //            the main sum, not three.
-//   out    = the producer warps read main + small accumulators (warp w: TMEM lanes
-//            32 (w & 3).., columns 64 (w >> 2)..), add the bias and store.
-//   No __syncthreads in the main loop: the four roles meet only on mbarriers (raw a landed,
-//   raw a read, a in TMEM, b landed, stage free, all done).
+//   out    = four epilogue warps (warp q: TMEM lanes 32 q ..) read main + small accumulators,
+//            hand the TMEM back to the MMA thread, add the bias and store. The CTA is
+//            persistent (one per SM), so the next tile's loads and conversions run meanwhile.
+//   No __syncthreads in the main loop: the five roles meet only on mbarriers (raw a landed,
+//   raw a read, a in TMEM + b landed, stage free, tile done, accumulators read).
 //
 // TMEM columns: [0,128) main accumulator, [128,256) small terms, 256 + 64 stage: A hi | A lo.
 //
