@@ -231,16 +231,15 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
             const float mn = move ? cmax : m_own;
             const float mref = mn == -INFINITY ? 0.0f : mn;
             const float pe_own = fast_exp2(sv - mref);
-            float psum = pe_own;
-#pragma unroll
-            for (int o = NQ * REP; o < LPK; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+            // l_own sums this lane's own probabilities only (the lanes of a query row share its
+            // reference, so their sums are added once, after the loop)
             if (__any_sync(0xffffffffu, move)) {
                 const float corr_own = move ? fast_exp2(m_own - mref) : 1.0f;
-                l_own = l_own * corr_own + psum;
+                l_own = l_own * corr_own + pe_own;
 #pragma unroll
                 for (int q = 0; q < NQ; ++q) scale4(acc[q], __shfl_sync(0xffffffffu, corr_own, q * REP, LPK));
             } else {
-                l_own += psum;
+                l_own += pe_own;
             }
             m_own = mn;
 #pragma unroll
@@ -252,6 +251,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
                 }
             }
         }
+#pragma unroll
+        for (int o = NQ * REP; o < LPK; o <<= 1) l_own += __shfl_xor_sync(0xffffffffu, l_own, o);
         // hand the per-row state to every lane of the group for the code below
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
