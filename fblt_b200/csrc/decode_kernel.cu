@@ -219,28 +219,26 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
             lane_group_transpose_reduce<V, LPK / 2>(s, lane);
             float sv = s[0];
             if (!finite_f(sv)) sv = -INFINITY;
-            float cmax = sv;
-#pragma unroll
-            for (int o = NQ * REP; o < LPK; o <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, o));
             // m_own is the reference the exponentials are taken against. It follows the running
-            // maximum only when a chunk's maximum is more than 2^8 above it (or at the first finite
-            // score): the rescale of the accumulators -- a shuffle and four multiplies per query row
-            // and chunk -- then happens a few times per sequence instead of every chunk, and the
-            // probabilities stay below 2^8.
-            const bool move = cmax > m_own + 8.0f || m_own == -INFINITY;
-            const float mn = move ? cmax : m_own;
-            const float mref = mn == -INFINITY ? 0.0f : mn;
-            const float pe_own = fast_exp2(sv - mref);
+            // maximum only when a score is more than 2^8 above it (or at the first finite score), so
+            // the common chunk needs neither the row-maximum butterfly nor the rescale of the
+            // accumulators -- one warp vote instead -- and the probabilities stay below 2^8.
             // l_own sums this lane's own probabilities only (the lanes of a query row share its
-            // reference, so their sums are added once, after the loop)
-            if (__any_sync(0xffffffffu, move)) {
-                const float corr_own = move ? fast_exp2(m_own - mref) : 1.0f;
-                l_own = l_own * corr_own + pe_own;
+            // reference, so their sums are added once, after the loop).
+            float mn = m_own;
+            if (__any_sync(0xffffffffu, sv > m_own + 8.0f || (m_own == -INFINITY && sv > -INFINITY))) {
+                float cmax = sv;
+#pragma unroll
+                for (int o = NQ * REP; o < LPK; o <<= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, o));
+                const bool move = cmax > m_own + 8.0f || m_own == -INFINITY;
+                mn = move ? cmax : m_own;
+                const float corr_own = move ? fast_exp2(m_own - (mn == -INFINITY ? 0.0f : mn)) : 1.0f;
+                l_own *= corr_own;
 #pragma unroll
                 for (int q = 0; q < NQ; ++q) scale4(acc[q], __shfl_sync(0xffffffffu, corr_own, q * REP, LPK));
-            } else {
-                l_own += pe_own;
             }
+            const float pe_own = fast_exp2(sv - (mn == -INFINITY ? 0.0f : mn));
+            l_own += pe_own;
             m_own = mn;
 #pragma unroll
             for (int q = 0; q < NQ; ++q) {
