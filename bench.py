@@ -222,7 +222,7 @@ def main():
     ap.add_argument("--cpu-prefill-seqs", type=int, default=512)
     ap.add_argument("--cpu-decode-seqs", type=int, default=128)
     ap.add_argument("--cpu-decode-steps", type=int, default=8)
-    ap.add_argument("--workload", default="scaled", choices=["scaled", "configs", "matmul", "blocks"],
+    ap.add_argument("--workload", default="scaled", choices=["scaled", "configs", "matmul", "blocks", "long"],
                     help="scaled = the headline job (one JSON line); configs = one line per small benchmark "
                          "configuration (byte self-attention, patch attention, cross-attention, cache decode)")
     ap.add_argument("--matmul-small", action="store_true",
@@ -249,6 +249,9 @@ def main():
         return
     if args.workload == "blocks":
         run_blocks(args)
+        return
+    if args.workload == "long":
+        run_long_prefill(args)
         return
 
     import torch
@@ -327,6 +330,11 @@ def main():
 
     pre_t0 = [torch.cuda.Event(enable_timing=True) for _ in range(args.warmup + args.steps)]
 
+    # side-stream duration of the gathers of the last timed step (they overlap the decode launches)
+    last_it = args.warmup + args.steps - 1
+    g_pre = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    g_dec = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(4)]
+
     def one_step(it: int):
         with torch.cuda.stream(main_stream):
             buf = it % len(out_d2)
@@ -338,8 +346,12 @@ def main():
                 ev_pre_done.record(main_stream)
                 comm_stream.wait_event(ev_pre_done)
                 with torch.cuda.stream(comm_stream):   # prefill rows travel while decode runs
+                    if it == last_it:
+                        g_pre[0].record(comm_stream)
                     shard.gather_rows(out_p, rows_per_rank, padded=pad_p, gathered=gath_p)
                     ev_pre_gathered.record(comm_stream)
+                    if it == last_it:
+                        g_pre[1].record(comm_stream)
                 if it >= len(out_d2):
                     main_stream.wait_event(ev_gathered[buf])  # this buffer's previous rows have been sent
             dec_t0[it].record(main_stream)
@@ -350,8 +362,12 @@ def main():
                     ev_chunk[c].record(main_stream)
                     comm_stream.wait_event(ev_chunk[c])
                     with torch.cuda.stream(comm_stream):
+                        if it == last_it:
+                            g_dec[c][0].record(comm_stream)
                         dist.all_gather_into_tensor(gath_d[c].view(-1, E),
                                                     out_d2[buf][c * chunk_steps:(c + 1) * chunk_steps].view(-1, E))
+                        if it == last_it:
+                            g_dec[c][1].record(comm_stream)
                         if c == n_chunks - 1:
                             ev_gathered[buf].record(comm_stream)
             dec_t1[it].record(main_stream)
@@ -388,6 +404,13 @@ def main():
         lt = torch.tensor([launches], device=dev, dtype=torch.int64)
         dist.all_reduce(lt)
         launches = int(lt[0])
+    gather = None
+    if world > 1:
+        gather = {"prefill_ms": g_pre[0].elapsed_time(g_pre[1]),
+                  "decode_chunk_ms": [g_dec[c][0].elapsed_time(g_dec[c][1]) for c in range(n_chunks)],
+                  "prefill_bytes_gathered": int(world * max_rows * E * 4),
+                  "decode_bytes_gathered_per_chunk": int(world * chunk_steps * B * N_NEW * E * 4),
+                  "note": "rank 0, last timed step, on the side stream while the decode launches run"}
     ms_per_step = ms / args.steps
     total_bytes = job_bytes(total_rows, args.batch, args.decode_steps)
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
@@ -434,6 +457,7 @@ def main():
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic", "config": workload_config(args, total_rows),
             "roofline": roofline, "prefill": prefill, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "host_binding": numa,
+            "gather": gather,
             "job_bytes": total_bytes,
         }
         emit(line)
@@ -460,7 +484,7 @@ def run_small_configs(args):
         for _ in range(max(3, args.warmup)):
             fn()
         times = []
-        for _ in range(max(args.steps, 10)):
+        for _ in range(max(args.steps, 20)):
             flush.zero_()
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
@@ -468,11 +492,15 @@ def run_small_configs(args):
             t1.record()
             torch.cuda.synchronize()
             times.append(t0.elapsed_time(t1))
-        return statistics.median(times)
+        times.sort()
+        return statistics.median(times), times[min(len(times) - 1, int(0.9 * len(times)))]
 
-    def report(name, ms, nbytes, cpu_s, err, extra=None):
-        line = {"workload": name, "ms": ms, "algorithmic_bytes": nbytes, "GB/s": nbytes / ms / 1e6,
-                "frac_of_hbm_peak": nbytes / ms / 1e6 / peak, "cpu_reference_ms": cpu_s * 1e3,
+    def report(name, t, nbytes, flops, cpu_s, err, extra=None):
+        ms, p90 = t
+        line = {"workload": name, "ms": ms, "ms_p90": p90, "iterations": max(args.steps, 20),
+                "algorithmic_bytes": nbytes, "GB/s": nbytes / ms / 1e6,
+                "frac_of_hbm_peak": nbytes / ms / 1e6 / peak, "algorithmic_flops": flops,
+                "TFLOP/s": flops / ms / 1e9, "cpu_reference_ms": cpu_s * 1e3,
                 "cpu_cores": ob.host_cores(), "max_abs_err": err, "l2": "flushed between iterations"}
         line.update(extra or {})
         emit(line)
@@ -487,9 +515,11 @@ def run_small_configs(args):
                                precision=prec)
             ms = timed(lambda: ops.attn_forward(b))
             if prec == L.PREC_FP32:
-                want, _, cpu_s = oracle_forward(case)
+                want, masks, cpu_s = oracle_forward(case)
+                # 4 x head_dim flop per allowed (query, key) pair and head
+                flops = 4 * case.head_dim * case.num_heads * sum(int((m == 0).sum()) for m in masks)
             err = float(np.abs(out.cpu().numpy() - want).max())
-            report(case.name + tag, ms, case.algorithmic_bytes(), cpu_s, err)
+            report(case.name + tag, ms, case.algorithmic_bytes(), flops, cpu_s, err)
             if case.mask.group_rule in (L.GROUP_PATCH_ENC, L.GROUP_PATCH_DEC):
                 break   # row kernel: one precision
     for case in (workloads.c4_decode(), workloads.c4_block_verify()):
@@ -503,7 +533,65 @@ def run_small_configs(args):
         ms = timed(lambda: ops.attn_decode(d, ws))
         want, cpu_s = oracle_decode(case)
         err = float(np.abs(out.cpu().numpy() - want).max())
-        report(case.name, ms, case.algorithmic_bytes(), cpu_s, err, {"splits": int(d.splits)})
+        n, lens = case.n_new, case.base_len.astype(np.int64)
+        pairs = int(((lens + n) * n).sum()) if case.block_mode else int(sum((lens + r + 1).sum() for r in range(n)))
+        report(case.name, ms, case.algorithmic_bytes(), 4 * case.head_dim * case.num_heads * pairs, cpu_s, err,
+               {"splits": int(d.splits)})
+
+
+def run_long_prefill(args):
+    """Causal byte self-attention over long sequences (16 heads x 64, 65536 rows in all): the shape
+    where the prefill is bound by the tensor pipe rather than by HBM. One line per sequence length,
+    mask, kernel and precision with device time, TFLOP/s of the allowed (query, key) pairs
+    (4 x head_dim flop each) and the fraction of the measured dense bf16 peak. A sample of rows is
+    checked against an fp64 softmax of the same tensors computed with torch."""
+    import torch
+    from fblt_b200 import lib as L
+    from fblt_b200 import ops
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peaks = json.loads(peaks_file.read_text()) if peaks_file.exists() else {}
+    bf16 = float(peaks.get("bf16_tflops", 1590.0))
+    g = torch.Generator(device="cuda").manual_seed(5)
+    total = 65536
+    for T, window in ((2048, 0), (8192, 0), (8192, 512)):
+        B = total // T
+        qkv = torch.randn((total, 3 * E), device="cuda", generator=g) * 0.125
+        q, k, v = qkv[:, 0:E], qkv[:, E:2 * E], qkv[:, 2 * E:]
+        out = torch.empty((total, E), device="cuda")
+        cu = np.arange(B + 1, dtype=np.int32) * T
+        w = window if window else T
+        pairs = B * (w * (w + 1) // 2 + (T - w) * w)       # keys max(0, i-w+1) .. i for every row i
+        flop = 4.0 * HD * pairs * H
+        rows = torch.tensor([0, 1, T // 3, T - 1, total - T + 777, total - 1], device="cuda")
+        for impl, iname in ((L.IMPL_TCGEN05, "tcgen05"), (L.IMPL_TILE, "mma.sync")):
+            for prec, pname in ((L.PREC_FP32, "fp32x3"), (L.PREC_TF32, "tf32")):
+                b = ops.make_batch(q, k, v, out, cu, cu, H, HD, SCALE,
+                                   ops.MaskConfig(is_causal=True, sliding_window=window), impl=impl, precision=prec)
+                for _ in range(3):
+                    ops.attn_forward(b)
+                n = max(args.steps, 5)
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                t0.record()
+                for _ in range(n):
+                    ops.attn_forward(b)
+                t1.record()
+                torch.cuda.synchronize()
+                ms = t0.elapsed_time(t1) / n
+                err = 0.0
+                for r in rows.tolist():
+                    s0, i = (r // T) * T, r % T
+                    lo = max(0, i - w + 1)
+                    kk = k[s0 + lo:s0 + i + 1].double().view(-1, H, HD)
+                    vv = v[s0 + lo:s0 + i + 1].double().view(-1, H, HD)
+                    sc = torch.einsum("hd,jhd->hj", q[r].double().view(H, HD), kk) * SCALE
+                    want = torch.einsum("hj,jhd->hd", torch.softmax(sc, dim=1), vv).reshape(E)
+                    err = max(err, float((out[r].double() - want).abs().max()))
+                emit({"workload": f"long_prefill_T{T}" + (f"_w{window}" if window else ""), "kernel": iname,
+                      "precision": pname, "sequences": B, "ms": ms, "TFLOP/s": flop / ms / 1e9,
+                      "frac_of_bf16_peak": flop / ms / 1e9 / bf16, "algorithmic_bytes": 4 * total * E * 4,
+                      "GB/s": 4 * total * E * 4 / ms / 1e6, "max_abs_err_sampled_rows": err,
+                      "inputs": "1.07 GB, larger than L2"})
 
 
 def run_matmul(args):
