@@ -227,6 +227,9 @@ def main():
                          "configuration (byte self-attention, patch attention, cross-attention, cache decode)")
     ap.add_argument("--matmul-small", action="store_true",
                     help="matmul workload: only the decode-step shapes (8192 rows), for profiler captures")
+    ap.add_argument("--gather-chunks", type=int, default=4,
+                    help="N > 1: the decode rows of a step are gathered in this many pieces while the launches go on")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0, help="N > 1: cap on the CTAs of an NCCL gather (0 = NCCL's default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
     args = ap.parse_args()
@@ -272,6 +275,9 @@ def main():
     full_affinity = os.sched_getaffinity(0)
     numa = shard.bind_to_device_numa_node(local_rank)
     if world > 1:
+        if args.nccl_max_ctas > 0:
+            # the gathers share the GPU with the decode launches: fewer NCCL CTAs leave more SMs to them
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_max_ctas))
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
 
@@ -314,7 +320,7 @@ def main():
         gath_p = torch.empty((world, max_rows, E), device=dev)
         # the decode rows of a step travel in chunks of a quarter of the decode launches, so that
         # only the last chunk's gather is still under way when the step's compute ends
-        n_chunks = 4 if args.decode_steps % 4 == 0 else 1
+        n_chunks = args.gather_chunks if args.decode_steps % args.gather_chunks == 0 else 1
         chunk_steps = args.decode_steps // n_chunks
         gath_d = [torch.empty((world, chunk_steps * B * N_NEW, E), device=dev) for _ in range(n_chunks)]
         ev_chunk = [torch.cuda.Event() for _ in range(n_chunks)]
@@ -333,7 +339,7 @@ def main():
     # side-stream duration of the gathers of the last timed step (they overlap the decode launches)
     last_it = args.warmup + args.steps - 1
     g_pre = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    g_dec = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(4)]
+    g_dec = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(args.decode_steps)]
 
     def one_step(it: int):
         with torch.cuda.stream(main_stream):
@@ -537,6 +543,69 @@ def run_small_configs(args):
         pairs = int(((lens + n) * n).sum()) if case.block_mode else int(sum((lens + r + 1).sum() for r in range(n)))
         report(case.name, ms, case.algorithmic_bytes(), 4 * case.head_dim * case.num_heads * pairs, cpu_s, err,
                {"splits": int(d.splits)})
+    run_decode_loop(args, torch, ops, emit)
+
+
+def run_decode_loop(args, torch, ops, emit_line):
+    """The decode-step block (QKV matmul, rotary + write-through + cache attention, output matmul) at the
+    cache-decode configuration (256 sequences, 4 heads x 64, one new row per step), 32 steps in a row:
+    launched step by step from the host, and as one captured CUDA graph replayed. Lengths live in
+    device memory, so the same graph serves the growing caches."""
+    Hc, n, batch, cache_rows, steps = 4, 1, 256, 640, 32
+    Ec = Hc * HD
+    g = torch.Generator(device="cuda").manual_seed(3)
+    kc = torch.randn((batch, cache_rows, Ec), device="cuda", generator=g)
+    vc = torch.randn((batch, cache_rows, Ec), device="cuda", generator=g)
+    base0 = (64 + torch.randint(0, 449, (batch,), device="cuda", generator=g)).to(torch.int32)
+    base = base0.clone()
+    w_qkv = ops.PackedWeights(torch.randn((Ec, 3 * Ec), device="cuda", generator=g) / 16.0)
+    w_proj = ops.PackedWeights(torch.randn((Ec, Ec), device="cuda", generator=g) / 16.0)
+    half = torch.arange(HD // 2, device="cuda", dtype=torch.float32)
+    ang = torch.arange(cache_rows, device="cuda", dtype=torch.float32)[:, None] * (500000.0 ** (-2.0 * half / HD))[None, :]
+    plan = ops.KvStepPlan(w_qkv, w_proj, kc, vc, base, Hc, n, rope_cos=torch.cos(ang).contiguous(),
+                          rope_sin=torch.sin(ang).contiguous())
+    plan.x.copy_(torch.randn((batch * n, Ec), device="cuda", generator=g))
+
+    def eager():
+        base.copy_(base0)
+        for _ in range(steps):
+            plan.run()
+            base.add_(n)
+
+    eager()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(steps):
+                plan.run(side)
+                base.add_(n)
+    torch.cuda.current_stream().wait_stream(side)
+
+    def replay():
+        base.copy_(base0)
+        graph.replay()
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(20):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0.record()
+            fn()
+            t1.record()
+            torch.cuda.synchronize()
+            ts.append(t0.elapsed_time(t1))
+        return statistics.median(ts)
+
+    e_ms, g_ms = timed(eager), timed(replay)
+    emit_line({"workload": "c4_decode_step_block_loop", "sequences": batch, "steps": steps, "launches_per_step": 4,
+               "host_launched_us_per_step": e_ms * 1e3 / steps, "cuda_graph_us_per_step": g_ms * 1e3 / steps,
+               "note": "caches stay in L2 between steps, as in a real decode loop"})
 
 
 def run_long_prefill(args):

@@ -406,6 +406,44 @@ def kv_self_attention_step(x: torch.Tensor, w_qkv: PackedWeights, w_proj: Packed
     return out
 
 
+class KvStepPlan:
+    """The decode-step block with every buffer allocated up front: run() only enqueues the three
+    launches (no allocation, no synchronisation), so a loop of steps can be captured once in a CUDA
+    graph and replayed while the caches grow -- the cache lengths are read from device memory
+    (base_len), not baked into the launches. x is the static input [batch*n_new, E]; out the static
+    output. max_len must bound base_len + n_new over every replay (default: the cache capacity)."""
+
+    def __init__(self, w_qkv: PackedWeights, w_proj: PackedWeights, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 base_len: torch.Tensor, num_heads: int, n_new: int, *, rope_cos: Optional[torch.Tensor] = None,
+                 rope_sin: Optional[torch.Tensor] = None, block_mode: bool = False, window: int = 0,
+                 max_len: int = 0, precision: int = L.PREC_FP32):
+        batch, E, dev = int(k_cache.shape[0]), int(k_cache.shape[2]), k_cache.device
+        rows = batch * n_new
+        self.x = torch.zeros(rows, E, dtype=torch.float32, device=dev)
+        self.out = torch.empty(rows, E, dtype=torch.float32, device=dev)
+        self._qkv = torch.empty(rows, 3 * E, dtype=torch.float32, device=dev)
+        self._comb = torch.empty(rows, E, dtype=torch.float32, device=dev)
+        self._ws = torch.empty(8 << 20, dtype=torch.uint8, device=dev)
+        self._keep = [w_qkv, w_proj, k_cache, v_cache, base_len, rope_cos, rope_sin]
+        d = self.desc = L.KvStepDesc()
+        d.batch, d.num_heads, d.head_dim, d.n_new = batch, num_heads, E // num_heads, n_new
+        d.block_mode, d.window, d.precision = int(block_mode), window, precision
+        d.max_len = max_len or int(k_cache.shape[1])
+        d.base_len = base_len.data_ptr()
+        d.k_cache, d.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+        d.cache_seq_stride, d.cache_row_stride = k_cache.stride(0), k_cache.stride(1)
+        d.input, d.input_stride = self.x.data_ptr(), self.x.stride(0)
+        d.packed_qkv, d.packed_proj = w_qkv.buf.data_ptr(), w_proj.buf.data_ptr()
+        d.output, d.output_stride = self.out.data_ptr(), self.out.stride(0)
+        d.qkv_work, d.combined_work = self._qkv.data_ptr(), self._comb.data_ptr()
+        d.workspace, d.workspace_bytes = self._ws.data_ptr(), self._ws.numel()
+        if rope_cos is not None:
+            d.rope_cos, d.rope_sin = rope_cos.data_ptr(), rope_sin.data_ptr()
+
+    def run(self, stream=None) -> None:
+        L.check(L.load().fblt_kv_self_attention_step(C.byref(self.desc), _stream_ptr(stream)))
+
+
 def unmask_step(logits: torch.Tensor, masked: torch.Tensor, tokens: torch.Tensor, strategy: int, threshold: float):
     """One unmask round over a batch of candidates. logits [batch*B, V] float32, masked/tokens
     [batch, B] uint8 (updated in place). Returns (sel [batch] int64 bit masks, conf [batch,B],

@@ -147,6 +147,77 @@ def test_kv_decode_step_self_attention_block(cuda_lib, block_mode, window):
         assert_close(vc[b, rows].cpu().numpy(), case.v_new[b * n:(b + 1) * n], f"cache V rows of sequence {b}")
 
 
+def test_kv_decode_steps_replayed_from_a_cuda_graph(cuda_lib):
+    """Eight decode steps captured once (step + length update) and replayed while the caches grow:
+    outputs and caches must equal the eager loop bit for bit, because the launches read the cache
+    lengths from device memory and allocate nothing."""
+    H, hd, n, batch, cache_rows, steps = 4, 64, 4, 6, 128, 8
+    E = H * hd
+    rng = np.random.default_rng(77)
+    base0 = np.array([0, 3, 17, 40, 64, 90], dtype=np.int32)
+    xs = torch.from_numpy(rng.standard_normal((steps, batch * n, E)).astype(np.float32)).cuda()
+    wq_h = (rng.standard_normal((E, 3 * E)) / np.sqrt(E)).astype(np.float32)
+    wp_h = (rng.standard_normal((E, E)) / np.sqrt(E)).astype(np.float32)
+    w_qkv, w_proj = ops.PackedWeights(torch.from_numpy(wq_h).cuda()), ops.PackedWeights(torch.from_numpy(wp_h).cuda())
+    csn, snn = ob.rope_tables(cache_rows, hd, use_ref=False)
+    cs, sn = torch.from_numpy(csn).cuda(), torch.from_numpy(snn).cuda()
+    cache0 = torch.from_numpy(rng.standard_normal((2, batch, cache_rows, E)).astype(np.float32)).cuda()
+
+    def fresh():
+        kc, vc = cache0[0].clone(), cache0[1].clone()
+        base = torch.from_numpy(base0).cuda()
+        return kc, vc, base, ops.KvStepPlan(w_qkv, w_proj, kc, vc, base, H, n, rope_cos=cs, rope_sin=sn)
+
+    # eager loop
+    kc_e, vc_e, base_e, plan_e = fresh()
+    outs_e = []
+    for t in range(steps):
+        plan_e.x.copy_(xs[t])
+        plan_e.run()
+        base_e.add_(n)
+        outs_e.append(plan_e.out.clone())
+    torch.cuda.synchronize()
+
+    # captured once, replayed
+    kc_g, vc_g, base_g, plan_g = fresh()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        plan_g.x.copy_(xs[0])
+        with torch.cuda.graph(graph, stream=side):
+            plan_g.run(side)
+            base_g.add_(n)
+    torch.cuda.current_stream().wait_stream(side)
+    # the capture itself ran nothing: caches and lengths are still the initial ones
+    assert torch.equal(base_g.cpu(), torch.from_numpy(base0))
+    outs_g = []
+    for t in range(steps):
+        plan_g.x.copy_(xs[t])
+        graph.replay()
+        outs_g.append(plan_g.out.clone())
+    torch.cuda.synchronize()
+    assert L.load().fblt_tcgen05_error() == 0
+    assert torch.equal(base_g.cpu(), torch.from_numpy(base0 + steps * n))
+    for t in range(steps):
+        assert torch.equal(outs_g[t], outs_e[t]), f"step {t}: graph replay differs from the eager launch"
+    assert torch.equal(kc_g, kc_e) and torch.equal(vc_g, vc_e)
+    # and the last step agrees with the CPU chain over the cache the loop has built
+    from helpers import oracle_decode
+    from fblt_b200 import workloads
+    base_last = base0 + (steps - 1) * n
+    case = workloads.decode_case(1, batch, H, n, False, lens=base_last, cache_rows=cache_rows)
+    case.k_cache, case.v_cache = kc_e.cpu().numpy(), vc_e.cpu().numpy()
+    qkv = ob.matmul(xs[-1].cpu().numpy(), wq_h, use_ref=False)
+    pos = (base_last[:, None] + np.arange(n)[None, :]).reshape(-1)
+    case.q = ob.rope_apply(qkv[:, :E], csn[pos], snn[pos], H, hd, use_ref=False)
+    case.k_new = ob.rope_apply(qkv[:, E:2 * E], csn[pos], snn[pos], H, hd, use_ref=False)
+    case.v_new = np.ascontiguousarray(qkv[:, 2 * E:])
+    combined, _ = oracle_decode(case, ref=False)
+    want = ob.matmul(combined, wp_h, use_ref=False)
+    assert_close(outs_e[-1].cpu().numpy(), want, "last replayed step against the CPU chain")
+
+
 def test_blocks_against_committed_fixtures(cuda_lib):
     """The committed outputs of the reference's own CPU code (tests/golden/make_golden.py) for the
     projection matmul and the two attention blocks: no reference object code needed at run time."""
