@@ -547,6 +547,10 @@ int fblt_cross_attention_forward(const fblt_cross_desc *desc, void *stream);
  * window); output = combined * weight_proj. Cache layout and the other fields as
  * in fblt_decode_desc. workspace may be NULL (then the key range is not split).
  * Does not advance base_len. All pointers device.
+ * The call only enqueues launches on `stream` (no allocation, no wait) and the
+ * lengths are read from base_len on the device when the kernels run, so a loop
+ * of steps can be captured once in a CUDA graph and replayed while the caches
+ * grow; max_len must then bound base_len[b] + n_new over every replay.
  */
 typedef struct {
     int32_t batch, num_heads, head_dim, n_new;
