@@ -5,6 +5,8 @@
 namespace fblt {
 
 int launch_row_kernel(const fblt_attn_desc &d, cudaStream_t stream);
+int launch_rowq_kernel(const fblt_attn_desc &d, cudaStream_t stream);
+bool rowq_kernel_supports(const fblt_attn_desc &d, const char **why);
 int launch_tile_kernel(const fblt_attn_desc &d, cudaStream_t stream);
 bool tile_kernel_supports(const fblt_attn_desc &d, const char **why);
 int launch_tile5_kernel(const fblt_attn_desc &d, cudaStream_t stream);
@@ -101,6 +103,9 @@ extern "C" int fblt_attn_forward(const fblt_attn_desc *d, void *stream) {
     case FBLT_IMPL_TCGEN05:
         if (!tile5_kernel_supports(*d, &why)) return fail(FBLT_ERR_UNSUPPORTED, "%s", why);
         return launch_tile5_kernel(*d, s);
+    case FBLT_IMPL_ROW_QUAD:
+        if (!rowq_kernel_supports(*d, &why)) return fail(FBLT_ERR_UNSUPPORTED, "%s", why);
+        return launch_rowq_kernel(*d, s);
     case FBLT_IMPL_AUTO:
         // short per-row key ranges (a patch's own bytes, one latent) stay on the row kernel
         if ((d->mask.group_rule == FBLT_GROUP_NONE || d->mask.group_rule == FBLT_GROUP_PATCH_LEQ) && d->max_k >= 32) {
@@ -108,6 +113,9 @@ extern "C" int fblt_attn_forward(const fblt_attn_desc *d, void *stream) {
             if (d->max_q >= 96 && tile5_kernel_supports(*d, &why)) return launch_tile5_kernel(*d, s);
             if (tile_kernel_supports(*d, &why)) return launch_tile_kernel(*d, s);
         }
+        // what is left has short key ranges per row (or needs the general kernel): four lanes per row
+        // where the shape allows, a warp per row otherwise
+        if (d->max_k <= 4096 && rowq_kernel_supports(*d, &why)) return launch_rowq_kernel(*d, s);
         return launch_row_kernel(*d, s);
     default: return fail(FBLT_ERR_ARG, "attn: unknown impl %d", d->impl);
     }

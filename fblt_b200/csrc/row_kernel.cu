@@ -135,6 +135,209 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
     }
 }
 
+// ---- four lanes per row ---------------------------------------------------------------------
+// The same per-row attention for the shapes where a row has a handful of keys (encoder
+// cross-attention: a patch's own bytes; decoder cross-attention: one latent): a warp per row is
+// then one long chain of dependent round trips (row tables -> range -> q -> keys) with 32 lanes
+// waiting on it. Here a row belongs to 4 lanes (head_dim / 4 columns each, 16-byte loads), so a
+// warp keeps 8 independent rows in flight and a CTA 32. Range rules only (explicit group ids and
+// the rotary embedding stay on the warp-per-row kernel).
+constexpr int kQuadRows = 32;     // rows per CTA of 128 threads
+constexpr int kQuadLongRow = 16;  // rows with more keys than this are walked by the whole warp
+
+// Running softmax state of one row (or of one quad's share of a long row).
+template <int NV>
+struct QuadState {
+    float m, l;
+    float4 acc[NV];
+    __device__ __forceinline__ void reset() {
+        m = -INFINITY;
+        l = 0.0f;
+#pragma unroll
+        for (int t = 0; t < NV; ++t) acc[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __device__ __forceinline__ void take(float sc, const float4 (&vv)[NV]) {
+        if (!finite_f(sc)) return; // non-finite score: weight 0
+        const float mn = fmaxf(m, sc);
+        const float corr = exp2f(m - mn), pe = exp2f(sc - mn);
+        l = l * corr + pe;
+#pragma unroll
+        for (int t = 0; t < NV; ++t) {
+            acc[t].x = acc[t].x * corr + pe * vv[t].x;
+            acc[t].y = acc[t].y * corr + pe * vv[t].y;
+            acc[t].z = acc[t].z * corr + pe * vv[t].z;
+            acc[t].w = acc[t].w * corr + pe * vv[t].w;
+        }
+        m = mn;
+    }
+};
+
+// Keys j and j + 1 (each if below hi) of one row: one round trip for their K and V pieces, the two
+// scores summed over the row's four lanes, both folded into st. Every lane of the warp calls this
+// together (full-mask shuffles); lanes without a key load nothing.
+template <int NV>
+__device__ __forceinline__ void quad_key_pair(QuadState<NV> &st, const float4 (&qv)[NV], const float *kb, const float *vb,
+                                              int64_t k_stride, int64_t v_stride, int j, int hi) {
+    const bool one = j < hi, two = j + 1 < hi;
+    const float *k0p = kb + (int64_t)(one ? j : 0) * k_stride, *v0p = vb + (int64_t)(one ? j : 0) * v_stride;
+    const float *k1p = k0p + (two ? k_stride : 0), *v1p = v0p + (two ? v_stride : 0);
+    float4 ka[NV], va[NV], kc[NV], vc[NV];
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+        const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+        ka[t] = one ? __ldg(reinterpret_cast<const float4 *>(k0p + t * 16)) : z;
+        va[t] = one ? __ldg(reinterpret_cast<const float4 *>(v0p + t * 16)) : z;
+        kc[t] = two ? __ldg(reinterpret_cast<const float4 *>(k1p + t * 16)) : z;
+        vc[t] = two ? __ldg(reinterpret_cast<const float4 *>(v1p + t * 16)) : z;
+    }
+    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+        s0 += qv[t].x * ka[t].x + qv[t].y * ka[t].y + qv[t].z * ka[t].z + qv[t].w * ka[t].w;
+        s1 += qv[t].x * kc[t].x + qv[t].y * kc[t].y + qv[t].z * kc[t].z + qv[t].w * kc[t].w;
+    }
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+    if (one) st.take(s0, va);
+    if (two) st.take(s1, vc);
+}
+
+// LONG = false drops the long-row pass (and its registers) for rules whose ranges cannot be long.
+template <int HD, bool LONG>
+__global__ void __launch_bounds__(kQuadRows * 4) rowq_attn_kernel(fblt_attn_desc d) {
+    constexpr int NV = HD / 16; // 16-byte pieces per lane; piece t of lane dl covers columns (t * 4 + dl) * 4 ..+3
+    const int b = blockIdx.z, h = blockIdx.y;
+    const int q0 = d.cu_q[b], nq = d.cu_q[b + 1] - q0;
+    if ((int)blockIdx.x * kQuadRows >= nq) return;
+    const int k0 = d.cu_k[b], nk = d.cu_k[b + 1] - k0;
+    const int lane = threadIdx.x & 31, dl = lane & 3, qd = lane >> 2;
+    const int i = blockIdx.x * kQuadRows + (threadIdx.x >> 2);
+    const bool valid = i < nq;
+
+    int lo = 0, hi = 0;
+    if (valid) {
+        const SeqMask s = resolve_mask(d.mask, b, q0, k0, nq, nk);
+        row_range(s, i, lo, hi);
+    }
+    const float qscale = d.scale * kLog2e;
+    const float *qrow = d.q + (int64_t)(q0 + (valid ? i : 0)) * d.q_stride + (int64_t)h * HD + dl * 4;
+    float4 qv[NV];
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+        qv[t] = valid ? __ldg(reinterpret_cast<const float4 *>(qrow + t * 16)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        qv[t].x *= qscale;
+        qv[t].y *= qscale;
+        qv[t].z *= qscale;
+        qv[t].w *= qscale;
+    }
+    QuadState<NV> st;
+    st.reset();
+    const float *kb = d.k + (int64_t)k0 * d.k_stride + (int64_t)h * HD + dl * 4;
+    const float *vb = d.v + (int64_t)k0 * d.v_stride + (int64_t)h * HD + dl * 4;
+
+    // Short rows: two keys per round trip, the eight rows of a warp in lockstep (trip count = the
+    // longest short row of the warp). Shuffles under per-row masks would instead split the warp
+    // into eight serial strands.
+    const bool long_row = LONG && hi - lo > kQuadLongRow;
+    const int trips = warp_max(long_row ? 0 : (hi - lo + 1) >> 1);
+    for (int it = 0; it < trips; ++it) quad_key_pair<NV>(st, qv, kb, vb, d.k_stride, d.v_stride, lo + 2 * it, long_row ? lo : hi);
+
+    // Long rows (a patch that absorbed the rest of its sequence): one at a time, the eight quads
+    // of the warp take every eighth key pair, then their partial softmax states are merged.
+    unsigned pending = LONG ? __ballot_sync(0xffffffffu, long_row && dl == 0) : 0u;
+    while (LONG && pending) {
+        const int src = __ffs(pending) - 1; // lane 0 of the owning quad
+        pending &= pending - 1;
+        const int rlo = __shfl_sync(0xffffffffu, lo, src), rhi = __shfl_sync(0xffffffffu, hi, src);
+        float4 rq[NV];
+#pragma unroll
+        for (int t = 0; t < NV; ++t) {
+            rq[t].x = __shfl_sync(0xffffffffu, qv[t].x, src + dl);
+            rq[t].y = __shfl_sync(0xffffffffu, qv[t].y, src + dl);
+            rq[t].z = __shfl_sync(0xffffffffu, qv[t].z, src + dl);
+            rq[t].w = __shfl_sync(0xffffffffu, qv[t].w, src + dl);
+        }
+        QuadState<NV> part;
+        part.reset();
+        const int trips8 = (rhi - rlo + 15) >> 4; // the same for every lane: 16 keys per warp trip
+        for (int it = 0; it < trips8; ++it)
+            quad_key_pair<NV>(part, rq, kb, vb, d.k_stride, d.v_stride, rlo + 16 * it + 2 * qd, rhi);
+        // merge the eight partial states (each step pairs quads 1, 2 and 4 apart); afterwards every
+        // quad holds the row's state
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, part.m, off), ol = __shfl_xor_sync(0xffffffffu, part.l, off);
+            const float mn = fmaxf(part.m, om);
+            const float ca = part.m == -INFINITY ? 0.0f : exp2f(part.m - mn), cb = om == -INFINITY ? 0.0f : exp2f(om - mn);
+            part.l = part.l * ca + ol * cb;
+#pragma unroll
+            for (int t = 0; t < NV; ++t) {
+                part.acc[t].x = part.acc[t].x * ca + __shfl_xor_sync(0xffffffffu, part.acc[t].x, off) * cb;
+                part.acc[t].y = part.acc[t].y * ca + __shfl_xor_sync(0xffffffffu, part.acc[t].y, off) * cb;
+                part.acc[t].z = part.acc[t].z * ca + __shfl_xor_sync(0xffffffffu, part.acc[t].z, off) * cb;
+                part.acc[t].w = part.acc[t].w * ca + __shfl_xor_sync(0xffffffffu, part.acc[t].w, off) * cb;
+            }
+            part.m = mn;
+        }
+        if (qd == (src >> 2)) st = part;
+    }
+
+    if (valid) {
+        const float inv = st.l > 0.0f ? 1.0f / st.l : 0.0f; // rows without keys give zeros
+        float *orow = d.out + (int64_t)(q0 + i) * d.out_stride + (int64_t)h * HD + dl * 4;
+#pragma unroll
+        for (int t = 0; t < NV; ++t)
+            *reinterpret_cast<float4 *>(orow + t * 16) =
+                make_float4(st.acc[t].x * inv, st.acc[t].y * inv, st.acc[t].z * inv, st.acc[t].w * inv);
+    }
+}
+
+bool rowq_kernel_supports(const fblt_attn_desc &d, const char **why) {
+    if (d.head_dim != 32 && d.head_dim != 64) {
+        *why = "quad-lane row kernel: head_dim must be 32 or 64";
+        return false;
+    }
+    if (d.mask.group_rule == FBLT_GROUP_IDS) {
+        *why = "explicit group ids are not a key range";
+        return false;
+    }
+    if (d.rope_cos) {
+        *why = "quad-lane row kernel: no rotary embedding";
+        return false;
+    }
+    if ((d.q_stride | d.k_stride | d.v_stride | d.out_stride) & 3) {
+        *why = "row strides must be multiples of 4 elements";
+        return false;
+    }
+    if (((uintptr_t)d.q | (uintptr_t)d.k | (uintptr_t)d.v | (uintptr_t)d.out) & 15) {
+        *why = "q/k/v/out must be 16-byte aligned";
+        return false;
+    }
+    if (d.num_heads > 65535 || d.batch > 65535) {
+        *why = "batch/heads exceed 65535";
+        return false;
+    }
+    return true;
+}
+
+int launch_rowq_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
+    if (d.max_q <= 0 || d.batch <= 0) return FBLT_OK;
+    dim3 grid((d.max_q + kQuadRows - 1) / kQuadRows, d.num_heads, d.batch);
+    // the decoder's one-latent rule gives every row at most `subtokens` keys
+    const bool may_be_long = !(d.mask.group_rule == FBLT_GROUP_PATCH_DEC && d.mask.subtokens <= kQuadLongRow);
+    if (d.head_dim == 32) {
+        if (may_be_long) rowq_attn_kernel<32, true><<<grid, kQuadRows * 4, 0, stream>>>(d);
+        else rowq_attn_kernel<32, false><<<grid, kQuadRows * 4, 0, stream>>>(d);
+    } else {
+        if (may_be_long) rowq_attn_kernel<64, true><<<grid, kQuadRows * 4, 0, stream>>>(d);
+        else rowq_attn_kernel<64, false><<<grid, kQuadRows * 4, 0, stream>>>(d);
+    }
+    count_launch();
+    return check_launch("rowq_attn_kernel");
+}
+
 int launch_row_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
     if (d.head_dim > 256) return fail(FBLT_ERR_UNSUPPORTED, "row kernel: head_dim %d > 256", d.head_dim);
     if (d.max_q <= 0 || d.batch <= 0) return FBLT_OK;

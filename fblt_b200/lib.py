@@ -18,7 +18,7 @@ c_u8_p = C.POINTER(C.c_uint8)
 OK, ERR_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_CAPACITY, ERR_LIMIT = range(7)
 BACKEND_CPU, BACKEND_CUDA = 0, 1
 GROUP_NONE, GROUP_PATCH_ENC, GROUP_PATCH_DEC, GROUP_PATCH_LEQ, GROUP_IDS = range(5)
-IMPL_AUTO, IMPL_ROW, IMPL_TILE, IMPL_TCGEN05 = range(4)
+IMPL_AUTO, IMPL_ROW, IMPL_TILE, IMPL_TCGEN05, IMPL_ROW_QUAD = range(5)
 PREC_FP32, PREC_TF32 = 0, 1
 
 

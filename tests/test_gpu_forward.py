@@ -28,6 +28,8 @@ def check(case: ForwardCase, kernels=KERNELS):
     want, masks, _ = oracle_forward(case)
     if kernels is KERNELS and case.head_dim == 64 and case.mask.group_rule != L.GROUP_IDS:
         kernels = KERNELS + T5_KERNELS          # the tcgen05 kernel takes head_dim 64
+    if kernels[0][0] == L.IMPL_ROW and case.head_dim in (32, 64) and case.mask.group_rule != L.GROUP_IDS:
+        kernels = kernels + [(L.IMPL_ROW_QUAD, L.PREC_FP32)]   # four lanes per row: same shapes, range rules
     for impl, prec in kernels:
         got, _ = forward_gpu(case, impl, prec)
         what = f"{case.name} impl={impl} prec={prec}"
@@ -254,7 +256,7 @@ def test_non_finite_scores_weigh_zero(cuda_lib):
     case = dataclasses.replace(case, k=k)
     want, _, _ = oracle_forward(case)
     assert np.isfinite(want).all()
-    for impl, prec in KERNELS + T5_KERNELS:
+    for impl, prec in KERNELS + T5_KERNELS + [(L.IMPL_ROW_QUAD, L.PREC_FP32)]:
         got, _ = forward_gpu(case, impl, prec)
         assert np.isfinite(got).all(), (impl, prec)
         tol = dict(atol=TF32_ATOL, rtol=TF32_RTOL) if prec == L.PREC_TF32 else {}
