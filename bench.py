@@ -17,6 +17,7 @@ host<->device copies inside the timed region.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -278,7 +279,8 @@ def main():
         if args.nccl_max_ctas > 0:
             # the gathers share the GPU with the decode launches: fewer NCCL CTAs leave more SMs to them
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_max_ctas))
-        dist.init_process_group("nccl", device_id=dev)
+        # a collective that stays enqueued past this deadline is aborted by the process group's watchdog
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
 
     # ---- this rank's shard ---------------------------------------------------
@@ -383,6 +385,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if world > 1:
+        # every rank has built its shard: check in on the host before the first gather is enqueued,
+        # so that a rank that died or fell behind during setup is named here instead of stalling a collective
+        shard.rendezvous(shard.default_store(), rank, world, "bench-setup", deadline_s=240.0)
     for it in range(args.warmup):
         one_step(it)
     barrier()

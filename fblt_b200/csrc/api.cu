@@ -2,6 +2,9 @@
 // host-side patch boundary helpers.
 #include "common.cuh"
 
+#include <stdlib.h>
+#include <string.h>
+
 namespace fblt {
 
 int launch_row_kernel(const fblt_attn_desc &d, cudaStream_t stream);
@@ -88,11 +91,39 @@ __global__ void mask_materialize_kernel(fblt_attn_desc d, int b, float *out) {
 
 } // namespace fblt
 
-extern "C" int fblt_attn_forward(const fblt_attn_desc *d, void *stream) {
+// Environment toggles for callers that pass FBLT_IMPL_AUTO / FBLT_PREC_FP32 (the defaults), in the
+// manner of the reference's BLT_FLASH_ATTN switch (models/attention.c:111-119):
+//   FBLT_ATTN_IMPL      = auto | row | quad | tile | tcgen05
+//   FBLT_ATTN_PRECISION = fp32 | tf32
+// Read at every call, so a host program may change them between calls. Unknown values are an error.
+static int env_overrides(fblt_attn_desc &d) {
+    if (d.impl == FBLT_IMPL_AUTO) {
+        if (const char *e = getenv("FBLT_ATTN_IMPL")) {
+            if (!strcmp(e, "row")) d.impl = FBLT_IMPL_ROW;
+            else if (!strcmp(e, "quad")) d.impl = FBLT_IMPL_ROW_QUAD;
+            else if (!strcmp(e, "tile")) d.impl = FBLT_IMPL_TILE;
+            else if (!strcmp(e, "tcgen05")) d.impl = FBLT_IMPL_TCGEN05;
+            else if (strcmp(e, "auto") && *e) return fblt::fail(FBLT_ERR_ARG, "FBLT_ATTN_IMPL=%s (auto, row, quad, tile, tcgen05)", e);
+        }
+    }
+    if (d.precision == FBLT_PREC_FP32) {
+        if (const char *e = getenv("FBLT_ATTN_PRECISION")) {
+            if (!strcmp(e, "tf32")) d.precision = FBLT_PREC_TF32;
+            else if (strcmp(e, "fp32") && *e) return fblt::fail(FBLT_ERR_ARG, "FBLT_ATTN_PRECISION=%s (fp32, tf32)", e);
+        }
+    }
+    return FBLT_OK;
+}
+
+extern "C" int fblt_attn_forward(const fblt_attn_desc *desc, void *stream) {
     using namespace fblt;
-    int st = validate_desc(d);
+    int st = validate_desc(desc);
     if (st != FBLT_OK) return st;
-    if (d->batch == 0 || d->max_q <= 0) return FBLT_OK;
+    if (desc->batch == 0 || desc->max_q <= 0) return FBLT_OK;
+    fblt_attn_desc local = *desc;
+    st = env_overrides(local);
+    if (st != FBLT_OK) return st;
+    const fblt_attn_desc *d = &local;
     cudaStream_t s = (cudaStream_t)stream;
     const char *why = "";
     switch (d->impl) {

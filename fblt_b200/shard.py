@@ -56,6 +56,65 @@ def unpad(gathered: torch.Tensor, rows_per_rank: List[int]) -> torch.Tensor:
     return torch.cat([gathered[r, :n] for r, n in enumerate(rows_per_rank)], dim=0)
 
 
+# ---- host-side check-in before collectives ------------------------------------------------------
+# The reference has no failure handling beyond exit(1) (core/backend.h:13-31). With one process per
+# GPU a rank that died, raised or fell behind must be noticed on the HOST, before the others enqueue
+# a gather that would wait for it on the device: every rank checks in through the job's key-value
+# store and waits, with a deadline, for the others. No kernel or collective is involved.
+
+class RankTimeout(RuntimeError):
+    """Some ranks did not check in before the deadline. `.missing` lists them."""
+
+    def __init__(self, tag: str, missing: List[int], waited_s: float):
+        super().__init__(f"rendezvous '{tag}': ranks {missing} did not check in within {waited_s:.1f} s")
+        self.missing = missing
+
+
+class RankFailed(RuntimeError):
+    """A rank announced a failure (report_failure) instead of checking in. `.rank`, `.reason`."""
+
+    def __init__(self, tag: str, rank: int, reason: str):
+        super().__init__(f"rendezvous '{tag}': rank {rank} failed: {reason}")
+        self.rank, self.reason = rank, reason
+
+
+def _key(tag: str, kind: str, rank: int) -> str:
+    return f"fblt/{tag}/{kind}/{rank}"
+
+
+def report_failure(store, rank: int, tag: str, reason: str) -> None:
+    """Called by a rank that cannot go on (exception, bad input): the others' rendezvous(tag) raises
+    RankFailed at once instead of waiting for the deadline."""
+    store.set(_key(tag, "failed", rank), reason.encode()[:512] or b"?")
+
+
+def rendezvous(store, rank: int, world_size: int, tag: str, deadline_s: float = 30.0, poll_s: float = 0.005) -> None:
+    """Check in under `tag` and wait until every rank has. Raises RankFailed as soon as a rank has
+    announced a failure, RankTimeout (naming the absent ranks) when the deadline passes. `store` is
+    any torch.distributed store shared by the ranks (the process group's own, a TCPStore, a
+    FileStore). Tags must not be reused within a job."""
+    import time
+    store.set(_key(tag, "ready", rank), b"1")
+    others = [r for r in range(world_size) if r != rank]
+    t0 = time.monotonic()
+    while True:
+        for r in others:
+            if store.check([_key(tag, "failed", r)]):
+                raise RankFailed(tag, r, store.get(_key(tag, "failed", r)).decode(errors="replace"))
+        missing = [r for r in others if not store.check([_key(tag, "ready", r)])]
+        if not missing:
+            return
+        waited = time.monotonic() - t0
+        if waited >= deadline_s:
+            raise RankTimeout(tag, missing, waited)
+        time.sleep(poll_s)
+
+
+def default_store():
+    """The key-value store of the default process group."""
+    return dist.distributed_c10d._get_default_store()
+
+
 def parse_cpulist(text: str) -> Set[int]:
     """'0-3,8,10-11' -> {0, 1, 2, 3, 8, 10, 11} (the format of /sys/devices/system/node/*/cpulist)."""
     cpus: Set[int] = set()

@@ -270,6 +270,13 @@ typedef struct {
     const int32_t *rope_k_pos;
 } fblt_attn_desc;
 
+/*
+ * Environment toggles, read at every call, for descriptors that leave impl at FBLT_IMPL_AUTO /
+ * precision at FBLT_PREC_FP32 (the reference switches kernels the same way, BLT_FLASH_ATTN in
+ * models/attention.c:111-119): FBLT_ATTN_IMPL = auto | row | quad | tile | tcgen05,
+ * FBLT_ATTN_PRECISION = fp32 | tf32. An unknown value is FBLT_ERR_ARG; a kernel that does not
+ * take the shape is FBLT_ERR_UNSUPPORTED, as when it is named in the descriptor.
+ */
 int fblt_attn_forward(const fblt_attn_desc *desc, void *stream);
 
 /*

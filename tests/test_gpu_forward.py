@@ -241,6 +241,33 @@ def test_rotary_tables_are_validated(cuda_lib):
         ops.attn_forward(batch)
 
 
+def test_environment_toggles(cuda_lib, monkeypatch):
+    """FBLT_ATTN_IMPL / FBLT_ATTN_PRECISION steer descriptors that ask for the defaults, are read at
+    every call, and reject unknown values."""
+    case = random_case(91, [0, 40, 150], [0, 40, 150], 2, 32, MaskConfig(is_causal=True))
+    want, _, _ = oracle_forward(case)
+    for name in ("auto", "row", "quad", "tile"):
+        monkeypatch.setenv("FBLT_ATTN_IMPL", name)
+        got, _ = forward_gpu(case, L.IMPL_AUTO, L.PREC_FP32)
+        assert_close(got, want, f"FBLT_ATTN_IMPL={name}")
+    monkeypatch.setenv("FBLT_ATTN_IMPL", "tcgen05")          # honoured: that kernel does not take head_dim 32
+    with pytest.raises(L.FbltError):
+        forward_gpu(case, L.IMPL_AUTO, L.PREC_FP32)
+    got, _ = forward_gpu(case, L.IMPL_TILE, L.PREC_FP32)     # an explicit choice in the descriptor wins
+    assert_close(got, want, "explicit impl beside the toggle")
+    monkeypatch.setenv("FBLT_ATTN_IMPL", "fastest")
+    with pytest.raises(L.FbltError):
+        forward_gpu(case, L.IMPL_AUTO, L.PREC_FP32)
+    monkeypatch.setenv("FBLT_ATTN_IMPL", "tile")
+    monkeypatch.setenv("FBLT_ATTN_PRECISION", "tf32")
+    got_tf32, _ = forward_gpu(case, L.IMPL_AUTO, L.PREC_FP32)
+    assert_close(got_tf32, want, "FBLT_ATTN_PRECISION=tf32", atol=TF32_ATOL, rtol=TF32_RTOL)
+    assert np.abs(got_tf32 - want).max() > np.abs(got - want).max()   # single-pass rounding is visible
+    monkeypatch.setenv("FBLT_ATTN_PRECISION", "bf16")
+    with pytest.raises(L.FbltError):
+        forward_gpu(case, L.IMPL_AUTO, L.PREC_FP32)
+
+
 def test_non_finite_scores_weigh_zero(cuda_lib):
     """A key whose score is not finite (infinity or any NaN bit pattern in its K row) carries weight
     0 for every query, as in ops/vecmath_cpu.c:33-52; the other keys are unaffected."""

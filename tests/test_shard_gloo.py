@@ -61,6 +61,62 @@ def test_gather_rows_world_size_2():
     assert results[0][2] == results[1][2] and len(set(results[0][2])) == 2   # unequal blocks were exercised
 
 
+def _rdv_worker(rank: int, world: int, path: str, mode: str, q):
+    """mode: "ok" = both check in; "late" = rank 1 arrives after the deadline; "fail" = rank 1 announces
+    a failure; "absent" = rank 1 never comes."""
+    import time
+    store = dist.FileStore(path, world)
+    t0 = time.monotonic()
+    try:
+        if rank == 1 and mode == "absent":
+            q.put((rank, "skipped", 0.0))
+            return
+        if rank == 1 and mode == "late":
+            time.sleep(1.5)
+        if rank == 1 and mode == "fail":
+            shard.report_failure(store, rank, "step0", "input shard unreadable")
+            q.put((rank, "reported", time.monotonic() - t0))
+            return
+        shard.rendezvous(store, rank, world, "step0", deadline_s=0.5 if mode != "ok" else 20.0)
+        q.put((rank, "ok", time.monotonic() - t0))
+    except shard.RankTimeout as e:
+        q.put((rank, f"timeout{e.missing}", time.monotonic() - t0))
+    except shard.RankFailed as e:
+        q.put((rank, f"failed{e.rank}:{e.reason}", time.monotonic() - t0))
+
+
+def _run_rdv(mode: str, tmp_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    path = str(tmp_path / f"store_{mode}")
+    procs = [ctx.Process(target=_rdv_worker, args=(r, 2, path, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict()
+    for _ in procs:
+        rank, what, secs = q.get(timeout=120)
+        results[rank] = (what, secs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return results
+
+
+def test_rendezvous_before_collectives(tmp_path):
+    """A rank that is late, absent or has failed is found out on the host, within the deadline, before
+    any collective is enqueued (none is: these ranks never create a process group)."""
+    r = _run_rdv("ok", tmp_path)
+    assert r[0][0] == "ok" and r[1][0] == "ok"
+    r = _run_rdv("absent", tmp_path)
+    assert r[0][0] == "timeout[1]" and r[0][1] < 10.0
+    r = _run_rdv("late", tmp_path)
+    assert r[0][0] == "timeout[1]"            # rank 0 gave up at its deadline ...
+    assert r[1][0] == "ok"                    # ... the late rank finds rank 0's check-in and goes on alone:
+    #                                           the caller of rank 0 has already raised, which is the signal
+    r = _run_rdv("fail", tmp_path)
+    assert r[0][0] == "failed1:input shard unreadable" and r[0][1] < 10.0
+
+
 def test_parse_cpulist():
     from fblt_b200 import shard
     assert shard.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
