@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("nvcc compilation failed")
-    link = [_nvcc(), *ARCH, "-shared", "-o", str(LIB), *objs, "-lcudart"]
+    link = [_nvcc(), *ARCH, "-shared", "-o", str(LIB), *objs, "-lcudart", "-ldl"]
     subprocess.run(link, check=True)
     return LIB
 

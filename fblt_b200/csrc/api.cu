@@ -116,6 +116,7 @@ static int env_overrides(fblt_attn_desc &d) {
 }
 
 extern "C" int fblt_attn_forward(const fblt_attn_desc *desc, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_attn_forward");
     using namespace fblt;
     int st = validate_desc(desc);
     if (st != FBLT_OK) return st;

@@ -5,6 +5,7 @@
 
 #include <cuda_runtime.h>
 #include <math.h>
+#include <nvtx3/nvToolsExt.h>
 #include <stdint.h>
 #include <stdio.h>
 
@@ -15,6 +16,16 @@ namespace fblt {
 // ---- host-side status -----------------------------------------------------
 int fail(int status, const char *fmt, ...);
 void count_launch(int n = 1);
+
+// NVTX range over a host entry point, so that a timeline or an ncu --nvtx filter shows which
+// library call a launch belongs to (the reference ships no ranges, docs/PROFILING.md:60-61).
+// Header-only NVTX: without a tool attached a push / pop is a load and a branch.
+struct NvtxRange {
+    explicit NvtxRange(const char *name) { nvtxRangePushA(name); }
+    ~NvtxRange() { nvtxRangePop(); }
+    NvtxRange(const NvtxRange &) = delete;
+    NvtxRange &operator=(const NvtxRange &) = delete;
+};
 int check_launch(const char *what);
 
 #define FBLT_CUDA_TRY(expr)                                                                \

@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(kUnmaskWarps * 32)
 
 extern "C" int fblt_argmax_rows(const float *logits, int64_t stride, int32_t rows, int32_t vocab, int32_t *ids_out,
                                 void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_argmax_rows");
     using namespace fblt;
     if (!logits || !ids_out || vocab < 1 || rows < 0 || stride < vocab) return fail(FBLT_ERR_ARG, "argmax_rows: bad arguments");
     if (rows == 0) return FBLT_OK;
@@ -181,6 +182,7 @@ extern "C" int fblt_argmax_rows(const float *logits, int64_t stride, int32_t row
 extern "C" int fblt_verify_accept(uint8_t *x, int64_t x_stride, const int32_t *pred, int64_t pred_stride,
                                   const int32_t *l, const int32_t *r, const int32_t *target_len, int32_t batch,
                                   int32_t *new_len, int32_t *accepted, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_verify_accept");
     using namespace fblt;
     if (!x || !pred || !l || !r || !target_len || !new_len || batch < 0) return fail(FBLT_ERR_ARG, "verify_accept: bad arguments");
     if (batch == 0) return FBLT_OK;
@@ -194,6 +196,7 @@ extern "C" int fblt_unmask_step(const float *logits, int64_t stride, int32_t bat
                                 int32_t strategy, float threshold, uint8_t *masked, uint8_t *tokens,
                                 uint32_t *sel_out, float *conf_out, float *ent_out, int32_t *remaining_out,
                                 void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_unmask_step");
     using namespace fblt;
     if (!logits || !masked || !tokens || batch < 0 || vocab < 1 || stride < vocab)
         return fail(FBLT_ERR_ARG, "unmask_step: bad arguments");

@@ -490,6 +490,7 @@ extern "C" size_t fblt_attn_decode_workspace(const fblt_decode_desc *d) {
 }
 
 extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size_t workspace_bytes, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_attn_decode");
     using namespace fblt;
     int st = validate_decode(d);
     if (st != FBLT_OK) return st;
@@ -573,6 +574,7 @@ static int static_scratch_address(float **out) {
 extern "C" size_t fblt_attn_decode_static_capacity(void) { return fblt::kStaticScratchBytes; }
 
 extern "C" int fblt_attn_decode_static(const fblt_decode_desc *d, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_attn_decode_static");
     using namespace fblt;
     int st = validate_decode(d);
     if (st != FBLT_OK) return st;

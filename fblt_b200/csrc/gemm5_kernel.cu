@@ -420,6 +420,7 @@ extern "C" int fblt_matmul_pack_weights(const float *b, int64_t ldb, int64_t K, 
 
 extern "C" int fblt_matmul(const float *a, int64_t lda, const void *packed_b, const float *bias, float *out,
                            int64_t ldo, int64_t M, int64_t K, int64_t N, int32_t precision, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_matmul");
     using namespace fblt;
     if (M < 0 || K <= 0 || N <= 0 || lda < K || ldo < N) return fail(FBLT_ERR_ARG, "matmul: bad shape or stride");
     if (M == 0) return FBLT_OK;

@@ -142,6 +142,7 @@ static int launch_l0(const fblt_head_args *a, cudaStream_t stream) {
 } // namespace fblt
 
 extern "C" int fblt_attention_head(const fblt_head_args *args, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_attention_head");
     return fblt::launch_l0(args, (cudaStream_t)stream);
 }
 

@@ -9,6 +9,7 @@
 #include <math.h>
 
 extern "C" int fblt_mha_forward(const fblt_mha_desc *d, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_mha_forward");
     using namespace fblt;
     if (!d) return fail(FBLT_ERR_ARG, "mha: NULL descriptor");
     if (d->batch < 0 || d->num_heads <= 0 || d->head_dim <= 0 || d->total_rows < 0 || d->max_len < 0)
@@ -53,6 +54,7 @@ extern "C" int fblt_mha_forward(const fblt_mha_desc *d, void *stream) {
 // Q from query_in, K and V from kv_in (one matmul against [weight_k | weight_v]), masked
 // attention under the patch rule of the descriptor, output projection. Four launches.
 extern "C" int fblt_cross_attention_forward(const fblt_cross_desc *d, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_cross_attention_forward");
     using namespace fblt;
     if (!d) return fail(FBLT_ERR_ARG, "cross: NULL descriptor");
     if (d->batch < 0 || d->num_heads <= 0 || d->head_dim <= 0 || d->total_q_rows < 0 || d->total_k_rows < 0)
@@ -106,6 +108,7 @@ extern "C" int fblt_cross_attention_forward(const fblt_cross_desc *d, void *stre
 // operator launch per head; here it is the matmul, the decode kernel (rotation and write-through
 // fused) and the matmul again.
 extern "C" int fblt_kv_self_attention_step(const fblt_kv_step_desc *d, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_kv_self_attention_step");
     using namespace fblt;
     if (!d) return fail(FBLT_ERR_ARG, "kv step: NULL descriptor");
     if (d->batch < 0 || d->num_heads <= 0 || d->head_dim <= 0 || d->n_new < 1)

@@ -165,10 +165,12 @@ static int session_forward_impl(fblt_session *s, const fblt_attn_desc *hd, bool 
 }
 
 extern "C" int fblt_session_forward(fblt_session *s, const fblt_attn_desc *hd) {
+    fblt::NvtxRange nvtx_range("fblt_session_forward");
     return fblt::session_forward_impl(s, hd, true);
 }
 
 extern "C" int fblt_session_forward_async(fblt_session *s, const fblt_attn_desc *hd) {
+    fblt::NvtxRange nvtx_range("fblt_session_forward_async");
     return fblt::session_forward_impl(s, hd, false);
 }
 
@@ -300,6 +302,7 @@ extern "C" int fblt_session_cache_load(fblt_session *s, int32_t batch, const int
 extern "C" int fblt_session_decode(fblt_session *s, int32_t batch, int32_t n_new, int32_t block_mode, int32_t window,
                                    float scale, const float *q_new, const float *k_new, const float *v_new, float *out,
                                    int32_t advance) {
+    fblt::NvtxRange nvtx_range("fblt_session_decode");
     using namespace fblt;
     if (!s || !q_new || !k_new || !v_new || !out) return fail(FBLT_ERR_ARG, "session_decode: NULL argument");
     if (batch < 0 || batch > s->max_batch || !s->kc) return fail(FBLT_ERR_CAPACITY, "session_decode: batch %d exceeds the session", batch);
@@ -351,6 +354,7 @@ extern "C" int fblt_session_decode_steps(fblt_session *s, int32_t batch, int32_t
                                          int32_t window, float scale, const float *q_new, const float *k_new,
                                          const float *v_new, int64_t in_step_stride, float *out,
                                          int64_t out_step_stride, int32_t advance) {
+    fblt::NvtxRange nvtx_range("fblt_session_decode_steps");
     using namespace fblt;
     if (!s || !q_new || !k_new || !v_new || !out) return fail(FBLT_ERR_ARG, "session_decode_steps: NULL argument");
     if (batch < 0 || batch > s->max_batch || !s->kc) return fail(FBLT_ERR_CAPACITY, "session_decode_steps: batch %d exceeds the session", batch);
