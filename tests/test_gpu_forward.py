@@ -85,6 +85,21 @@ def test_ragged_lengths_all_head_dims(cuda_lib, hd):
     check(random_case(42 + hd, cu, cu, 2, hd, MaskConfig()))  # bidirectional, no mask
 
 
+@pytest.mark.parametrize("hd", [2, 16, 32, 64, 128])
+def test_small_lengths_at_every_edge(cuda_lib, hd):
+    """Sequence lengths 1, 2 and one below / at / above the 32- and 128-row edges, for every head_dim
+    class (2 and 16 only the per-row kernel takes), causal and windowed, every kernel that takes the
+    shape; outputs sit between guard rows (gpu_utils), so a write past a short sequence is caught."""
+    lens = [1, 2, 31, 32, 33, 127, 128, 129]
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    kernels = KERNELS if hd in (32, 64, 128) else [(L.IMPL_ROW, L.PREC_FP32), (L.IMPL_AUTO, L.PREC_FP32)]
+    check(random_case(300 + hd, cu, cu, 3, hd, MaskConfig(is_causal=True)), kernels=kernels)
+    check(random_case(301 + hd, cu, cu, 3, hd, MaskConfig(is_causal=True, sliding_window=5)), kernels=kernels)
+    # cross shape: one query row per sequence over the same key counts
+    cu_q = np.arange(len(lens) + 1)
+    check(random_case(302 + hd, cu_q, cu, 3, hd, MaskConfig()), kernels=kernels)
+
+
 def test_docs_offsets_and_block_infer(cuda_lib):
     cu = np.array([0, 150, 150 + 97])
     docs = [np.array([40, 41, 120]), np.array([64])]
