@@ -42,7 +42,7 @@ def test_c4_decode_and_block_verify(cuda_lib):
         assert_close(got3, got, f"splits={s}", atol=1e-6, rtol=1e-5)
 
 
-@pytest.mark.parametrize("n_new", [1, 2, 3, 4, 5, 8, 13, 16])
+@pytest.mark.parametrize("n_new", [1, 2, 3, 4, 5, 8, 13, 16, 32])
 @pytest.mark.parametrize("block_mode", [False, True])
 def test_query_counts_and_modes(cuda_lib, n_new, block_mode):
     lens = [0, 1, 5, 31, 32, 33, 64, 100, 257]
