@@ -47,3 +47,11 @@ def test_job_byte_arithmetic():
     total = bench.prefill_bytes(rows) + sum(bench.decode_bytes(batch, bench.BASE_LEN + bench.N_NEW * t) for t in range(steps))
     assert bench.job_bytes(rows, batch, steps) == total
     assert np.isfinite(total)
+
+
+def test_reference_arm_on_other_ranks_does_nothing():
+    import os
+    env = dict(os.environ, RANK="1", LOCAL_RANK="1", WORLD_SIZE="2")
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=str(ROOT), env=env)
+    assert res.returncode == 0 and res.stdout.strip() == ""
