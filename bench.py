@@ -230,6 +230,9 @@ def main():
                     help="matmul workload: only the decode-step shapes (8192 rows), for profiler captures")
     ap.add_argument("--gather-chunks", type=int, default=4,
                     help="N > 1: the decode rows of a step are gathered in this many pieces while the launches go on")
+    ap.add_argument("--gather", default="nccl", choices=["nccl", "peer"],
+                    help="N > 1: outputs gathered by NCCL all-gather kernels, or by one-sided copy-engine copies into "
+                         "the peers' symmetric-memory buffers")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="N > 1: cap on the CTAs of an NCCL gather (0 = NCCL's default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
@@ -324,7 +327,14 @@ def main():
         # only the last chunk's gather is still under way when the step's compute ends
         n_chunks = args.gather_chunks if args.decode_steps % args.gather_chunks == 0 else 1
         chunk_steps = args.decode_steps // n_chunks
-        gath_d = [torch.empty((world, chunk_steps * B * N_NEW, E), device=dev) for _ in range(n_chunks)]
+        gath_d = [torch.empty((world, chunk_steps * B * N_NEW, E), device=dev) for _ in range(n_chunks)] \
+            if args.gather == "nccl" else None
+        peer_p = peer_d = None
+        if args.gather == "peer":
+            del gath_p
+            peer_p = shard.PeerGather(max_rows, E, dev)
+            peer_d = [shard.PeerGather(chunk_steps * B * N_NEW, E, dev) for _ in range(n_chunks)]
+            gath_p, gath_d = peer_p.buf, [g.buf for g in peer_d]
         ev_chunk = [torch.cuda.Event() for _ in range(n_chunks)]
         equal = len({e - b for b, e in ranges}) == 1
         assert equal, "decode gather assumes equal sequence counts per rank"
@@ -356,7 +366,10 @@ def main():
                 with torch.cuda.stream(comm_stream):   # prefill rows travel while decode runs
                     if it == last_it:
                         g_pre[0].record(comm_stream)
-                    shard.gather_rows(out_p, rows_per_rank, padded=pad_p, gathered=gath_p)
+                    if peer_p is not None:
+                        peer_p.put(out_p, rows_per_rank[rank])
+                    else:
+                        shard.gather_rows(out_p, rows_per_rank, padded=pad_p, gathered=gath_p)
                     ev_pre_gathered.record(comm_stream)
                     if it == last_it:
                         g_pre[1].record(comm_stream)
@@ -372,8 +385,11 @@ def main():
                     with torch.cuda.stream(comm_stream):
                         if it == last_it:
                             g_dec[c][0].record(comm_stream)
-                        dist.all_gather_into_tensor(gath_d[c].view(-1, E),
-                                                    out_d2[buf][c * chunk_steps:(c + 1) * chunk_steps].view(-1, E))
+                        rows_c = out_d2[buf][c * chunk_steps:(c + 1) * chunk_steps].view(-1, E)
+                        if peer_d is not None:
+                            peer_d[c].put(rows_c)
+                        else:
+                            dist.all_gather_into_tensor(gath_d[c].view(-1, E), rows_c)
                         if it == last_it:
                             g_dec[c][1].record(comm_stream)
                         if c == n_chunks - 1:
@@ -418,7 +434,19 @@ def main():
         launches = int(lt[0])
     gather = None
     if world > 1:
-        gather = {"prefill_ms": g_pre[0].elapsed_time(g_pre[1]),
+        # every rank's rows must have arrived everywhere: per-slot sums of what this rank holds
+        # against the sums the owners computed from their own outputs (after the closing barrier)
+        last_buf = out_d2[last_it % len(out_d2)]
+        mine = torch.stack([last_buf[c * chunk_steps:(c + 1) * chunk_steps].double().sum() for c in range(n_chunks)]
+                           + [out_p.double().sum()])
+        sums = torch.empty((world, n_chunks + 1), device=dev, dtype=torch.float64)
+        dist.all_gather_into_tensor(sums, mine)
+        got = torch.stack([torch.stack([gath_d[c][r].double().sum() for c in range(n_chunks)]
+                                       + [gath_p[r, :rows_per_rank[r]].double().sum()]) for r in range(world)])
+        gather_ok = bool(torch.allclose(got, sums, rtol=1e-9, atol=1e-6))
+        assert gather_ok, "gathered rows differ from what their owners computed"
+        gather = {"mode": args.gather, "checked": "per-rank sums of the gathered rows equal the owners' sums",
+                  "prefill_ms": g_pre[0].elapsed_time(g_pre[1]),
                   "decode_chunk_ms": [g_dec[c][0].elapsed_time(g_dec[c][1]) for c in range(n_chunks)],
                   "prefill_bytes_gathered": int(world * max_rows * E * 4),
                   "decode_bytes_gathered_per_chunk": int(world * chunk_steps * B * N_NEW * E * 4),

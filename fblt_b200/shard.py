@@ -51,6 +51,40 @@ def gather_rows(local: torch.Tensor, rows_per_rank: List[int], group=None, padde
     return gathered, rows_per_rank
 
 
+class PeerGather:
+    """All-gather of row blocks by one-sided copies over NVLink instead of a collective kernel.
+
+    Every rank owns a [world, rows, E] buffer in symmetric memory (peer-mapped by
+    torch.distributed._symmetric_memory); put() copies this rank's block into slot [rank] of every
+    rank's buffer with plain device-to-device copies, which the driver runs on the copy engines,
+    so the gather takes no SM from the attention launches it overlaps with (an NCCL all-gather
+    runs as a kernel). Nothing is ever loaded from a peer: data lands in the owner's memory first.
+
+    Completion is one-sided: when put() has finished on this rank's stream, this rank's rows have
+    arrived everywhere; a rank's own buffer is complete once every rank has reached that point
+    (a barrier, or the max over ranks of a device-timed region). Construction is collective.
+    """
+
+    def __init__(self, rows: int, E: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm
+        # no multicast binding: plain peer mappings are all the copies need
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.buf = symm.empty((self.world, rows, E), dtype=torch.float32, device=device)
+        self.handle = symm.rendezvous(self.buf, group)
+        self.peers = [self.buf if r == self.rank else self.handle.get_buffer(r, (self.world, rows, E), torch.float32)
+                      for r in range(self.world)]
+
+    def put(self, local: torch.Tensor, nrows: Optional[int] = None) -> None:
+        """Enqueue, on the current stream, the copies of local[:nrows] into slot [rank] of every buffer."""
+        n = local.shape[0] if nrows is None else nrows
+        src = local[:n]
+        for k in range(self.world):            # start with the next rank so that the ranks do not all
+            r = (self.rank + 1 + k) % self.world   # write to the same peer at the same time
+            self.peers[r][self.rank, :n].copy_(src, non_blocking=True)
+
+
 def unpad(gathered: torch.Tensor, rows_per_rank: List[int]) -> torch.Tensor:
     """Concatenate the valid rows of a gather_rows() result in rank order."""
     return torch.cat([gathered[r, :n] for r, n in enumerate(rows_per_rank)], dim=0)
