@@ -3,8 +3,10 @@
 One step = one pass of the hot path over the whole batch: block-causal patch-transformer
 prefill attention (16 heads x 64, patch structure from the seeded generator) followed by 64
 KV-cache decode steps with a block of 4 verify rows (cache 512 -> 768 rows), for 2048
-independent sequences sharded by batch over the ranks; outputs are gathered over NCCL when
-the batch is partitioned.
+independent sequences sharded by batch over the ranks; when the batch is partitioned the
+outputs are gathered over NVLink, by default with one-sided copy-engine copies into the peers'
+symmetric-memory buffers (`--gather peer`; no SM is taken from the attention launches) or with
+NCCL all-gathers (`--gather nccl`, also the fallback when the peer set-up fails).
 
     python bench.py [--gpus N --steps K --warmup W]            # this library
     python bench.py --impl reference [...]                     # reference CPU operator, host cores
@@ -230,7 +232,7 @@ def main():
                     help="matmul workload: only the decode-step shapes (8192 rows), for profiler captures")
     ap.add_argument("--gather-chunks", type=int, default=4,
                     help="N > 1: the decode rows of a step are gathered in this many pieces while the launches go on")
-    ap.add_argument("--gather", default="nccl", choices=["nccl", "peer"],
+    ap.add_argument("--gather", default="peer", choices=["nccl", "peer"],
                     help="N > 1: outputs gathered by NCCL all-gather kernels, or by one-sided copy-engine copies into "
                          "the peers' symmetric-memory buffers")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="N > 1: cap on the CTAs of an NCCL gather (0 = NCCL's default)")
@@ -330,11 +332,24 @@ def main():
         gath_d = [torch.empty((world, chunk_steps * B * N_NEW, E), device=dev) for _ in range(n_chunks)] \
             if args.gather == "nccl" else None
         peer_p = peer_d = None
+        gather_mode = args.gather
         if args.gather == "peer":
-            del gath_p
-            peer_p = shard.PeerGather(max_rows, E, dev)
-            peer_d = [shard.PeerGather(chunk_steps * B * N_NEW, E, dev) for _ in range(n_chunks)]
-            gath_p, gath_d = peer_p.buf, [g.buf for g in peer_d]
+            # collective set-up; if it fails on any rank, every rank falls back to NCCL all-gathers
+            try:
+                peer_p = shard.PeerGather(max_rows, E, dev)
+                peer_d = [shard.PeerGather(chunk_steps * B * N_NEW, E, dev) for _ in range(n_chunks)]
+                ok = torch.ones(1, device=dev)
+            except Exception as exc:   # noqa: BLE001 - any set-up failure selects the fallback
+                sys.stderr.write(f"rank {rank}: peer gather unavailable ({exc}); using NCCL\n")
+                ok = torch.zeros(1, device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if float(ok) > 0:
+                del gath_p
+                gath_p, gath_d = peer_p.buf, [g.buf for g in peer_d]
+            else:
+                peer_p = peer_d = None
+                gather_mode = "nccl (peer set-up failed)"
+                gath_d = [torch.empty((world, chunk_steps * B * N_NEW, E), device=dev) for _ in range(n_chunks)]
         ev_chunk = [torch.cuda.Event() for _ in range(n_chunks)]
         equal = len({e - b for b, e in ranges}) == 1
         assert equal, "decode gather assumes equal sequence counts per rank"
@@ -445,7 +460,7 @@ def main():
                                        + [gath_p[r, :rows_per_rank[r]].double().sum()]) for r in range(world)])
         gather_ok = bool(torch.allclose(got, sums, rtol=1e-9, atol=1e-6))
         assert gather_ok, "gathered rows differ from what their owners computed"
-        gather = {"mode": args.gather, "checked": "per-rank sums of the gathered rows equal the owners' sums",
+        gather = {"mode": gather_mode, "checked": "per-rank sums of the gathered rows equal the owners' sums",
                   "prefill_ms": g_pre[0].elapsed_time(g_pre[1]),
                   "decode_chunk_ms": [g_dec[c][0].elapsed_time(g_dec[c][1]) for c in range(n_chunks)],
                   "prefill_bytes_gathered": int(world * max_rows * E * 4),
