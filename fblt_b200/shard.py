@@ -67,7 +67,8 @@ class PeerGather:
 
     def __init__(self, rows: int, E: int, device: torch.device, group=None):
         import torch.distributed._symmetric_memory as symm
-        # no multicast binding: plain peer mappings are all the copies need
+        # plain peer mappings are all the copies need; ask the allocator not to bind a multicast
+        # object as well (a hint: this torch build still reports multicast support on the handle)
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         group = group or dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
