@@ -208,7 +208,7 @@ typedef struct {
 
 typedef enum {
     FBLT_IMPL_AUTO = 0,   /* pick per shape */
-    FBLT_IMPL_ROW = 1,    /* one warp per (query row, head), fp32 FMA; any head_dim % 4 == 0 up to 256, any mask */
+    FBLT_IMPL_ROW = 1,    /* one warp per (query row, head), fp32 FMA; any head_dim up to 256, any mask */
     FBLT_IMPL_TILE = 2,   /* tensor-core tiles, mma.sync TF32 (head_dim 32/64/128, range masks) */
     FBLT_IMPL_TCGEN05 = 3, /* tensor-core tiles, tcgen05 + TMEM (head_dim 64, range masks) */
     FBLT_IMPL_ROW_QUAD = 4 /* four lanes per (query row, head), fp32 FMA; head_dim 32/64, range masks, no rotary tables */
