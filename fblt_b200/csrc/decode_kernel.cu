@@ -18,6 +18,8 @@
 //     kernel merges them (no inter-CTA waiting anywhere).
 #include "common.cuh"
 
+#include <atomic>
+
 #include <limits.h>
 
 namespace fblt {
@@ -480,21 +482,8 @@ static int launch_decode_hd(const DecodeParams &p, int nq, cudaStream_t stream) 
     return st;
 }
 
-} // namespace fblt
-
-extern "C" size_t fblt_attn_decode_workspace(const fblt_decode_desc *d) {
-    if (!d || d->batch <= 0) return 0;
-    const int splits = fblt::resolve_splits(d);
-    if (splits <= 1) return 0;
-    return (size_t)d->batch * d->num_heads * d->n_new * splits * fblt::partial_floats(d->head_dim) * sizeof(float);
-}
-
-extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size_t workspace_bytes, void *stream) {
-    fblt::NvtxRange nvtx_range("fblt_attn_decode");
-    using namespace fblt;
-    int st = validate_decode(d);
-    if (st != FBLT_OK) return st;
-    if (d->batch == 0) return FBLT_OK;
+// The one place a descriptor becomes kernel parameters; both entry points go through it.
+static DecodeParams fill_decode_params(const fblt_decode_desc *d, float *partials) {
     DecodeParams p;
     p.batch = d->batch;
     p.H = d->num_heads;
@@ -517,10 +506,38 @@ extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size
     p.new_stride = d->kv_new_stride;
     p.out = d->out;
     p.out_stride = d->out_stride;
-    p.ws = (float *)workspace;
+    p.ws = partials;
     p.qscale = d->scale * kLog2e;
     p.rope_cos = d->rope_cos;
     p.rope_sin = d->rope_sin;
+    return p;
+}
+
+static int launch_decode(const fblt_decode_desc *d, const DecodeParams &p, cudaStream_t s) {
+    const int nq = pick_nq(d->n_new);
+    switch (d->head_dim) {
+    case 32: return launch_decode_hd<32>(p, nq, s);
+    case 64: return launch_decode_hd<64>(p, nq, s);
+    default: return launch_decode_hd<128>(p, nq, s);
+    }
+}
+
+} // namespace fblt
+
+extern "C" size_t fblt_attn_decode_workspace(const fblt_decode_desc *d) {
+    if (!d || d->batch <= 0) return 0;
+    const int splits = fblt::resolve_splits(d);
+    if (splits <= 1) return 0;
+    return (size_t)d->batch * d->num_heads * d->n_new * splits * fblt::partial_floats(d->head_dim) * sizeof(float);
+}
+
+extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size_t workspace_bytes, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_attn_decode");
+    using namespace fblt;
+    int st = validate_decode(d);
+    if (st != FBLT_OK) return st;
+    if (d->batch == 0) return FBLT_OK;
+    const DecodeParams p = fill_decode_params(d, (float *)workspace);
     if (p.splits > 1) {
         const size_t need = fblt_attn_decode_workspace(d);
         if (!workspace || workspace_bytes < need)
@@ -528,12 +545,7 @@ extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size
                         workspace_bytes);
         if ((uintptr_t)workspace & 15) return fail(FBLT_ERR_ARG, "decode: workspace must be 16-byte aligned");
     }
-    cudaStream_t s = (cudaStream_t)stream;
-    switch (d->head_dim) {
-    case 32: return launch_decode_hd<32>(p, nq, s);
-    case 64: return launch_decode_hd<64>(p, nq, s);
-    default: return launch_decode_hd<128>(p, nq, s);
-    }
+    return launch_decode(d, p, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -547,7 +559,8 @@ constexpr size_t kStaticScratchBytes = (size_t)4 << 20;
 static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchBytes / sizeof(float)];
 
 constexpr int kMaxDevices = 64;
-static float *g_static_scratch_addr[kMaxDevices]; // device address per device ordinal, 0 = not looked up yet
+// device address per device ordinal, null = not looked up yet; any host thread may read or fill a slot
+static std::atomic<float *> g_static_scratch_addr[kMaxDevices];
 
 // In host code `g_decode_static_scratch` is only a handle for the symbol; the
 // address a kernel can dereference has to be asked for, once per device, with
@@ -556,14 +569,14 @@ static int static_scratch_address(float **out) {
     int dev = -1;
     FBLT_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return fail(FBLT_ERR_LIMIT, "decode_static: device ordinal %d not supported", dev);
-    float *p = g_static_scratch_addr[dev];
+    float *p = g_static_scratch_addr[dev].load(std::memory_order_relaxed);
     if (!p) {
         void *addr = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&addr, g_decode_static_scratch);
         if (e != cudaSuccess || !addr)
             return fail(FBLT_ERR_CUDA, "decode_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
         p = static_cast<float *>(addr);
-        g_static_scratch_addr[dev] = p; // same value whichever thread gets here first
+        g_static_scratch_addr[dev].store(p, std::memory_order_relaxed); // same value whichever thread gets here first
     }
     *out = p;
     return FBLT_OK;
@@ -589,36 +602,7 @@ extern "C" int fblt_attn_decode_static(const fblt_decode_desc *d, void *stream) 
     float *scratch = nullptr;
     st = static_scratch_address(&scratch);
     if (st != FBLT_OK) return st;
-    DecodeParams p;
-    p.batch = d->batch;
-    p.H = d->num_heads;
-    p.n_new = d->n_new;
-    p.block_mode = d->block_mode ? 1 : 0;
-    p.window = d->window > 0 ? d->window : 0;
-    p.splits = splits;
-    const int nq = pick_nq(d->n_new);
-    p.qgroups = (d->n_new + nq - 1) / nq;
-    p.base_len = d->base_len;
-    p.base_add = d->base_add;
-    p.kc = d->k_cache;
-    p.vc = d->v_cache;
-    p.seq_stride = d->cache_seq_stride;
-    p.row_stride = d->cache_row_stride;
-    p.q = d->q;
-    p.q_stride = d->q_stride;
-    p.kn = d->k_new;
-    p.vn = d->v_new;
-    p.new_stride = d->kv_new_stride;
-    p.out = d->out;
-    p.out_stride = d->out_stride;
-    p.ws = scratch; // every (row, split) slot is written before the merge kernel reads it: nothing to clear
-    p.qscale = d->scale * kLog2e;
-    p.rope_cos = d->rope_cos;
-    p.rope_sin = d->rope_sin;
-    cudaStream_t s = (cudaStream_t)stream;
-    switch (d->head_dim) {
-    case 32: return launch_decode_hd<32>(p, nq, s);
-    case 64: return launch_decode_hd<64>(p, nq, s);
-    default: return launch_decode_hd<128>(p, nq, s);
-    }
+    // every (row, split) slot is written before the merge kernel reads it: nothing to clear
+    const DecodeParams p = fill_decode_params(d, scratch);
+    return launch_decode(d, p, (cudaStream_t)stream);
 }

@@ -3,6 +3,7 @@
 
 #include <atomic>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace fblt {
@@ -17,6 +18,18 @@ int fail(int status, const char *fmt, ...) {
     va_end(ap);
     return status;
 }
+
+// FBLT_REPORT_LAUNCHES=1: one line on stderr when the process ends, so that a host program that
+// only links the library (no call to fblt_launch_count of its own) can show that its attention
+// ran on these kernels.
+struct ExitReport {
+    ~ExitReport() {
+        const char *e = getenv("FBLT_REPORT_LAUNCHES");
+        if (e && e[0] == '1')
+            fprintf(stderr, "[fblt] %llu kernel launches\n", (unsigned long long)g_launches.load(std::memory_order_relaxed));
+    }
+};
+static ExitReport g_exit_report;
 
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 

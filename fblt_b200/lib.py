@@ -52,6 +52,24 @@ class MaskDesc(C.Structure):
     ]
 
 
+class MaskConfig(C.Structure):
+    """fblt_mask_config == blt_mask_config (ops/mask_builder.h:12-32); id arrays are host size_t."""
+    _fields_ = [
+        ("seq_len_q", C.c_size_t), ("seq_len_kv", C.c_size_t), ("sliding_window", C.c_size_t),
+        ("doc_boundaries", C.c_void_p), ("num_docs", C.c_size_t),
+        ("query_group_ids", C.c_void_p), ("kv_group_ids", C.c_void_p),
+        ("bidirectional_within_group", C.c_bool), ("is_causal", C.c_bool), ("causal_offset", C.c_size_t),
+    ]
+
+
+class BlockDiffusionConfig(C.Structure):
+    """fblt_block_diffusion_config == blt_block_diffusion_config (ops/mask_builder.h:43-68)."""
+    _fields_ = [
+        ("mode", C.c_int), ("seq_len", C.c_size_t), ("num_clean", C.c_size_t), ("block_size", C.c_size_t),
+        ("block_starts", C.c_void_p), ("num_blocks", C.c_size_t),
+    ]
+
+
 class MhaDesc(C.Structure):
     _fields_ = [
         ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32), ("max_len", C.c_int32),
@@ -140,6 +158,12 @@ SYMBOLS = {
     "fblt_attn_forward": (C.c_int, [C.POINTER(AttnDesc), C.c_void_p]),
     "fblt_mask_bitmap": (C.c_int, [C.POINTER(AttnDesc), C.c_void_p, C.c_int, C.c_void_p]),
     "fblt_mask_materialize": (C.c_int, [C.POINTER(AttnDesc), C.c_int32, C.c_void_p, c_i32_p, C.c_void_p]),
+    "fblt_mask_dense_scratch_bytes": (C.c_size_t, [C.POINTER(MaskConfig)]),
+    "fblt_build_attention_mask_dense": (C.c_int, [C.POINTER(MaskConfig), C.c_void_p, C.c_void_p, C.c_size_t, c_i32_p,
+                                                  C.c_void_p]),
+    "fblt_block_diffusion_mask_scratch_bytes": (C.c_size_t, [C.POINTER(BlockDiffusionConfig)]),
+    "fblt_build_block_diffusion_mask_dense": (C.c_int, [C.POINTER(BlockDiffusionConfig), C.c_void_p, C.c_void_p,
+                                                        C.c_size_t, c_i32_p, C.c_void_p]),
     "fblt_attn_decode_workspace": (C.c_size_t, [C.POINTER(DecodeDesc)]),
     "fblt_attn_decode": (C.c_int, [C.POINTER(DecodeDesc), C.c_void_p, C.c_size_t, C.c_void_p]),
     "fblt_attn_decode_static_capacity": (C.c_size_t, []),

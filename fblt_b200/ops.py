@@ -227,6 +227,53 @@ def mask_materialize(batch: AttnBatch, seq: int):
     return m, empty.value
 
 
+def _host_sizes(a):
+    """Host size_t array (the reference passes its id arrays as host pointers) or None."""
+    if a is None:
+        return None
+    return np.ascontiguousarray(np.asarray(a, dtype=np.uint64))
+
+
+def build_attention_mask(nq: int, nk: int, *, window: int = 0, doc_boundaries=None, q_groups=None, k_groups=None,
+                         bidirectional: bool = True, is_causal: bool = False, causal_offset: int = 0, stream=None):
+    """blt_build_attention_mask on the CUDA backend: dense [nq, nk] 0 / -inf tensor and the number of
+    query rows without an allowed key (fatal in the reference, ops/mask_builder_cpu.c:93)."""
+    lib = L.load()
+    c = L.MaskConfig()
+    c.seq_len_q, c.seq_len_kv, c.sliding_window = nq, nk, window
+    db, qg, kg = _host_sizes(doc_boundaries), _host_sizes(q_groups), _host_sizes(k_groups)
+    if db is not None:
+        c.doc_boundaries, c.num_docs = db.ctypes.data, len(db) + 1
+    if qg is not None:
+        c.query_group_ids, c.kv_group_ids = qg.ctypes.data, kg.ctypes.data
+    c.bidirectional_within_group, c.is_causal, c.causal_offset = bool(bidirectional), bool(is_causal), causal_offset
+    need = lib.fblt_mask_dense_scratch_bytes(C.byref(c))
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    m = torch.full((nq, nk), float("nan"), dtype=torch.float32, device="cuda")
+    empty = C.c_int32(-1)
+    L.check(lib.fblt_build_attention_mask_dense(C.byref(c), m.data_ptr(), scratch.data_ptr(), need, C.byref(empty),
+                                                _stream_ptr(stream)))
+    return m, empty.value
+
+
+def build_block_diffusion_mask(mode: int, S: int, N: int, B: int = 0, block_starts=None, stream=None):
+    """blt_build_block_diffusion_mask on the CUDA backend (mode 0 = TRAIN, 1 = INFER): [S, S] and the
+    number of empty rows."""
+    lib = L.load()
+    c = L.BlockDiffusionConfig()
+    c.mode, c.seq_len, c.num_clean, c.block_size = mode, S, N, B
+    bs = _host_sizes(block_starts)
+    if bs is not None:
+        c.block_starts, c.num_blocks = bs.ctypes.data, len(bs)
+    need = lib.fblt_block_diffusion_mask_scratch_bytes(C.byref(c))
+    scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    m = torch.full((S, S), float("nan"), dtype=torch.float32, device="cuda")
+    empty = C.c_int32(-1)
+    L.check(lib.fblt_build_block_diffusion_mask_dense(C.byref(c), m.data_ptr(), scratch.data_ptr(), need,
+                                                      C.byref(empty), _stream_ptr(stream)))
+    return m, empty.value
+
+
 # --------------------------------------------------------------------------- decode
 
 def make_decode(k_cache: torch.Tensor, v_cache: torch.Tensor, base_len: torch.Tensor, q: torch.Tensor,

@@ -124,25 +124,39 @@ def report_failure(store, rank: int, tag: str, reason: str) -> None:
 
 
 def rendezvous(store, rank: int, world_size: int, tag: str, deadline_s: float = 30.0, poll_s: float = 0.005) -> None:
-    """Check in under `tag` and wait until every rank has. Raises RankFailed as soon as a rank has
-    announced a failure, RankTimeout (naming the absent ranks) when the deadline passes. `store` is
-    any torch.distributed store shared by the ranks (the process group's own, a TCPStore, a
-    FileStore). Tags must not be reused within a job."""
+    """Check in under `tag` and return once every rank has checked in AND has seen everyone else do so.
+
+    Two phases over any torch.distributed store shared by the ranks (the process group's own, a
+    TCPStore, a FileStore): every rank publishes `ready`, waits for the others' `ready`, publishes
+    `go`, waits for the others' `go`. A rank that gives up publishes `failed` first, so the outcome
+    is the same on every rank: a rank that arrives after another one's deadline finds that rank's
+    `failed` key and raises RankFailed instead of going on alone towards a peer that has left.
+    Raises RankFailed as soon as any rank has announced a failure (report_failure, or a timeout
+    elsewhere), RankTimeout (naming the absent ranks) when this rank's own deadline passes. The
+    second phase has a deadline of its own: by then every rank was alive a moment ago. Tags must not
+    be reused within a job."""
     import time
-    store.set(_key(tag, "ready", rank), b"1")
     others = [r for r in range(world_size) if r != rank]
-    t0 = time.monotonic()
-    while True:
-        for r in others:
-            if store.check([_key(tag, "failed", r)]):
-                raise RankFailed(tag, r, store.get(_key(tag, "failed", r)).decode(errors="replace"))
-        missing = [r for r in others if not store.check([_key(tag, "ready", r)])]
-        if not missing:
-            return
-        waited = time.monotonic() - t0
-        if waited >= deadline_s:
-            raise RankTimeout(tag, missing, waited)
-        time.sleep(poll_s)
+
+    def wait_for(kind: str, limit_s: float) -> None:
+        t0 = time.monotonic()
+        while True:
+            for r in others:
+                if store.check([_key(tag, "failed", r)]):
+                    raise RankFailed(tag, r, store.get(_key(tag, "failed", r)).decode(errors="replace"))
+            missing = [r for r in others if not store.check([_key(tag, kind, r)])]
+            if not missing:
+                return
+            waited = time.monotonic() - t0
+            if waited >= limit_s:
+                report_failure(store, rank, tag, f"timed out after {waited:.1f} s waiting for ranks {missing} ({kind})")
+                raise RankTimeout(tag, missing, waited)
+            time.sleep(poll_s)
+
+    store.set(_key(tag, "ready", rank), b"1")
+    wait_for("ready", deadline_s)
+    store.set(_key(tag, "go", rank), b"1")
+    wait_for("go", max(deadline_s, 5.0))
 
 
 def default_store():

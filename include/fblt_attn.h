@@ -301,6 +301,59 @@ int fblt_mask_bitmap(const fblt_attn_desc *desc, uint8_t *bitmap, int use_range,
 int fblt_mask_materialize(const fblt_attn_desc *desc, int32_t seq, float *mask_out, int32_t *empty_rows_out,
                           void *stream);
 
+/*
+ * The reference's two dense mask builders behind its own config structs, for a
+ * host that keeps calling blt_build_attention_mask / blt_build_block_diffusion_mask
+ * on the CUDA backend (dispatcher: core/backend.c:190-192; replaced:
+ * ops/mask_builder.cu:100-216). Field-for-field layouts of blt_mask_config
+ * (ops/mask_builder.h:12-32) and blt_block_diffusion_config
+ * (ops/mask_builder.h:43-68); a pointer to either type may be passed. The id
+ * arrays are HOST pointers, as in the reference (ops/mask_builder.cu:10-13).
+ */
+typedef struct {
+    size_t seq_len_q;
+    size_t seq_len_kv;
+    size_t sliding_window;
+    const size_t *doc_boundaries; /* num_docs - 1 entries, ascending */
+    size_t num_docs;
+    const size_t *query_group_ids;
+    const size_t *kv_group_ids;
+    bool bidirectional_within_group;
+    bool is_causal;
+    size_t causal_offset;
+} fblt_mask_config;
+
+typedef enum { FBLT_BDM_TRAIN = 0, FBLT_BDM_INFER = 1 } fblt_block_diffusion_mode;
+
+typedef struct {
+    fblt_block_diffusion_mode mode;
+    size_t seq_len;
+    size_t num_clean;
+    size_t block_size;
+    const size_t *block_starts; /* TRAIN only, num_blocks entries */
+    size_t num_blocks;
+} fblt_block_diffusion_config;
+
+/*
+ * mask_out: device [seq_len_q, seq_len_kv] (square [seq_len, seq_len] for the
+ * block-diffusion form), 0 where attention is allowed and -inf elsewhere,
+ * bit-equal to the reference's CPU builders (ops/mask_builder_cpu.c:21-154).
+ * scratch: device memory of at least *_scratch_bytes(config), 16-byte aligned,
+ * supplied by the caller (the reference takes its temporaries from the arena
+ * it is handed, ops/mask_builder.cu:23-28); it may be reused once the stream
+ * has passed the call. *empty_rows_out (host, optional; asking for it
+ * synchronises the stream) = query rows with no allowed key, which the
+ * reference treats as fatal (ops/mask_builder_cpu.c:93,152). Preconditions of
+ * the reference that fail here return FBLT_ERR_ARG instead of exiting.
+ * fblt_b200/csrc/blt_backend_glue.c wraps both into the reference's symbols.
+ */
+size_t fblt_mask_dense_scratch_bytes(const fblt_mask_config *config);
+int fblt_build_attention_mask_dense(const fblt_mask_config *config, float *mask_out, void *scratch,
+                                    size_t scratch_bytes, int32_t *empty_rows_out, void *stream);
+size_t fblt_block_diffusion_mask_scratch_bytes(const fblt_block_diffusion_config *config);
+int fblt_build_block_diffusion_mask_dense(const fblt_block_diffusion_config *config, float *mask_out, void *scratch,
+                                          size_t scratch_bytes, int32_t *empty_rows_out, void *stream);
+
 /* ------------------------------------------------------------------------ */
 /* L1: KV-cache decode / block verify                                        */
 /* ------------------------------------------------------------------------ */
@@ -326,7 +379,7 @@ typedef struct {
     int32_t batch;
     int32_t num_heads;
     int32_t head_dim; /* 32, 64 or 128 */
-    int32_t n_new;    /* 1..16 */
+    int32_t n_new;    /* 1..32 (block_generation.c:154 caps the block size at 32) */
     int32_t block_mode;
     int32_t window;
     int32_t max_len;  /* host-known upper bound of base_len[b] + n_new */
@@ -377,8 +430,11 @@ int fblt_attn_decode(const fblt_decode_desc *desc, void *workspace, size_t works
  *     exceed the capacity is rejected with FBLT_ERR_LIMIT; pass splits = 1
  *     (no partials at all) or use fblt_attn_decode for those;
  *   - the first call on each device looks the array's device address up
- *     (cudaGetSymbolAddress, with that device current). Make that first call
- *     during set-up, before any stream capture begins;
+ *     (cudaGetSymbolAddress, with that device current) and keeps it for the
+ *     life of the process. Make that first call during set-up, before any
+ *     stream capture begins. The kept address does not survive a
+ *     cudaDeviceReset(): a process that resets a device must not call this
+ *     entry point on it afterwards;
  *   - all calls share the one array and it keeps whatever the last call left
  *     there. Nothing has to start at zero: each call overwrites every slot it
  *     later reads. Two calls whose kernels can overlap on the GPU (different
@@ -662,7 +718,9 @@ int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch);
  */
 int fblt_tcgen05_error(void);
 
-/* Number of kernels this library has launched in this process (all threads). */
+/* Number of kernels this library has launched in this process (all threads). With
+ * FBLT_REPORT_LAUNCHES=1 in the environment the same count is printed to stderr when the
+ * process ends ("[fblt] N kernel launches"). */
 uint64_t fblt_launch_count(void);
 /* sizeof of {fblt_head_args, fblt_patch_info, fblt_mask_desc, fblt_attn_desc,
  * fblt_decode_desc, fblt_mha_desc, fblt_cross_desc, fblt_kv_step_desc}, for bindings that re-declare the structs. Returns the count. */

@@ -27,9 +27,27 @@ _oracle = None
 _ref = None
 
 
-def build() -> None:
-    """make -C oracle (restatement always; the reference library when its sources are mounted)."""
-    subprocess.run(["make", "-C", str(HERE)], check=True, stdout=subprocess.DEVNULL)
+def reference_tree() -> Optional[Path]:
+    """Where the upstream source tree is mounted: FBLT_REFERENCE_TREE, else a folder named
+    `reference` beside the repository. None when absent (as on the GPU box, which uses the
+    prebuilt files under oracle/_ref)."""
+    cands = [os.environ.get("FBLT_REFERENCE_TREE"), HERE.parent.parent / "reference"]
+    for c in cands:
+        if c and (Path(c) / "csrc" / "ops" / "attn_core_cpu.c").exists():
+            return Path(c)
+    return None
+
+
+def build(accept: bool = True) -> None:
+    """make -C oracle: the restatement always; where the reference's sources are mounted also its
+    CPU object code and (accept=True, library already built) the two acceptance executables."""
+    cmd = ["make", "-C", str(HERE), "-j8"]
+    tree = reference_tree()
+    if tree is not None:
+        cmd.append(f"REF={tree}")
+    subprocess.run(cmd + ["all"], check=True, stdout=subprocess.DEVNULL)
+    if accept and tree is not None and (HERE.parent / "fblt_b200" / "libfblt_attn.so").exists():
+        subprocess.run(cmd + ["accept"], check=True, stdout=subprocess.DEVNULL)
 
 
 def oracle() -> C.CDLL:
@@ -99,6 +117,7 @@ def ref() -> C.CDLL:
         lib.ref_aligned_commit_select.argtypes = [C.POINTER(PatchInfo), C.c_size_t, C.c_size_t, C.c_size_t]
         lib.ref_kv_common_patches.restype = C.c_size_t
         lib.ref_kv_common_patches.argtypes = [C.POINTER(PatchInfo), C.c_size_t, C.POINTER(PatchInfo), C.c_size_t]
+        lib.ref_argmax_rows.argtypes = [c_f_p, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint32)]
         lib.ref_struct_layout.restype = C.c_size_t
         lib.ref_struct_layout.argtypes = [c_sz_p, C.c_size_t]
         _ref = lib

@@ -31,6 +31,7 @@
 #include "ops/matmul.h"
 #include "ops/patch_pool.h"
 #include "ops/rope.h"
+#include "ops/row_stats.h"
 
 void ref_attention_head(const blt_attention_head_args *a) { blt_attention_head_core(BLT_BACKEND_CPU, a); }
 
@@ -259,6 +260,23 @@ void ref_rope_apply(const float *x, const float *cos_t, const float *sin_t, floa
 }
 
 /* sizeof / offsetof of the ABI structs, for the layout check of include/fblt_attn.h. */
+/* Row argmax by the reference's public operator (ops/row_stats_cpu.c:30-47, the rule its
+ * generation loops decide with: infer/self_speculation.c:301,332). */
+void ref_argmax_rows(const float *logits, size_t rows, size_t vocab, uint32_t *ids_out) {
+    blt_tensor t;
+    memset(&t, 0, sizeof(t));
+    t.data = (void *)logits;
+    t.shape[0] = rows;
+    t.shape[1] = vocab;
+    t.strides[0] = vocab;
+    t.strides[1] = 1;
+    t.ndim = 2;
+    t.numel = rows * vocab;
+    t.dtype = BLT_DTYPE_FP32;
+    t.backend = BLT_BACKEND_CPU;
+    blt_argmax_rows(&t, ids_out);
+}
+
 size_t ref_struct_layout(size_t *out, size_t cap) {
     const size_t v[] = {
         sizeof(blt_attention_head_args),

@@ -62,6 +62,35 @@ def test_c3_cross_attention(cuda_lib):
         check(workloads.c3_cross_attention(d, batch=4), kernels=[(L.IMPL_AUTO, L.PREC_FP32)])
 
 
+@pytest.mark.parametrize("hd", [32, 64])
+@pytest.mark.parametrize("k", [1, 3])
+def test_decode_step_cross_tier(cuda_lib, hd, k):
+    """Cross-attention of an incremental decode step (infer/kv_cache.c:303-324): n fresh byte rows at
+    absolute positions base.. read the tier-2 latents under the mask of infer/kv_cache.c:206-218,
+    245-249 -- one latent group per row by the decoder rule, the last row redirected to the final
+    latent when the trailing patch is closed. Numeric result of every kernel that takes the shape
+    against the reference operator under exactly that host-built mask."""
+    seq_bytes = 96
+    lens = [synth.geometric_patches(77, s, seq_bytes) for s in range(4)]
+    bounds = [synth.bounds_from_lengths(l) for l in lens]
+    P = np.array([len(l) for l in lens])
+    cu_k = np.concatenate([[0], np.cumsum(P * k)])
+    # bases: start of the sequence, inside a patch, on a patch's final byte, rows running past the end
+    bases = [0, int(bounds[1][3]) + 1, int(bounds[2][5]) - 1, seq_bytes - 2]
+    for n in (1, 4):
+        cu_q = np.arange(5) * n
+        for tc in ([0, 0, 0, 0], [1, 0, 1, 1]):
+            mask = MaskConfig(group_rule=L.GROUP_PATCH_DEC, subtokens=k, patch_bounds=bounds, q_pos_offset=bases,
+                              trailing_closed=tc)
+            case = random_case(500 + 10 * n + k, cu_q, cu_k, 4, hd, mask)
+            want, masks, _ = oracle_forward(case)
+            for b in range(4):   # the oracle's mask is the decode step's own
+                step_mask = ob.decode_cross_mask(bounds[b], k, n, bases[b], bool(tc[b]))
+                assert masks[b].tobytes() == step_mask.tobytes(), (n, k, tc, b)
+                assert (step_mask == 0).sum(axis=1).tolist() == [k] * n      # one latent group per row
+            check(case)
+
+
 def test_c5_prefill_sample(cuda_lib):
     check(workloads.c5_prefill(batch=8))
 

@@ -117,6 +117,52 @@ def test_commit_select_and_adapt_b(ref):
         assert ab(cur, acc, lo, hi, 0.5) == want
 
 
+def _verify(x, l, r, target, logits):
+    import ctypes as C
+    buf = np.zeros(16, np.uint8)
+    buf[:len(x)] = x
+    acc = C.c_size_t(0)
+    n = ob.oracle().oracle_verify_accept(buf.ctypes.data_as(C.POINTER(C.c_uint8)), logits.ctypes.data_as(ob.c_f_p),
+                                         logits.shape[1], l, r, target, C.byref(acc))
+    return n, buf, acc.value
+
+
+def test_verify_accept_cases_of_the_reference():
+    """The four hand-computable branches of the reference's verify step
+    (tests/unit/infer/unit_self_speculation.c:178-255): its model there predicts byte 0 at every row
+    (all logits equal, lowest index wins), which is an all-zero logit matrix here."""
+    logits = np.zeros((16, 256), np.float32)
+    n, x, acc = _verify([7, 7, 5, 5], 2, 2, 16, logits)          # A: first draft byte wrong
+    assert (n, acc) == (3, 0) and x[:3].tolist() == [7, 7, 0]
+    n, x, acc = _verify([7, 7, 0, 0, 0], 2, 2, 16, logits)       # B: all right, one free byte
+    assert (n, acc) == (5, 2) and x[:5].tolist() == [7, 7, 0, 0, 0]
+    n, x, acc = _verify([7, 7, 0, 0], 2, 2, 4, logits)           # C: all right, budget reached
+    assert (n, acc) == (4, 2)
+    n, x, acc = _verify([9, 9, 0, 5, 5], 2, 3, 16, logits)       # D: second draft byte wrong
+    assert (n, acc) == (4, 1) and x[2:4].tolist() == [0, 0]
+
+
+@pytest.mark.skipif(not ob.have_ref(), reason="reference object code not built here")
+def test_argmax_rule_equals_reference_operator():
+    """The restated row argmax against the reference's public operator (ops/row_stats_cpu.c:30-47)
+    on rows full of exact ties, infinities and a single element: same index everywhere."""
+    import ctypes as C
+    rng = np.random.default_rng(11)
+    o, r = ob.oracle(), ob.ref()
+    for vocab in (1, 2, 7, 256, 300):
+        x = rng.standard_normal((64, vocab)).astype(np.float32)
+        x[::2] = np.round(x[::2])                        # many ties
+        x[3, :] = 0.25
+        x[5, :] = -np.inf
+        if vocab > 2:
+            x[7, 1], x[7, vocab - 1] = np.inf, np.inf
+        x = np.ascontiguousarray(x)
+        ids = np.zeros(64, np.uint32)
+        r.ref_argmax_rows(x.ctypes.data_as(ob.c_f_p), 64, vocab, ids.ctypes.data_as(C.POINTER(C.c_uint32)))
+        mine = [o.oracle_argmax_row(x[i].ctypes.data_as(ob.c_f_p), vocab) for i in range(64)]
+        assert mine == ids.tolist()
+
+
 def test_decode_masks_match_builder():
     # the incremental decoder's host loop (infer/kv_cache.c:229-236) is the builder's rule with a causal offset
     for base, n, w in [(0, 3, 0), (7, 4, 0), (9, 2, 4), (20, 5, 6)]:

@@ -66,13 +66,17 @@ def _rdv_worker(rank: int, world: int, path: str, mode: str, q):
     a failure; "absent" = rank 1 never comes."""
     import time
     store = dist.FileStore(path, world)
+    # line the processes up first (interpreter start-up differs by seconds under load), so that
+    # "late" and "on time" below are measured from a common start
+    store.set(f"started/{rank}", b"1")
+    store.wait([f"started/{r}" for r in range(world)])
     t0 = time.monotonic()
     try:
         if rank == 1 and mode == "absent":
             q.put((rank, "skipped", 0.0))
             return
         if rank == 1 and mode == "late":
-            time.sleep(1.5)
+            time.sleep(2.5)
         if rank == 1 and mode == "fail":
             shard.report_failure(store, rank, "step0", "input shard unreadable")
             q.put((rank, "reported", time.monotonic() - t0))
@@ -110,9 +114,8 @@ def test_rendezvous_before_collectives(tmp_path):
     r = _run_rdv("absent", tmp_path)
     assert r[0][0] == "timeout[1]" and r[0][1] < 10.0
     r = _run_rdv("late", tmp_path)
-    assert r[0][0] == "timeout[1]"            # rank 0 gave up at its deadline ...
-    assert r[1][0] == "ok"                    # ... the late rank finds rank 0's check-in and goes on alone:
-    #                                           the caller of rank 0 has already raised, which is the signal
+    assert r[0][0] == "timeout[1]"            # rank 0 gave up at its deadline and said so in the store ...
+    assert r[1][0].startswith("failed0:timed out")   # ... so the late rank does not go on alone
     r = _run_rdv("fail", tmp_path)
     assert r[0][0] == "failed1:input shard unreadable" and r[0][1] < 10.0
 

@@ -15,11 +15,15 @@ import torch
 
 from fblt_b200 import lib as L
 from fblt_b200 import ops, workloads
+from helpers import assert_close, oracle_decode
 
 pytestmark = pytest.mark.gpu
 
 
-def _run_both(case, splits):
+def _run_both(case, splits, stream=None):
+    """Outputs of the workspace entry point and of the static-scratch entry point for one step.
+    splits = 0 leaves the number of key-range pieces to the library. `stream`: a torch stream the
+    static call is issued on (the inputs are ready before it starts)."""
     lib = L.load()
     kc, vc = torch.from_numpy(case.k_cache).cuda(), torch.from_numpy(case.v_cache).cuda()
     base, q = torch.from_numpy(case.base_len).cuda(), torch.from_numpy(case.q).cuda()
@@ -30,12 +34,20 @@ def _run_both(case, splits):
                   max_len=int(case.base_len.max()) + case.n_new, splits=splits)
     d_a = ops.make_decode(kc, vc, base, q, out_a, case.num_heads, case.head_dim, case.n_new, case.scale, **common)
     ws = ops.decode_workspace(d_a)
-    assert ws is not None, "the case must exercise the scratch (splits > 1)"
+    assert ws is not None, "the case must exercise the scratch (more than one piece per key range)"
     ops.attn_decode(d_a, ws)
+    torch.cuda.synchronize()
     d_b = ops.make_decode(kc, vc, base, q, out_b, case.num_heads, case.head_dim, case.n_new, case.scale, **common)
-    L.check(lib.fblt_attn_decode_static(C.byref(d_b), None))
+    L.check(lib.fblt_attn_decode_static(C.byref(d_b), None if stream is None else C.c_void_p(stream.cuda_stream)))
     torch.cuda.synchronize()
     return out_a.cpu().numpy(), out_b.cpu().numpy()
+
+
+def _check(case, splits, stream=None):
+    want_ws, got = _run_both(case, splits, stream)
+    assert_close(got, want_ws, "static scratch vs caller workspace")
+    want_cpu, _ = oracle_decode(case)                    # and against the CPU operator itself
+    assert_close(got, want_cpu, "static scratch vs oracle")
 
 
 def test_static_scratch_matches_workspace_entry_twice_in_a_row(cuda_lib):
@@ -43,10 +55,22 @@ def test_static_scratch_matches_workspace_entry_twice_in_a_row(cuda_lib):
     first = workloads.decode_case(201, 6, 4, 4, True, lens=[300, 64, 511, 129, 400, 256])
     second = workloads.decode_case(202, 3, 2, 1, False, lens=[500, 77, 260], window=200)
     for case, splits in ((first, 4), (second, 3), (first, 2)):
-        want, got = _run_both(case, splits)
-        assert np.isfinite(got).all()
-        err = np.abs(got - want)
-        assert (err <= 1e-4 + 1e-3 * np.abs(want)).all(), f"max abs err {err.max():.3e}"
+        _check(case, splits)
+
+
+def test_static_scratch_with_the_library_choosing_the_split(cuda_lib):
+    # few sequences over long caches: left to itself (splits = 0) the library cuts every key range
+    # into several pieces, so this is the path a caller gets without tuning anything
+    case = workloads.decode_case(203, 2, 4, 4, True, lens=[3000, 1777])
+    _check(case, 0)
+    _check(case, 0)
+
+
+def test_static_scratch_on_a_side_stream(cuda_lib):
+    side = torch.cuda.Stream()
+    case = workloads.decode_case(204, 5, 2, 2, False, lens=[700, 64, 333, 512, 90], window=0)
+    _check(case, 4, stream=side)
+    _check(case, 2, stream=side)
 
 
 def test_static_scratch_rejects_oversized_requests(cuda_lib):
