@@ -21,6 +21,8 @@
 #include <atomic>
 
 #include <limits.h>
+#include <stdlib.h>
+#include <string.h>
 
 namespace fblt {
 
@@ -110,20 +112,36 @@ __host__ __device__ constexpr int dec_partial_floats() {
     return HD + 4; // acc[HD], m, l, 2 pad (keeps 16-byte alignment)
 }
 
+// Shared memory of one CTA: the warps' partial states meet here.
 template <int HD, int NQ>
-__global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p) {
+struct DecShared {
+    float4 acc[kDecWarps][NQ][HD / 4];
+    float m[kDecWarps][NQ], l[kDecWarps][NQ];
+};
+
+// Key range a query group may attend to, over all of its rows: [lo_min, hi_max).
+__device__ __forceinline__ void dec_group_range(const DecodeParams &p, int base, int r0, int nv, int &lo_min, int &hi_max) {
+    const int total = base + p.n_new;
+    hi_max = p.block_mode ? total : base + r0 + nv;
+    lo_min = (p.window > 0 && !p.block_mode) ? max(0, base + r0 + 1 - p.window) : 0;
+}
+
+// One piece of work: query group qg of (sequence b, head h) over the keys [k0, k1) (already inside
+// the group's range). The result goes to the output rows (direct) or, as (acc, m, l) partials, to
+// wdst + q * wrow floats for row q of the group.
+template <int HD, int NQ>
+__device__ __forceinline__ void decode_piece(const DecodeParams &p, DecShared<HD, NQ> &sh, int b, int h, int qg, int base,
+                                             int k0, int k1, bool direct, float *wdst, int64_t wrow,
+                                             bool write_through) {
     constexpr int LPK = HD / 4;   // lanes per key row
     constexpr int KPW = 32 / LPK; // key rows per warp load
     // keys per lane group and chunk: as many as fit "one score per lane", at most 8
     constexpr int U = (LPK / NQ) > 8 ? 8 : ((LPK / NQ) < 1 ? 1 : (LPK / NQ));
     constexpr int CH = KPW * U; // keys per warp per chunk
 
-    const int h = blockIdx.x, sp = blockIdx.y;
-    const int b = blockIdx.z / p.qgroups, qg = blockIdx.z - b * p.qgroups;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int grp = lane / LPK, dl = lane % LPK;
     const int n = p.n_new;
-    const int base = p.base_len[b] + p.base_add;
     const int total = base + n;
     const int r0 = qg * NQ;
     const int nv = min(NQ, n - r0); // valid rows in this query group (>= 1)
@@ -141,21 +159,13 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
         }
     }
     // rows ascend, so do both bounds
-    const int lo_min = lo_r[0], hi_min = hi_r[0];
-    int lo_max = lo_r[0], hi_max = hi_r[0];
+    const int hi_min = hi_r[0];
+    int lo_max = lo_r[0];
 #pragma unroll
     for (int q = 1; q < NQ; ++q) {
-        if (q < nv) {
-            lo_max = lo_r[q];
-            hi_max = hi_r[q];
-        }
+        if (q < nv) lo_max = lo_r[q];
     }
 
-    // this CTA's share of [lo_min, hi_max)
-    const int span = hi_max - lo_min;
-    const int per = ((span + p.splits - 1) / p.splits + CH - 1) / CH * CH;
-    const int k0 = min(hi_max, lo_min + sp * per);
-    const int k1 = min(hi_max, k0 + per);
     // keys all valid rows see, served from the cache
     int F0 = max(k0, lo_max);
     int F1 = min(k1, hi_min);
@@ -299,7 +309,9 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
                 const float pe = exp2f(sv - mref);
                 l[q] = l[q] * corr + pe;
                 scale4(acc[q], corr);
-                fma4(acc[q], pe, vv);
+                // a key the row does not see contributes nothing, whatever its value row holds
+                // (the reference skips zero weights, ops/attn_core_cpu.c:48)
+                fma4(acc[q], pe, vis ? vv : make_float4(0.f, 0.f, 0.f, 0.f));
                 m[q] = mn;
             }
         }
@@ -330,8 +342,9 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
     }
 
     // ---- merge warps through shared memory ---------------------------------
-    __shared__ float4 sm_acc[kDecWarps][NQ][LPK];
-    __shared__ float sm_m[kDecWarps][NQ], sm_l[kDecWarps][NQ];
+    auto &sm_acc = sh.acc;
+    auto &sm_m = sh.m;
+    auto &sm_l = sh.l;
     if (grp == 0) {
 #pragma unroll
         for (int q = 0; q < NQ; ++q) {
@@ -359,12 +372,12 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
             fma4(A, cw, sm_acc[w][q][c]);
         }
         const int r = r0 + q;
-        if (p.splits == 1) {
+        if (direct) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             if (L > 0.0f) o = make_float4(A.x / L, A.y / L, A.z / L, A.w / L);
             *reinterpret_cast<float4 *>(p.out + (int64_t)(b * n + r) * p.out_stride + (int64_t)h * HD + c * 4) = o;
         } else {
-            float *w = p.ws + ((((int64_t)b * p.H + h) * n + r) * p.splits + sp) * dec_partial_floats<HD>();
+            float *w = wdst + (int64_t)q * wrow;
             *reinterpret_cast<float4 *>(w + c * 4) = A;
             if (c == 0) {
                 w[HD] = M;
@@ -374,7 +387,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
     }
 
     // ---- write-through of the appended rows --------------------------------
-    if (p.kn && sp == p.splits - 1 && qg == 0) {
+    if (write_through) {
         for (int t = tid; t < n * LPK; t += kDecThreads) {
             const int row = t / LPK, c = t - row * LPK;
             const int64_t src = (int64_t)(b * n + row) * p.new_stride + (int64_t)h * HD + c * 4;
@@ -383,6 +396,205 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
             if (p.rope_cos) knew = rope_pairs(knew, p.rope_cos, p.rope_sin, base + row, HD / 2, c * 2);
             *reinterpret_cast<float4 *>(p.kc + dst) = knew;
             *reinterpret_cast<float4 *>(p.vc + dst) = ld4(p.vn + src);
+        }
+    }
+}
+
+template <int HD, int NQ>
+__host__ __device__ constexpr int dec_chunk_keys() { // keys per warp per chunk of the unmasked stream (CH above)
+    constexpr int LPK = HD / 4, KPW = 32 / LPK;
+    constexpr int U = (LPK / NQ) > 8 ? 8 : ((LPK / NQ) < 1 ? 1 : (LPK / NQ));
+    return KPW * U;
+}
+
+// Grid form: CTA = (head, key-range split, sequence x query group).
+template <int HD, int NQ>
+__global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p) {
+    constexpr int CH = dec_chunk_keys<HD, NQ>();
+    __shared__ DecShared<HD, NQ> sh;
+    const int h = blockIdx.x, sp = blockIdx.y;
+    const int b = blockIdx.z / p.qgroups, qg = blockIdx.z - b * p.qgroups;
+    const int base = p.base_len[b] + p.base_add;
+    const int r0 = qg * NQ, nv = min(NQ, p.n_new - r0);
+    int lo_min, hi_max;
+    dec_group_range(p, base, r0, nv, lo_min, hi_max);
+    // this CTA's share of [lo_min, hi_max)
+    const int span = hi_max - lo_min;
+    const int per = ((span + p.splits - 1) / p.splits + CH - 1) / CH * CH;
+    const int k0 = min(hi_max, lo_min + sp * per);
+    const int k1 = min(hi_max, k0 + per);
+    float *w = p.ws + ((((int64_t)b * p.H + h) * p.n_new + r0) * p.splits + sp) * dec_partial_floats<HD>();
+    decode_piece<HD, NQ>(p, sh, b, h, qg, base, k0, k1, p.splits == 1, w, (int64_t)p.splits * dec_partial_floats<HD>(),
+                         p.kn != nullptr && sp == p.splits - 1 && qg == 0);
+}
+
+// ---------------------------------------------------------------------------
+// Stream form: a persistent grid, one CTA per resident slot of the GPU, over the
+// linearised (sequence, query group, head, key block) space. Every CTA takes an
+// equal, contiguous share of that space, so all of them stream about the same
+// number of cache rows and finish together whatever the per-sequence lengths and
+// however the unit count divides by the number of slots; a share may begin and
+// end inside a unit, and such pieces leave (acc, m, l) partials that a second
+// small launch merges. The lengths live in device memory, so every CTA derives
+// the partition itself from a prefix sum over the sequences (shared memory).
+// No CTA waits for another one anywhere.
+// ---------------------------------------------------------------------------
+constexpr int kPieceValid = 4, kPieceHead = 1, kPieceTail = 2;
+struct DecStreamLayout { // workspace: [2 * G piece descriptors (unit, flags)] [2 * G * NQ partials]
+    int2 *desc;
+    float *part;
+};
+__host__ __device__ inline size_t dec_stream_desc_bytes(int G) { return ((size_t)G * 2 * sizeof(int2) + 255) & ~(size_t)255; }
+
+// Key blocks of sequence b: the union of its query groups' ranges cut into pieces of `A` keys.
+__device__ __forceinline__ void dec_seq_span(const DecodeParams &p, int base, int &lo_u, int &hi_u) {
+    hi_u = base + p.n_new;
+    lo_u = (p.window > 0 && !p.block_mode) ? max(0, base + 1 - p.window) : 0;
+}
+
+template <int HD, int NQ>
+__global__ void __launch_bounds__(kDecThreads, NQ <= 4 ? 5 : 3) decode_stream_kernel(DecodeParams p, int2 *desc, float *part) {
+    constexpr int A = dec_chunk_keys<HD, NQ>() * kDecWarps; // keys per block: one chunk for every warp
+    constexpr int PF = dec_partial_floats<HD>();
+    extern __shared__ int s_pref[]; // [batch + 1]: blocks before sequence b
+    __shared__ DecShared<HD, NQ> sh;
+    __shared__ int s_warp_sum[kDecWarps];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int units_per_seq = p.H * p.qgroups;
+
+    // ---- prefix sum of the sequences' block counts ------------------------------
+    {
+        const int per_thread = (p.batch + kDecThreads - 1) / kDecThreads;
+        const int b0 = tid * per_thread, b1 = min(p.batch, b0 + per_thread);
+        int local = 0;
+        for (int b = b0; b < b1; ++b) {
+            int lo_u, hi_u;
+            dec_seq_span(p, p.base_len[b] + p.base_add, lo_u, hi_u);
+            const int nb = (hi_u - lo_u + A - 1) / A;
+            s_pref[b] = local; // exclusive, within this thread's run
+            local += nb * units_per_seq;
+        }
+        int incl = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += t;
+        }
+        if (lane == 31) s_warp_sum[warp] = incl;
+        __syncthreads();
+        int before = incl - local;
+        for (int w = 0; w < warp; ++w) before += s_warp_sum[w];
+        for (int b = b0; b < b1; ++b) s_pref[b] += before;
+        if (tid == kDecThreads - 1) s_pref[p.batch] = before + local;
+        __syncthreads();
+    }
+    const int64_t T = s_pref[p.batch];
+    const int G = gridDim.x, g = blockIdx.x;
+    int x = (int)(T * g / G);
+    const int x_end = (int)(T * (g + 1) / G);
+    if (tid == 0) {
+        desc[g * 2] = make_int2(0, 0);
+        desc[g * 2 + 1] = make_int2(0, 0);
+    }
+    bool first = true;
+    int b = 0;
+    while (x < x_end) {
+        // sequence holding block x: s_pref[b] <= x < s_pref[b + 1] (pieces ascend, so does b)
+        {
+            int lo = b, hi = p.batch;
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (s_pref[mid] <= x) lo = mid;
+                else hi = mid;
+            }
+            b = lo;
+        }
+        const int base = p.base_len[b] + p.base_add;
+        int lo_u, hi_u;
+        dec_seq_span(p, base, lo_u, hi_u);
+        const int nb = (hi_u - lo_u + A - 1) / A;
+        const int local = x - s_pref[b];
+        const int ul = local / nb, blk0 = local - ul * nb;
+        const int blk1 = min(nb, blk0 + (x_end - x));
+        const int qg = ul / p.H, h = ul - qg * p.H;
+        const int r0 = qg * NQ, nv = min(NQ, p.n_new - r0);
+        int lo_min, hi_max;
+        dec_group_range(p, base, r0, nv, lo_min, hi_max);
+        int k0 = max(lo_min, lo_u + blk0 * A);
+        int k1 = min(hi_max, lo_u + blk1 * A);
+        if (k1 < k0) k1 = k0; // a block outside this group's own range: an empty piece
+        const bool head = blk0 == 0, tail = blk1 == nb, whole = head && tail;
+        const int slot = g * 2 + (first ? 0 : 1);
+        if (!whole && tid == 0)
+            desc[slot] = make_int2(b * units_per_seq + ul, kPieceValid | (head ? kPieceHead : 0) | (tail ? kPieceTail : 0));
+        decode_piece<HD, NQ>(p, sh, b, h, qg, base, k0, k1, whole, part + (int64_t)slot * NQ * PF, PF,
+                             p.kn != nullptr && tail && qg == 0);
+        __syncthreads(); // the warps' shared state is reused by the next piece
+        x += blk1 - blk0;
+        first = false;
+    }
+}
+
+// The CTA after gg that holds the next piece of `unit` (its first slot): CTAs whose share was empty
+// (more CTAs than blocks) wrote no descriptor and are stepped over.
+__device__ __forceinline__ bool next_piece(const int2 *desc, int G, int unit, int &gg) {
+    for (++gg; gg < G; ++gg) {
+        const int2 d = desc[gg * 2];
+        if (!(d.y & kPieceValid)) continue;
+        return d.x == unit && !(d.y & kPieceHead);
+    }
+    return false;
+}
+
+// Merge pass of the stream form: CTA g owns the unit whose first piece is g's last piece (or its
+// only one) when that unit continues into the following CTAs; the continuation pieces are the
+// first pieces of g + 1, g + 2, ... up to the one flagged as the unit's end.
+template <int HD, int NQ>
+__global__ void __launch_bounds__(128) decode_stream_merge_kernel(DecodeParams p, const int2 *desc, const float *part) {
+    constexpr int LPK = HD / 4, PF = dec_partial_floats<HD>();
+    const int g = blockIdx.x, G = gridDim.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int own = -1;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+        const int2 d = desc[g * 2 + s];
+        if ((d.y & kPieceValid) && (d.y & kPieceHead) && !(d.y & kPieceTail)) own = s;
+    }
+    if (own < 0) return;
+    const int unit = desc[g * 2 + own].x;
+    const int units_per_seq = p.H * p.qgroups;
+    const int b = unit / units_per_seq, ul = unit - b * units_per_seq;
+    const int qg = ul / p.H, h = ul - qg * p.H;
+    const int nv = min(NQ, p.n_new - qg * NQ);
+    for (int q = warp; q < nv; q += 4) {
+        // pass 1: the row maximum over the pieces; pass 2: the weighted sums
+        float M = -INFINITY;
+        {
+            int gg = g, s = own;
+            while (true) {
+                M = fmaxf(M, part[((int64_t)(gg * 2 + s) * NQ + q) * PF + HD]);
+                if (desc[gg * 2 + s].y & kPieceTail) break;
+                if (!next_piece(desc, G, unit, gg)) break;
+                s = 0;
+            }
+        }
+        const float mref = M == -INFINITY ? 0.0f : M;
+        if (lane < LPK) {
+            float L = 0.0f;
+            float4 Acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            int gg = g, s = own;
+            while (true) {
+                const float *w = part + ((int64_t)(gg * 2 + s) * NQ + q) * PF;
+                const float cw = exp2f(w[HD] - mref);
+                L += w[HD + 1] * cw;
+                fma4(Acc, cw, *reinterpret_cast<const float4 *>(w + lane * 4));
+                if (desc[gg * 2 + s].y & kPieceTail) break;
+                if (!next_piece(desc, G, unit, gg)) break;
+                s = 0;
+            }
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (L > 0.0f) o = make_float4(Acc.x / L, Acc.y / L, Acc.z / L, Acc.w / L);
+            *reinterpret_cast<float4 *>(p.out + (int64_t)(b * p.n_new + qg * NQ + q) * p.out_stride + (int64_t)h * HD + lane * 4) = o;
         }
     }
 }
@@ -461,15 +673,111 @@ static int validate_decode(const fblt_decode_desc *d) {
     return FBLT_OK;
 }
 
-template <int HD>
-static int launch_decode_hd(const DecodeParams &p, int nq, cudaStream_t stream) {
-    dim3 grid(p.H, p.splits, p.batch * p.qgroups);
-    switch (nq) {
-    case 1: decode_attn_kernel<HD, 1><<<grid, kDecThreads, 0, stream>>>(p); break;
-    case 2: decode_attn_kernel<HD, 2><<<grid, kDecThreads, 0, stream>>>(p); break;
-    case 4: decode_attn_kernel<HD, 4><<<grid, kDecThreads, 0, stream>>>(p); break;
-    default: decode_attn_kernel<HD, 8><<<grid, kDecThreads, 0, stream>>>(p); break;
+// ---- launch plan: grid form or stream form ---------------------------------------
+struct DecodePlan {
+    bool stream;  // persistent grid over equal shares of the key-block space
+    int grid;     // stream form: number of CTAs
+    int splits;   // grid form: key-range pieces per unit
+    size_t need;  // bytes of scratch for partials (and, stream form, piece descriptors)
+};
+
+constexpr int kStreamMaxBatch = 8192; // the per-sequence prefix sum sits in shared memory
+
+template <int HD, int NQ>
+static int stream_slots_t(int *slots) {
+    static std::atomic<int> cache[64]; // resident CTAs of this instantiation per device ordinal, 0 = not asked yet
+    int dev = 0;
+    FBLT_CUDA_TRY(cudaGetDevice(&dev));
+    int v = dev < 64 ? cache[dev].load(std::memory_order_relaxed) : 0;
+    if (!v) {
+        int per_sm = 0, sms = 0;
+        FBLT_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stream_kernel<HD, NQ>, kDecThreads,
+                                                                    (kStreamMaxBatch + 1) * sizeof(int)));
+        FBLT_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        v = per_sm * sms;
+        if (v < 1) return fail(FBLT_ERR_CUDA, "decode: the stream kernel does not fit an SM");
+        if (dev < 64) cache[dev].store(v, std::memory_order_relaxed);
     }
+    *slots = v;
+    return FBLT_OK;
+}
+
+static int stream_slots(int hd, int nq, int *slots) {
+#define FBLT_SLOTS(HD)                                                  \
+    switch (nq) {                                                       \
+    case 1: return stream_slots_t<HD, 1>(slots);                        \
+    case 2: return stream_slots_t<HD, 2>(slots);                        \
+    case 4: return stream_slots_t<HD, 4>(slots);                        \
+    default: return stream_slots_t<HD, 8>(slots);                       \
+    }
+    switch (hd) {
+    case 32: FBLT_SLOTS(32)
+    case 64: FBLT_SLOTS(64)
+    default: FBLT_SLOTS(128)
+    }
+#undef FBLT_SLOTS
+}
+
+static int chunk_keys(int hd, int nq) { // dec_chunk_keys<HD, NQ>() for run-time values
+    const int lpk = hd / 4, kpw = 32 / lpk;
+    int u = lpk / nq;
+    u = u > 8 ? 8 : (u < 1 ? 1 : u);
+    return kpw * u;
+}
+
+// splits > 0: the grid form with that many pieces. splits == 0: the library chooses -- the grid form with
+// a split count from the launch width, which is the faster of the two on every measured shape (it keeps
+// the CTAs that run together on neighbouring heads of the same cache rows); FBLT_DECODE_MODE=stream in
+// the environment selects the stream form instead. splits < 0: the stream form or an error.
+static int make_plan(const fblt_decode_desc *d, bool allow_stream, DecodePlan *plan) {
+    const int nq = pick_nq(d->n_new);
+    const int qgroups = (d->n_new + nq - 1) / nq;
+    plan->stream = false;
+    plan->grid = 0;
+    bool want = allow_stream && d->splits < 0;
+    if (allow_stream && d->splits == 0) {
+        const char *e = getenv("FBLT_DECODE_MODE");
+        if (e && !strcmp(e, "stream")) want = true;
+    }
+    const int A = chunk_keys(d->head_dim, nq) * kDecWarps;
+    const int64_t max_blocks = (int64_t)d->batch * d->num_heads * qgroups * ((d->max_len > 0 ? d->max_len : 0) / A + 1);
+    const bool fits = d->batch <= kStreamMaxBatch && d->max_len > 0 && max_blocks < (int64_t)1 << 30;
+    if (want && fits) {
+        int slots = 0;
+        const int st = stream_slots(d->head_dim, nq, &slots);
+        if (st != FBLT_OK) return st;
+        // no more CTAs than there are shares of a few blocks each
+        int64_t g = max_blocks / 4;
+        if (g < 1) g = 1;
+        if (g > slots) g = slots;
+        plan->stream = true;
+        plan->grid = (int)g;
+        plan->splits = 1;
+        plan->need = dec_stream_desc_bytes(plan->grid) + (size_t)plan->grid * 2 * nq * partial_floats(d->head_dim) * sizeof(float);
+        return FBLT_OK;
+    }
+    if (d->splits < 0) return fail(FBLT_ERR_UNSUPPORTED, "decode: the stream form needs batch <= %d and max_len set", kStreamMaxBatch);
+    plan->splits = resolve_splits(d);
+    plan->need = plan->splits <= 1 ? 0
+                                   : (size_t)d->batch * d->num_heads * d->n_new * plan->splits * partial_floats(d->head_dim) * sizeof(float);
+    return FBLT_OK;
+}
+
+template <int HD, int NQ>
+static int launch_decode_t(const DecodeParams &p, const DecodePlan &plan, cudaStream_t stream) {
+    if (plan.stream) {
+        int2 *desc = reinterpret_cast<int2 *>(p.ws);
+        float *part = reinterpret_cast<float *>(reinterpret_cast<char *>(p.ws) + dec_stream_desc_bytes(plan.grid));
+        decode_stream_kernel<HD, NQ><<<plan.grid, kDecThreads, (p.batch + 1) * sizeof(int), stream>>>(p, desc, part);
+        count_launch();
+        int st = check_launch("decode_stream_kernel");
+        if (st != FBLT_OK) return st;
+        decode_stream_merge_kernel<HD, NQ><<<plan.grid, 128, 0, stream>>>(p, desc, part);
+        count_launch();
+        return check_launch("decode_stream_merge_kernel");
+    }
+    dim3 grid(p.H, p.splits, p.batch * p.qgroups);
+    decode_attn_kernel<HD, NQ><<<grid, kDecThreads, 0, stream>>>(p);
     count_launch();
     int st = check_launch("decode_attn_kernel");
     if (st != FBLT_OK) return st;
@@ -482,15 +790,25 @@ static int launch_decode_hd(const DecodeParams &p, int nq, cudaStream_t stream) 
     return st;
 }
 
+template <int HD>
+static int launch_decode_hd(const DecodeParams &p, const DecodePlan &plan, int nq, cudaStream_t stream) {
+    switch (nq) {
+    case 1: return launch_decode_t<HD, 1>(p, plan, stream);
+    case 2: return launch_decode_t<HD, 2>(p, plan, stream);
+    case 4: return launch_decode_t<HD, 4>(p, plan, stream);
+    default: return launch_decode_t<HD, 8>(p, plan, stream);
+    }
+}
+
 // The one place a descriptor becomes kernel parameters; both entry points go through it.
-static DecodeParams fill_decode_params(const fblt_decode_desc *d, float *partials) {
+static DecodeParams fill_decode_params(const fblt_decode_desc *d, const DecodePlan &plan, float *scratch) {
     DecodeParams p;
     p.batch = d->batch;
     p.H = d->num_heads;
     p.n_new = d->n_new;
     p.block_mode = d->block_mode ? 1 : 0;
     p.window = d->window > 0 ? d->window : 0;
-    p.splits = resolve_splits(d);
+    p.splits = plan.splits;
     const int nq = pick_nq(d->n_new);
     p.qgroups = (d->n_new + nq - 1) / nq;
     p.base_len = d->base_len;
@@ -506,29 +824,29 @@ static DecodeParams fill_decode_params(const fblt_decode_desc *d, float *partial
     p.new_stride = d->kv_new_stride;
     p.out = d->out;
     p.out_stride = d->out_stride;
-    p.ws = partials;
+    p.ws = scratch;
     p.qscale = d->scale * kLog2e;
     p.rope_cos = d->rope_cos;
     p.rope_sin = d->rope_sin;
     return p;
 }
 
-static int launch_decode(const fblt_decode_desc *d, const DecodeParams &p, cudaStream_t s) {
+static int launch_decode(const fblt_decode_desc *d, const DecodeParams &p, const DecodePlan &plan, cudaStream_t s) {
     const int nq = pick_nq(d->n_new);
     switch (d->head_dim) {
-    case 32: return launch_decode_hd<32>(p, nq, s);
-    case 64: return launch_decode_hd<64>(p, nq, s);
-    default: return launch_decode_hd<128>(p, nq, s);
+    case 32: return launch_decode_hd<32>(p, plan, nq, s);
+    case 64: return launch_decode_hd<64>(p, plan, nq, s);
+    default: return launch_decode_hd<128>(p, plan, nq, s);
     }
 }
 
 } // namespace fblt
 
 extern "C" size_t fblt_attn_decode_workspace(const fblt_decode_desc *d) {
-    if (!d || d->batch <= 0) return 0;
-    const int splits = fblt::resolve_splits(d);
-    if (splits <= 1) return 0;
-    return (size_t)d->batch * d->num_heads * d->n_new * splits * fblt::partial_floats(d->head_dim) * sizeof(float);
+    if (!d || d->batch <= 0 || fblt::validate_decode(d) != FBLT_OK) return 0;
+    fblt::DecodePlan plan;
+    if (fblt::make_plan(d, true, &plan) != FBLT_OK) return 0;
+    return plan.need;
 }
 
 extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size_t workspace_bytes, void *stream) {
@@ -537,15 +855,17 @@ extern "C" int fblt_attn_decode(const fblt_decode_desc *d, void *workspace, size
     int st = validate_decode(d);
     if (st != FBLT_OK) return st;
     if (d->batch == 0) return FBLT_OK;
-    const DecodeParams p = fill_decode_params(d, (float *)workspace);
-    if (p.splits > 1) {
-        const size_t need = fblt_attn_decode_workspace(d);
-        if (!workspace || workspace_bytes < need)
-            return fail(FBLT_ERR_WORKSPACE, "decode: %d splits need %zu bytes of workspace, got %zu", p.splits, need,
-                        workspace_bytes);
+    DecodePlan plan;
+    st = make_plan(d, true, &plan);
+    if (st != FBLT_OK) return st;
+    if (plan.need > 0) {
+        if (!workspace || workspace_bytes < plan.need)
+            return fail(FBLT_ERR_WORKSPACE, "decode: %zu bytes of workspace needed (fblt_attn_decode_workspace), got %zu",
+                        plan.need, workspace_bytes);
         if ((uintptr_t)workspace & 15) return fail(FBLT_ERR_ARG, "decode: workspace must be 16-byte aligned");
     }
-    return launch_decode(d, p, (cudaStream_t)stream);
+    const DecodeParams p = fill_decode_params(d, plan, (float *)workspace);
+    return launch_decode(d, p, plan, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -592,17 +912,22 @@ extern "C" int fblt_attn_decode_static(const fblt_decode_desc *d, void *stream) 
     int st = validate_decode(d);
     if (st != FBLT_OK) return st;
     if (d->batch == 0) return FBLT_OK;
-    const int splits = resolve_splits(d);
-    const size_t need = fblt_attn_decode_workspace(d);
-    if (need > kStaticScratchBytes)
+    DecodePlan plan;
+    st = make_plan(d, true, &plan);
+    if (st != FBLT_OK) return st;
+    if (plan.stream && plan.need > kStaticScratchBytes && d->splits == 0) { // stream form chosen by the environment
+        st = make_plan(d, false, &plan); // the grid form may need less
+        if (st != FBLT_OK) return st;
+    }
+    if (plan.need > kStaticScratchBytes)
         return fail(FBLT_ERR_LIMIT,
-                    "decode_static: %d splits of this batch need %zu bytes of partials; the built-in scratch holds %zu "
+                    "decode_static: this call needs %zu bytes of partials; the built-in scratch holds %zu "
                     "(use fblt_attn_decode with a caller workspace, or set splits = 1)",
-                    splits, need, kStaticScratchBytes);
+                    plan.need, kStaticScratchBytes);
     float *scratch = nullptr;
     st = static_scratch_address(&scratch);
     if (st != FBLT_OK) return st;
-    // every (row, split) slot is written before the merge kernel reads it: nothing to clear
-    const DecodeParams p = fill_decode_params(d, scratch);
-    return launch_decode(d, p, (cudaStream_t)stream);
+    // every slot the merge kernels read is written by the launch before them: nothing to clear
+    const DecodeParams p = fill_decode_params(d, plan, scratch);
+    return launch_decode(d, p, plan, (cudaStream_t)stream);
 }

@@ -151,6 +151,7 @@ extern "C" int fblt_session_create(fblt_session **out, int32_t max_batch, int32_
         // split-K partials exist only while (sequences x heads) is below the
         // launch-width target, which bounds units x splits
         s->ws_bytes = (size_t)2048 * max_new * ((size_t)head_dim + 4) * sizeof(float);
+        if (s->ws_bytes < ((size_t)8 << 20)) s->ws_bytes = (size_t)8 << 20; // the stream form: two partials per resident CTA
         S_TRY(cudaMalloc(&s->ws, s->ws_bytes));
     }
 #undef S_TRY

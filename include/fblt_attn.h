@@ -383,7 +383,9 @@ typedef struct {
     int32_t block_mode;
     int32_t window;
     int32_t max_len;  /* host-known upper bound of base_len[b] + n_new */
-    int32_t splits;   /* key-range splits per (sequence, head); 0 = choose */
+    int32_t splits;   /* > 0: key-range pieces per (sequence, head), one CTA each; 0 = choose;
+                       * < 0: persistent grid over equal shares of all key blocks (batch <= 8192,
+                       * max_len required), for few sequences of very unequal length */
     const int32_t *base_len; /* device [batch] */
     float *k_cache;          /* device */
     float *v_cache;

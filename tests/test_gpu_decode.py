@@ -47,7 +47,8 @@ def test_c4_decode_and_block_verify(cuda_lib):
 def test_query_counts_and_modes(cuda_lib, n_new, block_mode):
     lens = [0, 1, 5, 31, 32, 33, 64, 100, 257]
     case = workloads.decode_case(70 + n_new, len(lens), 2, n_new, block_mode, lens=lens)
-    check(case)
+    check(case)                     # the library's choice of pieces
+    check(case, splits=-1)          # persistent grid over equal shares
     check(case, fused_append=False, splits=3)
 
 
@@ -75,6 +76,45 @@ def test_other_head_dims(cuda_lib, hd):
     check(case)
     case.block_mode = False
     check(case, splits=2)
+
+
+@pytest.mark.parametrize("shape", ["few_long", "many_short", "ragged_window", "one"])
+def test_stream_form_partitions(cuda_lib, shape):
+    """The persistent form cuts the (sequence, head, key block) space into equal shares: units that span
+    many CTAs, CTAs that cover many units, shares that begin and end inside a unit, empty sequences."""
+    rng = np.random.default_rng(12)
+    if shape == "few_long":
+        case = workloads.decode_case(301, 3, 2, 4, True, lens=[4000, 1, 2500])
+    elif shape == "many_short":
+        case = workloads.decode_case(302, 700, 4, 1, False, lens=rng.integers(0, 90, 700))
+    elif shape == "ragged_window":
+        case = workloads.decode_case(303, 37, 2, 7, False, lens=rng.integers(0, 600, 37), window=130)
+    else:
+        case = workloads.decode_case(304, 1, 1, 2, True, lens=[777])
+    got_s, _, _ = check(case, splits=-1)
+    got_g, _, _ = check(case, splits=1)
+    assert_close(got_s, got_g, "stream vs grid", atol=1e-6, rtol=1e-5)
+    check(case, splits=-1, fused_append=False)
+
+
+def test_zero_weight_keys_ignore_their_values(cuda_lib):
+    """A key a row does not see contributes nothing even when its value row holds Inf or NaN (the
+    reference skips zero weights, ops/attn_core_cpu.c:48): rows in front of the window and, for the
+    earlier rows of a causal block, the appended rows behind them."""
+    n, window = 4, 40
+    case = workloads.decode_case(305, 3, 2, n, False, lens=[100, 64, 300], window=window)
+    want, _ = oracle_decode(case)
+    for b, base in enumerate(case.base_len):
+        case.v_cache[b, :max(0, int(base) + 1 - window)] = np.inf        # before every row's window
+        case.v_cache[b, max(0, int(base) + 1 - window)] = 1.0e30          # seen by row 0 only: finite, large
+    case.v_new[n - 1::n] = np.nan                                         # last appended row: only row n-1 sees it
+    want2, _ = oracle_decode(case)
+    keep = np.ones(len(want), bool)
+    keep[n - 1::n] = False
+    for sp in (0, 1, 2):
+        got, _, _ = decode_gpu(case, splits=sp)
+        assert np.isfinite(got[keep]).all(), f"splits={sp}"
+        assert_close(got[keep], want2[keep], f"zero-weight values, splits={sp}", atol=1e-4, rtol=1e-3)
 
 
 def test_c5_decode_sample(cuda_lib):
