@@ -4,9 +4,11 @@ One step = one pass of the hot path over the whole batch: block-causal patch-tra
 prefill attention (16 heads x 64, patch structure from the seeded generator) followed by 64
 KV-cache decode steps with a block of 4 verify rows (cache 512 -> 768 rows), for 2048
 independent sequences sharded by batch over the ranks; when the batch is partitioned the
-outputs are gathered over NVLink, by default with one-sided copy-engine copies into the peers'
-symmetric-memory buffers (`--gather peer`; no SM is taken from the attention launches) or with
-NCCL all-gathers (`--gather nccl`, also the fallback when the peer set-up fails).
+outputs are gathered over NVLink, by default with the library's own gather (`--gather ipc`:
+fblt_gather_* of the C ABI, one-sided copy-engine copies into IPC-mapped peer buffers after a
+host-side check-in; no SM is taken from the attention launches), with the same copies over
+torch's symmetric memory (`--gather peer`) or with NCCL all-gathers (`--gather nccl`, also the
+fallback when the peer set-up fails).
 
     python bench.py [--gpus N --steps K --warmup W]            # this library
     python bench.py --impl reference [...]                     # reference CPU operator, host cores
@@ -221,7 +223,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=2048, help="total sequences over all ranks")
     ap.add_argument("--decode-steps", type=int, default=64)
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--cpu-prefill-seqs", type=int, default=512)
     ap.add_argument("--cpu-decode-seqs", type=int, default=128)
     ap.add_argument("--cpu-decode-steps", type=int, default=8)
@@ -232,12 +234,14 @@ def main():
                     help="matmul workload: only the decode-step shapes (8192 rows), for profiler captures")
     ap.add_argument("--gather-chunks", type=int, default=4,
                     help="N > 1: the decode rows of a step are gathered in this many pieces while the launches go on")
-    ap.add_argument("--gather", default="peer", choices=["nccl", "peer"],
-                    help="N > 1: outputs gathered by NCCL all-gather kernels, or by one-sided copy-engine copies into "
-                         "the peers' symmetric-memory buffers")
+    ap.add_argument("--gather", default="ipc", choices=["nccl", "peer", "ipc"],
+                    help="N > 1: outputs gathered by the library's own one-sided copy-engine copies into IPC-mapped peer "
+                         "buffers (ipc: fblt_gather_* of the C ABI), by the same copies over torch's symmetric memory "
+                         "(peer), or by NCCL all-gather kernels (nccl)")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="N > 1: cap on the CTAs of an NCCL gather (0 = NCCL's default)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg")
+    ap.add_argument("--no-configs", action="store_true", help="skip the small configurations (`configs` key, one GPU)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -284,6 +288,9 @@ def main():
         if args.nccl_max_ctas > 0:
             # the gathers share the GPU with the decode launches: fewer NCCL CTAs leave more SMs to them
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_max_ctas))
+        # plain rings / trees for the few collectives this job makes: a rank that leaves early must not
+        # be bound to an NVLink multicast object (the gathers themselves are peer copies)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         # a collective that stays enqueued past this deadline is aborted by the process group's watchdog
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
@@ -322,6 +329,22 @@ def main():
     main_stream = torch.cuda.Stream(device=dev)
     comm_stream = torch.cuda.Stream(device=dev)
     if world > 1:
+        # every rank has built its shard: check in on the HOST before anything collective happens (the
+        # gather set-up below, the first all-reduce), so that a rank that died or fell behind while
+        # building is named here instead of leaving the others inside a collective
+        torch.cuda.synchronize()
+        try:
+            shard.rendezvous(shard.default_store(), rank, world, "bench-setup", deadline_s=240.0)
+        except (shard.RankTimeout, shard.RankFailed) as exc:
+            sys.stderr.write(f"rank {rank}: {exc}\n")
+            dist.destroy_process_group()
+            sys.exit(3)
+        store = shard.default_store()
+        if rank == 0:
+            import tempfile
+            base = "/dev/shm" if os.path.isdir("/dev/shm") else None
+            store.set("fblt/exchange_dir", tempfile.mkdtemp(prefix="fblt_bench_", dir=base).encode())
+        exchange_dir = store.get("fblt/exchange_dir").decode()
         max_rows = max(rows_per_rank)
         pad_p = torch.zeros((max_rows, E), device=dev)
         gath_p = torch.empty((world, max_rows, E), device=dev)
@@ -333,11 +356,16 @@ def main():
             if args.gather == "nccl" else None
         peer_p = peer_d = None
         gather_mode = args.gather
-        if args.gather == "peer":
-            # collective set-up; if it fails on any rank, every rank falls back to NCCL all-gathers
+        if args.gather in ("ipc", "peer"):
+            # set-up; if it fails on any rank, every rank falls back to NCCL all-gathers
             try:
-                peer_p = shard.PeerGather(max_rows, E, dev)
-                peer_d = [shard.PeerGather(chunk_steps * B * N_NEW, E, dev) for _ in range(n_chunks)]
+                if args.gather == "ipc":     # the library's own gather: C ABI, IPC-mapped peers, host check-in
+                    peer_p = shard.IpcGather(max_rows, E, rank, world, exchange_dir, "prefill")
+                    peer_d = [shard.IpcGather(chunk_steps * B * N_NEW, E, rank, world, exchange_dir, f"decode{c}")
+                              for c in range(n_chunks)]
+                else:                        # torch's symmetric memory + Tensor.copy_
+                    peer_p = shard.PeerGather(max_rows, E, dev)
+                    peer_d = [shard.PeerGather(chunk_steps * B * N_NEW, E, dev) for _ in range(n_chunks)]
                 ok = torch.ones(1, device=dev)
             except Exception as exc:   # noqa: BLE001 - any set-up failure selects the fallback
                 sys.stderr.write(f"rank {rank}: peer gather unavailable ({exc}); using NCCL\n")
@@ -416,10 +444,6 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    if world > 1:
-        # every rank has built its shard: check in on the host before the first gather is enqueued,
-        # so that a rank that died or fell behind during setup is named here instead of stalling a collective
-        shard.rendezvous(shard.default_store(), rank, world, "bench-setup", deadline_s=240.0)
     for it in range(args.warmup):
         one_step(it)
     barrier()
@@ -506,6 +530,11 @@ def main():
         cpu = run_cpu_baseline(args, torch, qkv, cu, kc, vc, qn, kn, vn, out_p,
                                out_d2[(args.warmup + args.steps - 1) % len(out_d2)], total_rows)
 
+    # ---- the small configurations at their full sizes (microseconds each; one GPU only) ----
+    configs = None
+    if rank == 0 and world == 1 and not args.no_configs:
+        configs = small_config_lines(args, with_tf32=False)
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -514,16 +543,33 @@ def main():
             "roofline": roofline, "prefill": prefill, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks, "host_binding": numa,
             "gather": gather,
             "job_bytes": total_bytes,
+            "configs": configs,
         }
         emit(line)
     if world > 1:
+        barrier()          # nobody frees a receive buffer a peer may still be writing into
+        if peer_p is not None and hasattr(peer_p, "close"):
+            for g_ in [peer_p] + list(peer_d):
+                g_.close()
         dist.destroy_process_group()
 
 
 def run_small_configs(args):
+    """`--workload configs`: one JSON line per small configuration (both precisions) and the decode-step loop."""
+    import torch
+    from fblt_b200 import ops
+    for line in small_config_lines(args, with_tf32=True):
+        emit(line)
+    run_decode_loop(args, torch, ops, emit)
+
+
+def small_config_lines(args, with_tf32: bool):
     """Device time, roofline fraction, CPU reference time and max error of every small
     configuration at its full size (inputs from the seeded host generators). L2 is flushed
-    between timed iterations because these working sets fit in it."""
+    between timed iterations because these working sets fit in it. The decode configurations are
+    also timed as a run of back-to-back launches over rotating copies of the caches (together
+    larger than L2), which is how a decode loop issues them: launch latency then overlaps the
+    previous launch."""
     import torch
     sys.path.insert(0, str(ROOT / "tests"))
     from fblt_b200 import lib as L
@@ -534,6 +580,7 @@ def run_small_configs(args):
     peaks_file = ROOT / "MEASURED_PEAKS.json"
     peak = float(json.loads(peaks_file.read_text())["hbm_gbs"]) if peaks_file.exists() else 6650.0
     flush = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+    lines = []
 
     def timed(fn):
         for _ in range(max(3, args.warmup)):
@@ -558,14 +605,14 @@ def run_small_configs(args):
                 "TFLOP/s": flops / ms / 1e9, "cpu_reference_ms": cpu_s * 1e3,
                 "cpu_cores": ob.host_cores(), "max_abs_err": err, "l2": "flushed between iterations"}
         line.update(extra or {})
-        emit(line)
+        lines.append(line)
 
     fwd = [workloads.c1_byte_self_attention(), workloads.c2_patch_attention(), workloads.c3_cross_attention("enc"),
            workloads.c3_cross_attention("dec_paper"), workloads.c3_cross_attention("dec_leq")]
     for case in fwd:
         q, k, v = upload_case(case)
         out = torch.empty((int(case.cu_q[-1]), case.embed), device="cuda")
-        for prec, tag in ((L.PREC_FP32, ""), (L.PREC_TF32, "+tf32")):
+        for prec, tag in ((L.PREC_FP32, ""), (L.PREC_TF32, "+tf32"))[: 2 if with_tf32 else 1]:
             b = ops.make_batch(q, k, v, out, case.cu_q, case.cu_k, case.num_heads, case.head_dim, case.scale, case.mask,
                                precision=prec)
             ms = timed(lambda: ops.attn_forward(b))
@@ -590,9 +637,32 @@ def run_small_configs(args):
         err = float(np.abs(out.cpu().numpy() - want).max())
         n, lens = case.n_new, case.base_len.astype(np.int64)
         pairs = int(((lens + n) * n).sum()) if case.block_mode else int(sum((lens + r + 1).sum() for r in range(n)))
+        # back to back over four copies of the caches (4 x 151 MB > L2), eight launches per timed run
+        sets = [(kc, vc)] + [(kc.clone(), vc.clone()) for _ in range(3)]
+        descs = [ops.make_decode(k_, v_, base, q, out, case.num_heads, case.head_dim, case.n_new, case.scale,
+                                 block_mode=case.block_mode, k_new=kn, v_new=vn,
+                                 max_len=int(case.base_len.max()) + case.n_new) for k_, v_ in sets]
+        def burst():
+            for i in range(8):
+                ops.attn_decode(descs[i % 4], ws)
+        for _ in range(3):
+            burst()
+        ts = []
+        for _ in range(10):
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            t0.record()
+            burst()
+            t1.record()
+            torch.cuda.synchronize()
+            ts.append(t0.elapsed_time(t1) / 8)
+        b2b = statistics.median(ts)
         report(case.name, ms, case.algorithmic_bytes(), 4 * case.head_dim * case.num_heads * pairs, cpu_s, err,
-               {"splits": int(d.splits)})
-    run_decode_loop(args, torch, ops, emit)
+               {"splits": int(d.splits), "ms_back_to_back": b2b,
+                "frac_of_hbm_peak_back_to_back": case.algorithmic_bytes() / b2b / 1e6 / peak,
+                "back_to_back": "8 launches over 4 rotating copies of the caches (larger than L2 together)"})
+        del sets, descs
+    return lines
 
 
 def run_decode_loop(args, torch, ops, emit_line):
@@ -841,8 +911,49 @@ def run_blocks(args):
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.010  # profiles/decode_attn_kernel_config5.md (256-sequence capture)
 
 
+def measure_host_link(torch, dev, barrier, world: int):
+    """Ceiling of the host link in this run: every rank copies a 1 GiB pinned buffer to its GPU and back
+    with plain asynchronous copies, all ranks at once -- one direction at a time and both together
+    (the session overlaps uploads and downloads). GB/s per GPU, the slowest rank's figure."""
+    import torch.distributed as dist
+    n = 1 << 30
+    host_a = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    host_b = torch.empty(n, dtype=torch.uint8, pin_memory=True)
+    host_a.fill_(1)
+    dev_a = torch.empty(n, dtype=torch.uint8, device=dev)
+    dev_b = torch.zeros(n, dtype=torch.uint8, device=dev)
+    s_up, s_down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+    def run(up: bool, down: bool, reps: int = 3) -> float:
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            if up:
+                with torch.cuda.stream(s_up):
+                    dev_a.copy_(host_a, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s_down):
+                    host_b.copy_(dev_b, non_blocking=True)
+        torch.cuda.synchronize()
+        sec = time.perf_counter() - t0
+        if world > 1:
+            tt = torch.tensor([sec], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            sec = float(tt[0])
+        return reps * n / sec / 1e9
+
+    run(True, True, 1)
+    res = {"h2d_GBps_per_gpu": run(True, False), "d2h_GBps_per_gpu": run(False, True)}
+    both = run(True, True)
+    res["duplex_GBps_per_gpu_each_way"] = both
+    res["how"] = "1 GiB pinned <-> device, cudaMemcpyAsync, all ranks concurrently, slowest rank"
+    del host_a, host_b, dev_a, dev_b
+    return res
+
+
 def run_e2e(args, torch, ops, dev, qkv, cu, rows, B, cache_rows, kc, vc, qn, kn, vn, world, total_bytes, barrier):
     import torch.distributed as dist
+    steps = args.decode_steps
     sess = ops.Session(B, H, HD, max_q_rows=rows, max_k_rows=rows, cache_rows=cache_rows, max_new=N_NEW)
     h_qkv = torch.empty((rows, 3 * E), dtype=torch.float32, pin_memory=True)
     h_qkv.copy_(qkv)
@@ -851,10 +962,14 @@ def run_e2e(args, torch, ops, dev, qkv, cu, rows, B, cache_rows, kc, vc, qn, kn,
     h_vc = torch.empty((B, BASE_LEN, E), dtype=torch.float32, pin_memory=True)
     h_kc.copy_(kc[:, :BASE_LEN])
     h_vc.copy_(vc[:, :BASE_LEN])
-    h_new = [torch.empty((B * N_NEW, E), dtype=torch.float32, pin_memory=True) for _ in range(3)]
-    for h, d in zip(h_new, (qn, kn, vn)):
-        h.copy_(d)
-    h_od = torch.empty((B * N_NEW, E), dtype=torch.float32, pin_memory=True)
+    # every decode step has rows of its own, as a caller's would be: [steps, B * 4, E] in and out
+    step_rows = B * N_NEW
+    h_new = [torch.empty((steps, step_rows, E), dtype=torch.float32, pin_memory=True) for _ in range(3)]
+    gen = torch.Generator(device=dev).manual_seed(77)
+    for h in h_new:
+        for t in range(steps):
+            h[t].copy_(torch.randn((step_rows, E), generator=gen, device=dev))
+    h_od = torch.empty((steps, step_rows, E), dtype=torch.float32, pin_memory=True)
     torch.cuda.synchronize()
     lens0 = np.full(B, BASE_LEN, dtype=np.int32)
     q_h, k_h, v_h = h_qkv[:, 0:E], h_qkv[:, E:2 * E], h_qkv[:, 2 * E:]
@@ -864,8 +979,9 @@ def run_e2e(args, torch, ops, dev, qkv, cu, rows, B, cache_rows, kc, vc, qn, kn,
         sess.forward(q_h, k_h, v_h, h_out, cu, cu, SCALE, ops.MaskConfig(is_causal=True), q_stride=3 * E,
                      k_stride=3 * E, v_stride=3 * E, out_stride=E, wait=False)
         sess.cache_load(lens0, h_kc, h_vc, BASE_LEN)
-        # the 64 steps' rows are known up front here, so copies and kernels may overlap
-        sess.decode_steps(B, N_NEW, args.decode_steps, h_new[0], h_new[1], h_new[2], h_od, SCALE, block_mode=True)
+        # the steps' rows are known up front here, so copies and kernels may overlap
+        sess.decode_steps(B, N_NEW, steps, h_new[0], h_new[1], h_new[2], h_od, SCALE, block_mode=True,
+                          in_step_stride=step_rows * E, out_step_stride=step_rows * E)
         sess.wait()
 
     step()  # warm-up
@@ -880,10 +996,17 @@ def run_e2e(args, torch, ops, dev, qkv, cu, rows, B, cache_rows, kc, vc, qn, kn,
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         sec = float(tt[0])
     sess.close()
-    h2d = 4 * E * (3 * rows + 2 * B * BASE_LEN + 3 * B * N_NEW * args.decode_steps)
-    d2h = 4 * E * (rows + B * N_NEW * args.decode_steps)
-    return {"value": total_bytes / sec / 1e9, "unit": UNIT, "ms_per_step": sec * 1e3, "h2d_bytes_per_step": h2d * world,
-            "d2h_bytes_per_step": d2h * world,
+    del h_new, h_od, h_qkv, h_out, h_kc, h_vc
+    h2d = 4 * E * (3 * rows + 2 * B * BASE_LEN + 3 * step_rows * steps)
+    d2h = 4 * E * (rows + step_rows * steps)
+    link = measure_host_link(torch, dev, barrier, world)
+    # the copies of a step cannot take less than this on the link as measured (each direction at
+    # its own one-way rate, the two fully overlapped: the kindest floor, so the fraction is a lower bound)
+    floor_s = max(h2d / (link["h2d_GBps_per_gpu"] * 1e9), d2h / (link["d2h_GBps_per_gpu"] * 1e9))
+    return {"value": total_bytes / sec / 1e9, "unit": UNIT, "ms_per_step": sec * 1e3, "timed_steps": args.e2e_steps,
+            "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world,
+            "link": link, "link_floor_ms": floor_s * 1e3, "frac_of_link": floor_s / sec,
+            "rows": "every decode step uploads and downloads rows of its own (distinct pinned memory per step)",
             "path": "fblt_session_forward_async + fblt_session_cache_load + fblt_session_decode_steps + fblt_session_wait on pinned host buffers"}
 
 

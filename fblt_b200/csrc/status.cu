@@ -52,6 +52,8 @@ extern "C" const char *fblt_status_string(int status) {
     case FBLT_ERR_CUDA: return "CUDA runtime error";
     case FBLT_ERR_CAPACITY: return "capacity exceeded";
     case FBLT_ERR_LIMIT: return "size beyond a fixed maximum";
+    case FBLT_ERR_PEER: return "another rank announced a failure";
+    case FBLT_ERR_TIMEOUT: return "a host-side deadline passed";
     default: return "unknown status";
     }
 }

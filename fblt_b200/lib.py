@@ -15,7 +15,7 @@ c_float_p = C.POINTER(C.c_float)
 c_i32_p = C.POINTER(C.c_int32)
 c_u8_p = C.POINTER(C.c_uint8)
 
-OK, ERR_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_CAPACITY, ERR_LIMIT = range(7)
+OK, ERR_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_CAPACITY, ERR_LIMIT, ERR_PEER, ERR_TIMEOUT = range(9)
 BACKEND_CPU, BACKEND_CUDA = 0, 1
 GROUP_NONE, GROUP_PATCH_ENC, GROUP_PATCH_DEC, GROUP_PATCH_LEQ, GROUP_IDS = range(5)
 IMPL_AUTO, IMPL_ROW, IMPL_TILE, IMPL_TCGEN05, IMPL_ROW_QUAD = range(5)
@@ -158,6 +158,17 @@ SYMBOLS = {
     "fblt_attn_forward": (C.c_int, [C.POINTER(AttnDesc), C.c_void_p]),
     "fblt_mask_bitmap": (C.c_int, [C.POINTER(AttnDesc), C.c_void_p, C.c_int, C.c_void_p]),
     "fblt_mask_materialize": (C.c_int, [C.POINTER(AttnDesc), C.c_int32, C.c_void_p, c_i32_p, C.c_void_p]),
+    "fblt_shard_partition": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "fblt_rendezvous_files": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p,
+                                        C.c_int32]),
+    "fblt_rendezvous_report_failure": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int32]),
+    "fblt_gather_handle_bytes": (C.c_size_t, []),
+    "fblt_gather_create": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_size_t, C.c_size_t]),
+    "fblt_gather_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "fblt_gather_connect": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "fblt_gather_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]),
+    "fblt_gather_buffer": (C.c_void_p, [C.c_void_p]),
+    "fblt_gather_destroy": (None, [C.c_void_p]),
     "fblt_mask_dense_scratch_bytes": (C.c_size_t, [C.POINTER(MaskConfig)]),
     "fblt_build_attention_mask_dense": (C.c_int, [C.POINTER(MaskConfig), C.c_void_p, C.c_void_p, C.c_size_t, c_i32_p,
                                                   C.c_void_p]),

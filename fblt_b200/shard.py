@@ -86,6 +86,57 @@ class PeerGather:
             self.peers[r][self.rank, :n].copy_(src, non_blocking=True)
 
 
+class IpcGather:
+    """The library's own gather (fblt_gather_* in include/fblt_attn.h) from Python: the same one-sided
+    copy-engine copies as PeerGather, but set up and enqueued by the C ABI -- receive buffers from
+    cudaMalloc, peers mapped through CUDA IPC handles that the ranks exchange on the host with a
+    deadline (fblt_rendezvous_files over `exchange_dir`, a directory all ranks of the box share).
+    No torch.distributed call is involved in the set-up or in put()."""
+
+    def __init__(self, rows: int, E: int, rank: int, world: int, exchange_dir: str, tag: str, deadline_s: float = 120.0):
+        import ctypes as C
+        from . import lib as L
+        self._lib, self.rank, self.world, self.rows, self.E = L.load(), rank, world, rows, E
+        self._h = C.c_void_p()
+        L.check(self._lib.fblt_gather_create(C.byref(self._h), rank, world, rows, E))
+        nb = self._lib.fblt_gather_handle_bytes()
+        mine = C.create_string_buffer(nb)
+        L.check(self._lib.fblt_gather_export(self._h, mine))
+        everyone = C.create_string_buffer(nb * world)
+        os.makedirs(exchange_dir, exist_ok=True)
+        L.check(self._lib.fblt_rendezvous_files(exchange_dir.encode(), tag.encode(), rank, world, mine, nb, everyone,
+                                                int(deadline_s * 1000)))
+        L.check(self._lib.fblt_gather_connect(self._h, everyone))
+        ptr = self._lib.fblt_gather_buffer(self._h)
+        # a tensor view of this rank's receive buffer (owned by the library)
+        self.buf = _device_view(ptr, (world, rows, E))
+
+    def put(self, local: torch.Tensor, nrows: Optional[int] = None, row_offset: int = 0, stream=None) -> None:
+        from . import lib as L
+        n = local.shape[0] if nrows is None else nrows
+        assert local.is_contiguous() and local.dtype == torch.float32 and local.shape[1] == self.E
+        st = (stream or torch.cuda.current_stream()).cuda_stream
+        L.check(self._lib.fblt_gather_rows(self._h, local.data_ptr(), n, row_offset, st))
+
+    def close(self) -> None:
+        """Only after a barrier of the job: peers write into this rank's buffer until then."""
+        if self._h:
+            self.buf = None
+            self._lib.fblt_gather_destroy(self._h)
+            self._h = None
+
+
+class _CudaArrayView:
+    """Minimal __cuda_array_interface__ holder so that torch can view library-owned device memory."""
+
+    def __init__(self, ptr: int, shape):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f4", "data": (int(ptr), False), "version": 3}
+
+
+def _device_view(ptr: int, shape) -> torch.Tensor:
+    return torch.as_tensor(_CudaArrayView(ptr, shape), device="cuda")
+
+
 def unpad(gathered: torch.Tensor, rows_per_rank: List[int]) -> torch.Tensor:
     """Concatenate the valid rows of a gather_rows() result in rank order."""
     return torch.cat([gathered[r, :n] for r, n in enumerate(rows_per_rank)], dim=0)
@@ -197,21 +248,48 @@ def bind_to_device_numa_node(device_index: int) -> dict:
     Pinned host buffers allocated afterwards are first touched on that node, and the thread that
     issues the copies runs there, so host<->device traffic of a rank does not cross the socket
     interconnect. Every rank of a one-process-per-GPU job calls this before it allocates host
-    memory. Returns what was done; does nothing when the topology is not exposed."""
-    info = {"numa_node": None, "cpus": None}
+    memory. Returns what was done -- and, when nothing could be bound, why (`why_not`): the topology
+    comes from sysfs first and from the driver (NVML's CPU affinity of the device) second."""
+    info = {"numa_node": None, "cpus": None, "source": None, "why_not": None}
+    allowed = os.sched_getaffinity(0)
+    # 1) sysfs: the PCI device's NUMA node and that node's CPU list
     try:
         addr = _pci_address(device_index)
         if not addr:
-            return info
-        node = int(open(f"/sys/bus/pci/devices/{addr}/numa_node").read().strip())
-        if node < 0:
-            return info
-        cpus = parse_cpulist(open(f"/sys/devices/system/node/node{node}/cpulist").read())
-        target = cpus & os.sched_getaffinity(0)
-        if not target:
-            return info
-        os.sched_setaffinity(0, target)
-        info.update(numa_node=node, cpus=len(target))
-    except (OSError, ValueError):
-        pass
+            info["why_not"] = "no PCI address for the device"
+        else:
+            node = int(open(f"/sys/bus/pci/devices/{addr}/numa_node").read().strip())
+            if node < 0:
+                info["why_not"] = f"sysfs reports numa_node {node} for {addr} (no affinity exposed to this container)"
+            else:
+                cpus = parse_cpulist(open(f"/sys/devices/system/node/node{node}/cpulist").read())
+                target = cpus & allowed
+                if target:
+                    os.sched_setaffinity(0, target)
+                    info.update(numa_node=node, cpus=len(target), source="sysfs", why_not=None)
+                    return info
+                info["why_not"] = f"node {node}'s CPUs are outside this process's affinity mask"
+    except (OSError, ValueError) as exc:
+        info["why_not"] = f"sysfs: {type(exc).__name__}: {exc}"
+    # 2) the driver's own answer (NVML: the CPUs closest to the device), read-only
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            props = torch.cuda.get_device_properties(device_index)
+            handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(props.uuid)).encode()) if hasattr(props, "uuid") \
+                else pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            words = (max(allowed | {0}) // 64) + 1
+            mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+            cpus = {w * 64 + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1}
+            target = cpus & allowed
+            if target and target != allowed:
+                os.sched_setaffinity(0, target)
+                info.update(cpus=len(target), source="nvml cpu affinity", why_not=None)
+            elif target == allowed:
+                info["why_not"] = (info["why_not"] or "") + "; nvml: the device's CPU set is the whole affinity mask"
+        finally:
+            pynvml.nvmlShutdown()
+    except Exception as exc:   # noqa: BLE001 - NVML absent or refusing is not an error for the caller
+        info["why_not"] = (info["why_not"] or "") + f"; nvml: {type(exc).__name__}: {exc}"
     return info

@@ -42,7 +42,9 @@ typedef enum {
     FBLT_ERR_WORKSPACE = 3,   /* workspace missing or too small              */
     FBLT_ERR_CUDA = 4,        /* a CUDA runtime call failed                  */
     FBLT_ERR_CAPACITY = 5,    /* KV cache / session capacity exceeded        */
-    FBLT_ERR_LIMIT = 6        /* size beyond a documented fixed maximum      */
+    FBLT_ERR_LIMIT = 6,       /* size beyond a documented fixed maximum      */
+    FBLT_ERR_PEER = 7,        /* another rank announced a failure            */
+    FBLT_ERR_TIMEOUT = 8      /* a host-side deadline passed                 */
 } fblt_status;
 
 /* Text of the last error raised on the calling thread ("" if none). */
@@ -719,6 +721,52 @@ int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch);
  * returns that code (0 = none, -1 = CUDA error) and clears it.
  */
 int fblt_tcgen05_error(void);
+
+/* ------------------------------------------------------------------------ */
+/* One process per GPU: batch sharding and the output gather                 */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * The reference runs one sequence at a time in one process (infer.c); its plan for batches
+ * is a [batch, ...] cache (infer/kv_cache.h:71-75). Independent sequences shard by batch with
+ * no exchange inside attention: rank `rank` of `world` owns units [*begin, *end), contiguous,
+ * the first units % world ranks one unit longer.
+ */
+int fblt_shard_partition(int64_t units, int32_t world, int32_t rank, int64_t *begin, int64_t *end);
+
+/*
+ * Host-side all-gather of one small blob per rank through a directory every rank can reach
+ * (a tmpfs on one box), with a deadline: the check-in that comes before the first device copy
+ * towards a peer. all[r * bytes ..] receives rank r's blob. FBLT_ERR_TIMEOUT names the first
+ * absent rank in fblt_last_error(); a rank that timed out, or that called
+ * fblt_rendezvous_report_failure, makes every later arrival fail with FBLT_ERR_PEER instead of
+ * going on alone. `tag` must be unique per rendezvous within the directory.
+ */
+int fblt_rendezvous_files(const char *dir, const char *tag, int32_t rank, int32_t world, const void *mine,
+                          size_t bytes, void *all, int32_t deadline_ms);
+int fblt_rendezvous_report_failure(const char *dir, const char *tag, int32_t rank);
+
+/*
+ * Gather of output rows onto every GPU of one box. Each rank owns a receive buffer
+ * [world, max_rows, row_elems] (fblt_gather_buffer, device memory of the current device,
+ * allocated by fblt_gather_create); fblt_gather_rows copies `nrows` of this rank's rows
+ * (device) to rows [row_offset, row_offset + nrows) of slot [rank] of EVERY rank's buffer with
+ * asynchronous device-to-device copies on `stream` (copy engines over NVLink; no kernel, no
+ * load from a peer, no waiting on the device). Set-up: every rank creates, exports its
+ * fblt_gather_handle_bytes()-byte handle, the job all-gathers the handles on the host
+ * (fblt_rendezvous_files, or its own store) and every rank connects with the world * bytes
+ * array. A rank's buffer holds everybody's rows once every rank's copies have completed: the
+ * caller orders that (a barrier of the job after synchronising `stream`). Destroy only after
+ * such a barrier: peers write into the buffer until then.
+ */
+typedef struct fblt_gather fblt_gather;
+size_t fblt_gather_handle_bytes(void);
+int fblt_gather_create(fblt_gather **out, int32_t rank, int32_t world, size_t max_rows, size_t row_elems);
+int fblt_gather_export(fblt_gather *g, void *handle_out);
+int fblt_gather_connect(fblt_gather *g, const void *all_handles);
+int fblt_gather_rows(fblt_gather *g, const float *rows, size_t nrows, size_t row_offset, void *stream);
+float *fblt_gather_buffer(fblt_gather *g);
+void fblt_gather_destroy(fblt_gather *g);
 
 /* Number of kernels this library has launched in this process (all threads). With
  * FBLT_REPORT_LAUNCHES=1 in the environment the same count is printed to stderr when the
