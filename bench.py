@@ -906,9 +906,10 @@ def run_blocks(args):
     emit(line)
 
 
-# dram bytes per algorithmic byte of the decode kernel, from the ncu capture summarised in
-# profiles/; traffic of a full launch is scaled from it by the rows processed.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.010  # profiles/decode_attn_kernel_config5.md (256-sequence capture)
+# dram__bytes_read + dram__bytes_write per algorithmic byte of the decode kernel, from an ncu capture
+# of a 256-sequence launch; the traffic of a full launch is scaled from it by the rows processed
+# (traffic grows in proportion: every cache row is read once).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.010
 
 
 def measure_host_link(torch, dev, barrier, world: int):

@@ -2,6 +2,7 @@
 // host-side patch boundary helpers.
 #include "common.cuh"
 
+#include <atomic>
 #include <stdlib.h>
 #include <string.h>
 
@@ -71,9 +72,12 @@ __global__ void mask_bitmap_kernel(fblt_attn_desc d, uint8_t *bitmap, int use_ra
     bitmap[(int64_t)b * cells + cell] = bit;
 }
 
-__device__ int g_empty_rows;
+// Counters for rows without an allowed key: one word per call in flight, handed out round-robin, so
+// that concurrent fblt_mask_materialize calls (other streams, other host threads) do not share one.
+constexpr int kEmptyRowSlots = 64;
+__device__ int g_empty_rows[kEmptyRowSlots];
 
-__global__ void mask_materialize_kernel(fblt_attn_desc d, int b, float *out) {
+__global__ void mask_materialize_kernel(fblt_attn_desc d, int b, float *out, int slot) {
     const int q0 = d.cu_q[b], nq = d.cu_q[b + 1] - q0;
     const int k0 = d.cu_k[b], nk = d.cu_k[b + 1] - k0;
     const int i = blockIdx.x;
@@ -86,7 +90,7 @@ __global__ void mask_materialize_kernel(fblt_attn_desc d, int b, float *out) {
         any |= ok ? 1 : 0;
     }
     any = __syncthreads_or(any);
-    if (threadIdx.x == 0 && !any) atomicAdd(&g_empty_rows, 1);
+    if (threadIdx.x == 0 && !any) atomicAdd(&g_empty_rows[slot], 1);
 }
 
 } // namespace fblt
@@ -176,15 +180,17 @@ extern "C" int fblt_mask_materialize(const fblt_attn_desc *d, int32_t seq, float
     if (!mask_out || seq < 0 || seq >= d->batch) return fail(FBLT_ERR_ARG, "mask_materialize: bad arguments");
     if (d->max_q <= 0) return FBLT_OK;
     cudaStream_t s = (cudaStream_t)stream;
+    static std::atomic<unsigned> next_slot{0};
+    const int slot = (int)(next_slot.fetch_add(1, std::memory_order_relaxed) % kEmptyRowSlots);
     const int zero = 0;
-    FBLT_CUDA_TRY(cudaMemcpyToSymbolAsync(g_empty_rows, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s));
-    mask_materialize_kernel<<<d->max_q, 128, 0, s>>>(*d, seq, mask_out);
+    FBLT_CUDA_TRY(cudaMemcpyToSymbolAsync(g_empty_rows, &zero, sizeof(int), slot * sizeof(int), cudaMemcpyHostToDevice, s));
+    mask_materialize_kernel<<<d->max_q, 128, 0, s>>>(*d, seq, mask_out, slot);
     count_launch();
     st = check_launch("mask_materialize_kernel");
     if (st != FBLT_OK) return st;
     if (empty_rows_out) {
         int v = 0;
-        FBLT_CUDA_TRY(cudaMemcpyFromSymbolAsync(&v, g_empty_rows, sizeof(int), 0, cudaMemcpyDeviceToHost, s));
+        FBLT_CUDA_TRY(cudaMemcpyFromSymbolAsync(&v, g_empty_rows, sizeof(int), slot * sizeof(int), cudaMemcpyDeviceToHost, s));
         FBLT_CUDA_TRY(cudaStreamSynchronize(s));
         *empty_rows_out = v;
     }

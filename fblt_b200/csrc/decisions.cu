@@ -68,6 +68,45 @@ __global__ void verify_accept_kernel(uint8_t *x, int64_t x_stride, const int32_t
     }
 }
 
+// One verify-and-commit round for a batch of sequences that decode over a KV cache: the accept loop
+// above with the predictions indexed from the first row the verifier computed in this round
+// (position row0 = the cache length before the pass), followed by the roll-back of that sequence's
+// cache (blt_kv_cache_truncate, infer/kv_cache.c:94-99) to the rows that were computed from bytes
+// that stayed: committed length before the round + accepted drafts. One thread per sequence.
+__global__ void dv_commit_kernel(uint8_t *x, int64_t x_stride, const int32_t *pred, int width, int32_t *l,
+                                 const int32_t *r, const int32_t *target_len, int32_t *cache_len, int32_t *accepted,
+                                 int batch) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= batch) return;
+    uint8_t *xc = x + (int64_t)c * x_stride;
+    const int32_t *pc = pred + (int64_t)c * width; // pc[i]: argmax of the row at position row0 + i, i.e. byte row0 + i + 1
+    const int lc = l[c], cand = lc + r[c], row0 = cache_len[c];
+    // every byte in [lc, cand] needs the row before it among the computed ones
+    if (lc < 1 || r[c] < 0 || lc - 1 < row0 || cand - 1 - row0 >= width) {
+        if (accepted) accepted[c] = -1; // malformed round: nothing is changed
+        return;
+    }
+    int acc = r[c], nl = cand;
+    bool replaced = false;
+    for (int p = lc; p < cand; ++p) {
+        const uint8_t want = (uint8_t)pc[p - 1 - row0];
+        if (xc[p] != want) {
+            xc[p] = want;
+            nl = p + 1;
+            acc = p - lc;
+            replaced = true;
+            break;
+        }
+    }
+    if (!replaced && cand < target_len[c]) {
+        xc[cand] = (uint8_t)pc[cand - 1 - row0];
+        nl = cand + 1;
+    }
+    l[c] = nl;
+    cache_len[c] = lc + acc;
+    if (accepted) accepted[c] = acc;
+}
+
 // Cell selection of one unmask round (infer/block_generation.c:20-58); the same code runs
 // on the host (the fblt_unmask_select_* entry points) and in unmask_step_kernel.
 __host__ __device__ inline uint32_t select_confidence(const float *scores, const uint8_t *masked, size_t B, float alpha) {
@@ -190,6 +229,28 @@ extern "C" int fblt_verify_accept(uint8_t *x, int64_t x_stride, const int32_t *p
                                                                                target_len, batch, new_len, accepted);
     count_launch();
     return check_launch("verify_accept_kernel");
+}
+
+extern "C" int fblt_dv_commit(const float *logits, int64_t stride, int32_t width, int32_t vocab, int32_t batch, uint8_t *x,
+                              int64_t x_stride, int32_t *l, const int32_t *r, const int32_t *target_len,
+                              int32_t *cache_len, int32_t *accepted, int32_t *pred_scratch, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_dv_commit");
+    using namespace fblt;
+    if (!logits || !x || !l || !r || !target_len || !cache_len || !pred_scratch || batch < 0 || width < 1 || vocab < 1 ||
+        stride < vocab)
+        return fail(FBLT_ERR_ARG, "dv_commit: bad arguments");
+    if (vocab > 256) return fail(FBLT_ERR_LIMIT, "dv_commit: predictions are bytes (vocab %d > 256)", vocab);
+    if (batch == 0) return FBLT_OK;
+    const int64_t rows = (int64_t)batch * width;
+    if (rows > 0x7fffffff) return fail(FBLT_ERR_LIMIT, "dv_commit: batch * width beyond int32");
+    argmax_rows_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, (cudaStream_t)stream>>>(logits, stride, (int)rows, vocab, pred_scratch);
+    count_launch();
+    int st = check_launch("argmax_rows_kernel");
+    if (st != FBLT_OK) return st;
+    dv_commit_kernel<<<(batch + 127) / 128, 128, 0, (cudaStream_t)stream>>>(x, x_stride, pred_scratch, width, l, r, target_len,
+                                                                          cache_len, accepted, batch);
+    count_launch();
+    return check_launch("dv_commit_kernel");
 }
 
 extern "C" int fblt_unmask_step(const float *logits, int64_t stride, int32_t batch, int32_t B, int32_t vocab,

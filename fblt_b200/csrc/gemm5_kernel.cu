@@ -391,6 +391,17 @@ int gemm5_take_error() {
     return (int)v;
 }
 
+int gemm5_take_error_on(cudaStream_t s) { // the same, ordered with one stream only
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbolAsync(&v, g_gemm_error, sizeof(v), 0, cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+    if (v) {
+        cudaMemcpyToSymbolAsync(g_gemm_error, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, s);
+        cudaStreamSynchronize(s);
+    }
+    return (int)v;
+}
+
 static inline int64_t ceil_div(int64_t x, int64_t y) { return (x + y - 1) / y; }
 
 } // namespace fblt

@@ -163,6 +163,7 @@ extern "C" void fblt_session_destroy(fblt_session *s) { fblt::session_free(s); }
 
 namespace fblt {
 static int session_forward_impl(fblt_session *s, const fblt_attn_desc *hd, bool blocking);
+int tcgen05_error_on_stream(cudaStream_t s); // tile5_kernel.cu
 }
 
 extern "C" int fblt_session_forward(fblt_session *s, const fblt_attn_desc *hd) {
@@ -185,7 +186,9 @@ extern "C" int fblt_session_wait(fblt_session *s) {
     const bool had_forward = s->fwd_pending;
     s->fwd_pending = false;
     if (had_forward) {
-        if (const int code = fblt_tcgen05_error())
+        // the session's streams are idle, so its kernels have finished: read the error words on the
+        // session's own stream instead of stalling every other stream of the device
+        if (const int code = tcgen05_error_on_stream(s->stream))
             return fail(FBLT_ERR_CUDA, "session_wait: a tcgen05 CTA gave up on a bounded wait (code 0x%x)", code);
     }
     return FBLT_OK;

@@ -389,6 +389,22 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
 }
 
 int gemm5_take_error(); // gemm5_kernel.cu
+int gemm5_take_error_on(cudaStream_t s);
+
+// The same report for a caller that has just synchronised its own streams: reads (and, when set,
+// clears) the two error words in order with `s` and waits for `s` only -- other streams of the
+// device keep running.
+int tcgen05_error_on_stream(cudaStream_t s) {
+    unsigned int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbolAsync(&v, g_t5_error, sizeof(v), 0, cudaMemcpyDeviceToHost, s) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(s) != cudaSuccess) return -1;
+    if (v) {
+        cudaMemcpyToSymbolAsync(g_t5_error, &zero, sizeof(zero), 0, cudaMemcpyHostToDevice, s);
+        cudaStreamSynchronize(s);
+    }
+    const int g = gemm5_take_error_on(s);
+    return v ? (int)v : g;
+}
 
 bool tile5_kernel_supports(const fblt_attn_desc &d, const char **why) {
     if (d.head_dim != 64) {

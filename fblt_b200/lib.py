@@ -182,6 +182,8 @@ SYMBOLS = {
     "fblt_argmax_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]),
     "fblt_verify_accept": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "fblt_dv_commit": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p,
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "fblt_unmask_select_confidence": (C.c_uint32, [c_float_p, c_u8_p, C.c_size_t, C.c_float]),
     "fblt_unmask_select_eb": (C.c_uint32, [c_float_p, c_u8_p, C.c_size_t, C.c_float]),
     "fblt_aligned_commit_select": (C.c_size_t, [C.POINTER(PatchInfo), C.c_size_t, C.c_size_t, C.c_size_t]),

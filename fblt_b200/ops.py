@@ -518,6 +518,19 @@ def verify_accept(x: torch.Tensor, pred: torch.Tensor, l: torch.Tensor, r: torch
     return new_len, accepted
 
 
+def dv_commit(logits: torch.Tensor, width: int, x: torch.Tensor, l: torch.Tensor, r: torch.Tensor,
+              target_len: torch.Tensor, cache_len: torch.Tensor, stream=None) -> torch.Tensor:
+    """One batched verify-and-commit round on the device (fblt_dv_commit): x, l and cache_len are
+    updated in place; returns the accepted counts. logits: [batch * width, vocab]."""
+    batch = x.shape[0]
+    accepted = torch.empty(batch, dtype=torch.int32, device=x.device)
+    pred = torch.empty(batch * width, dtype=torch.int32, device=x.device)
+    L.check(L.load().fblt_dv_commit(logits.data_ptr(), logits.stride(0), width, logits.shape[1], batch, x.data_ptr(),
+                                    x.stride(0), l.data_ptr(), r.data_ptr(), target_len.data_ptr(), cache_len.data_ptr(),
+                                    accepted.data_ptr(), pred.data_ptr(), _stream_ptr(stream)))
+    return accepted
+
+
 # --------------------------------------------------------------------------- host-buffer sessions
 
 class Session:

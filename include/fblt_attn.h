@@ -478,6 +478,32 @@ int fblt_verify_accept(uint8_t *x, int64_t x_stride, const int32_t *pred, int64_
                        const int32_t *r, const int32_t *target_len, int32_t batch, int32_t *new_len,
                        int32_t *accepted, void *stream);
 
+/*
+ * One verify-and-commit round of block drafting with verification (BLT-DV) for a batch of
+ * independent sequences that decode over a KV cache, entirely on the device: the verifier's
+ * argmax, the accept loop of blt_verify_draft (infer/self_speculation.c:154-182) as the
+ * generation loop calls it (infer/block_generation.c:436-453) and the per-sequence cache
+ * roll-back (blt_kv_cache_truncate, infer/kv_cache.c:94-99) -- no logits, bytes or lengths
+ * travel to the host between the verifier's last layer and the next round's launch.
+ *
+ * Sequence c has committed bytes x[c][0 .. l[c]) followed by r[c] drafted bytes, and its cache
+ * held cache_len[c] valid rows before the verifier ran (cache_len[c] <= l[c] - 1: the rows of
+ * bytes cache_len[c] .. l[c] + r[c] - 1 were computed in this round). logits is
+ * [batch * width, stride]: row c * width + i is the verifier's output at position
+ * cache_len[c] + i, i.e. its prediction for byte cache_len[c] + i + 1; width >= l[c] + r[c] -
+ * cache_len[c] for every c. Effects, per sequence, exactly as the reference's host loop: drafts
+ * are accepted up to the first mismatch, which is replaced by the prediction; on a full match one
+ * free byte is appended unless target_len[c] is reached. l[c] receives the new committed length,
+ * accepted[c] (optional) the number of accepted drafts, and cache_len[c] becomes the old l[c] +
+ * accepted[c]: the rows computed from bytes that stayed (what follows was computed from a
+ * rejected draft and is overwritten by the next round). A sequence whose lengths do not fit the
+ * description is left untouched and reports accepted = -1.
+ * pred_scratch: device [batch * width] int32. All pointers device. Bytes: vocab <= 256.
+ */
+int fblt_dv_commit(const float *logits, int64_t stride, int32_t width, int32_t vocab, int32_t batch, uint8_t *x,
+                   int64_t x_stride, int32_t *l, const int32_t *r, const int32_t *target_len, int32_t *cache_len,
+                   int32_t *accepted, int32_t *pred_scratch, void *stream);
+
 /* Host mirrors of the selection helpers (same names minus the prefix, same
  * results): blt_unmask_select_confidence / _eb (infer/block_generation.c:20-58),
  * blt_aligned_commit_select (infer/self_speculation.c:73-80),

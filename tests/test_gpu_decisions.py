@@ -144,3 +144,126 @@ def test_unmask_step_matches_host_loop(cuda_lib, strategy, thr):
             assert (sel.cpu().numpy() == want_sel).all(), (B, V, rnd)
             assert (m_d.cpu().numpy() == masked).all() and (t_d.cpu().numpy() == tokens).all()
             assert (left.cpu().numpy() == masked.sum(axis=1)).all()
+
+
+def test_dv_commit_matches_host_loop(cuda_lib):
+    """fblt_dv_commit against the reference's host loop run one sequence at a time: the verifier's rows
+    start at each sequence's own cache length, bytes / lengths / accepted counts / cache roll-back
+    must match exactly."""
+    rng = np.random.default_rng(21)
+    batch, V, xw = 257, 256, 64
+    o = ob.oracle()
+    l = rng.integers(1, 24, batch).astype(np.int32)
+    r = rng.integers(0, 9, batch).astype(np.int32)
+    cache = (l - 1 - rng.integers(0, 2, batch)).clip(0).astype(np.int32)   # last byte's row pending, or one more
+    target = (l + r + rng.integers(0, 2, batch)).astype(np.int32)
+    width = int((l + r - cache).max())
+    x = rng.integers(0, 256, (batch, xw), dtype=np.uint8)
+    absolute = rng.standard_normal((batch, xw, V)).astype(np.float32)       # logits by absolute position
+    absolute[::7] = np.round(absolute[::7] * 2) / 2                          # ties: lowest index wins
+    pred = np.stack([oracle_argmax(absolute[c]) for c in range(batch)])
+    for c in range(batch):
+        keep = rng.integers(0, r[c] + 2)
+        for p in range(l[c], min(l[c] + keep, l[c] + r[c])):
+            x[c, p] = pred[c, p - 1]
+    want_x, want_len, want_acc = x.copy(), np.zeros(batch, np.int32), np.zeros(batch, np.int32)
+    for c in range(batch):
+        acc = C.c_size_t(0)
+        row = np.ascontiguousarray(want_x[c])
+        want_len[c] = o.oracle_verify_accept(row.ctypes.data_as(C.POINTER(C.c_uint8)),
+                                             np.ascontiguousarray(absolute[c]).ctypes.data_as(ob.c_f_p), V, int(l[c]),
+                                             int(r[c]), int(target[c]), C.byref(acc))
+        want_x[c], want_acc[c] = row, acc.value
+    # what the verifier hands over: `width` rows per sequence starting at its cache length
+    rel = np.zeros((batch, width, V), np.float32)
+    for c in range(batch):
+        n = min(width, xw - cache[c])
+        rel[c, :n] = absolute[c, cache[c]:cache[c] + n]
+    xd, ld, cd = torch.from_numpy(x.copy()).cuda(), torch.from_numpy(l.copy()).cuda(), torch.from_numpy(cache.copy()).cuda()
+    acc_d = ops.dv_commit(torch.from_numpy(rel).cuda().view(batch * width, V), width, xd, ld, torch.from_numpy(r).cuda(),
+                          torch.from_numpy(target).cuda(), cd)
+    assert (acc_d.cpu().numpy() == want_acc).all()
+    assert (ld.cpu().numpy() == want_len).all()
+    assert (xd.cpu().numpy() == want_x).all()
+    assert (cd.cpu().numpy() == l + want_acc).all()             # roll-back point: rows computed from bytes that stayed
+    # a sequence whose rows do not cover its drafts is left alone and flagged
+    bad_cache = torch.from_numpy((l + 1).astype(np.int32)).cuda()
+    x2, l2 = torch.from_numpy(x.copy()).cuda(), torch.from_numpy(l.copy()).cuda()
+    flagged = ops.dv_commit(torch.from_numpy(rel).cuda().view(batch * width, V), width, x2, l2, torch.from_numpy(r).cuda(),
+                            torch.from_numpy(target).cuda(), bad_cache)
+    assert (flagged.cpu().numpy() == -1).all() and (x2.cpu().numpy() == x).all() and (l2.cpu().numpy() == l).all()
+
+
+def _dv_generate(seqs, prompts, steps, B, tables, cache_rows=160):
+    """A toy generation loop of draft -> verify -> commit rounds for the sequences `seqs` as ONE batch,
+    everything on the device between rounds: K / V / Q rows of a byte are table rows of that byte plus
+    a position term, the verifier is cache attention (causal, fblt_attn_decode with write-through)
+    followed by a projection to 256 logits (fblt_matmul), the commit is fblt_dv_commit, which also rolls
+    the cache lengths back. Drafts are wrong on purpose every few positions, so roll-backs happen."""
+    H, hd, V = 2, 64, 256
+    E = H * hd
+    ek, ev, eq, pos, w_head = tables
+    n = len(seqs)
+    xw = 8 + steps * (B + 1) + B + 8
+    x = torch.zeros((n, xw), dtype=torch.uint8, device="cuda")
+    for i, s in enumerate(seqs):
+        x[i, :len(prompts[s])] = torch.tensor(list(prompts[s]), dtype=torch.uint8)
+    l = torch.tensor([len(prompts[s]) for s in seqs], dtype=torch.int32, device="cuda")
+    cache_len = torch.zeros(n, dtype=torch.int32, device="cuda")
+    target = torch.full((n,), xw - 1, dtype=torch.int32, device="cuda")
+    kc = torch.zeros((n, cache_rows, E), device="cuda")
+    vc = torch.zeros((n, cache_rows, E), device="cuda")
+    head = ops.PackedWeights(w_head)
+    seq_id = torch.tensor(seqs, device="cuda")
+    width = B + 3   # rows per sequence and pass: the pending byte (or the prompt) plus the drafts; the same
+    #                 count in every run, so that a sequence meets the same kernel alone and in a batch
+    ar = torch.arange(n, device="cuda")
+
+    def verifier_rows():
+        """Logits of the rows at positions cache_len .. cache_len + width - 1 of every sequence."""
+        p_rows = cache_len.long()[:, None] + torch.arange(width, device="cuda")[None, :]
+        byte = x.gather(1, p_rows.clamp(max=xw - 1)).long()
+        q = (eq[byte] + pos[p_rows]).view(n * width, E).contiguous()
+        k = (ek[byte] + pos[p_rows]).view(n * width, E).contiguous()
+        v = ev[byte].view(n * width, E).contiguous()
+        out = torch.empty_like(q)
+        d = ops.make_decode(kc, vc, cache_len, q, out, H, hd, width, 0.125, block_mode=False, k_new=k, v_new=v,
+                            max_len=cache_rows, splits=1)
+        ops.attn_decode(d, None)
+        return ops.matmul(out, head)
+
+    for step in range(steps):
+        r = torch.full((n,), B, dtype=torch.int32, device="cuda")
+        # drafter: greedy bytes from the same model, one at a time (the cache lengths do not move, so the
+        # rows these passes write are overwritten later), then spoiled at a position that depends on
+        # the sequence and the round -- some rounds keep every draft, most are cut short
+        for i in range(B):
+            pred = ops.argmax_rows(verifier_rows()).view(n, width)
+            at = (l + i - 1 - cache_len).long()
+            x[ar, (l + i).long()] = pred[ar, at].to(torch.uint8)
+        spoil = (seq_id * 3 + step) % (B + 2)
+        hit = spoil < B
+        x[ar[hit], (l.long() + spoil)[hit]] ^= 0x55
+        ops.dv_commit(verifier_rows(), width, x, l, r, target, cache_len)
+    torch.cuda.synchronize()
+    return x.cpu().numpy(), l.cpu().numpy(), cache_len.cpu().numpy()
+
+
+def test_dv_rounds_batched_equal_one_at_a_time(cuda_lib):
+    """Draft -> verify -> accept -> roll back per row (infer/block_generation.c:405-453) for a batch of
+    independent sequences gives byte-identical output to running each sequence alone."""
+    g = torch.Generator(device="cuda").manual_seed(9)
+    E, V = 128, 256
+    tables = (torch.randn((256, E), device="cuda", generator=g), torch.randn((256, E), device="cuda", generator=g),
+              torch.randn((256, E), device="cuda", generator=g), 0.3 * torch.randn((512, E), device="cuda", generator=g),
+              torch.randn((E, V), device="cuda", generator=g))
+    prompts = [bytes([65 + s, 66, 67 + 2 * s][: 1 + s % 3]) for s in range(9)]
+    seqs = list(range(9))
+    xb, lb, cb = _dv_generate(seqs, prompts, steps=7, B=4, tables=tables)
+    gained = lb - np.array([len(p) for p in prompts])
+    assert (gained >= 7).all() and gained.max() >= 7 * 2                  # every round commits; some keep several drafts
+    assert len(set(gained.tolist())) > 1                                  # and the rows advance by different amounts
+    for s in seqs:
+        x1, l1, c1 = _dv_generate([s], prompts, steps=7, B=4, tables=tables)
+        assert l1[0] == lb[s] and c1[0] == cb[s]
+        assert x1[0, :l1[0]].tobytes() == xb[s, :lb[s]].tobytes(), f"sequence {s}"
