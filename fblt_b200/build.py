@@ -13,7 +13,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libfblt_attn.so"
-SOURCES = ["status.cu", "head_l0.cu", "row_kernel.cu", "tile_kernel.cu", "tile5_kernel.cu", "gemm5_kernel.cu", "mha.cu", "decode_kernel.cu", "decisions.cu", "mask_dense.cu", "gather.cu",
+SOURCES = ["status.cu", "head_l0.cu", "row_kernel.cu", "tile_kernel.cu", "tile5_kernel.cu", "unit5_kernel.cu", "gemm5_kernel.cu", "mha.cu", "decode_kernel.cu", "decisions.cu", "mask_dense.cu", "gather.cu",
            "api.cu", "session.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -15,6 +15,8 @@ int launch_tile_kernel(const fblt_attn_desc &d, cudaStream_t stream);
 bool tile_kernel_supports(const fblt_attn_desc &d, const char **why);
 int launch_tile5_kernel(const fblt_attn_desc &d, cudaStream_t stream);
 bool tile5_kernel_supports(const fblt_attn_desc &d, const char **why);
+int launch_unit5_kernel(const fblt_attn_desc &d, cudaStream_t stream);
+bool unit5_kernel_supports(const fblt_attn_desc &d, const char **why);
 
 static int validate_desc(const fblt_attn_desc *d) {
     if (!d) return fail(FBLT_ERR_ARG, "attn: NULL descriptor");
@@ -107,7 +109,8 @@ static int env_overrides(fblt_attn_desc &d) {
             else if (!strcmp(e, "quad")) d.impl = FBLT_IMPL_ROW_QUAD;
             else if (!strcmp(e, "tile")) d.impl = FBLT_IMPL_TILE;
             else if (!strcmp(e, "tcgen05")) d.impl = FBLT_IMPL_TCGEN05;
-            else if (strcmp(e, "auto") && *e) return fblt::fail(FBLT_ERR_ARG, "FBLT_ATTN_IMPL=%s (auto, row, quad, tile, tcgen05)", e);
+            else if (!strcmp(e, "unit")) d.impl = FBLT_IMPL_UNIT;
+            else if (strcmp(e, "auto") && *e) return fblt::fail(FBLT_ERR_ARG, "FBLT_ATTN_IMPL=%s (auto, row, quad, tile, tcgen05, unit)", e);
         }
     }
     if (d.precision == FBLT_PREC_FP32) {
@@ -142,9 +145,14 @@ extern "C" int fblt_attn_forward(const fblt_attn_desc *desc, void *stream) {
     case FBLT_IMPL_ROW_QUAD:
         if (!rowq_kernel_supports(*d, &why)) return fail(FBLT_ERR_UNSUPPORTED, "%s", why);
         return launch_rowq_kernel(*d, s);
+    case FBLT_IMPL_UNIT:
+        if (!unit5_kernel_supports(*d, &why)) return fail(FBLT_ERR_UNSUPPORTED, "%s", why);
+        return launch_unit5_kernel(*d, s);
     case FBLT_IMPL_AUTO:
         // short per-row key ranges (a patch's own bytes, one latent) stay on the row kernel
         if ((d->mask.group_rule == FBLT_GROUP_NONE || d->mask.group_rule == FBLT_GROUP_PATCH_LEQ) && d->max_k >= 32) {
+            // whole sequences of up to 128 rows and keys: one tcgen05 tile per (sequence, head), persistent
+            if (d->max_q >= 32 && unit5_kernel_supports(*d, &why)) return launch_unit5_kernel(*d, s);
             // 128-row tcgen05 tiles once sequences fill most of a tile; 64-row mma.sync tiles otherwise
             if (d->max_q >= 96 && tile5_kernel_supports(*d, &why)) return launch_tile5_kernel(*d, s);
             if (tile_kernel_supports(*d, &why)) return launch_tile_kernel(*d, s);

@@ -30,6 +30,7 @@ extern "C" int fblt_mha_forward(const fblt_mha_desc *d, void *stream) {
     a.num_heads = d->num_heads;
     a.head_dim = d->head_dim;
     a.max_q = a.max_k = d->max_len;
+    if (d->total_rows <= 0x7fffffff) a.total_q_rows = a.total_k_rows = (int32_t)d->total_rows;
     a.impl = FBLT_IMPL_AUTO;
     a.precision = d->precision;
     a.cu_q = a.cu_k = d->cu_rows;
@@ -81,6 +82,10 @@ extern "C" int fblt_cross_attention_forward(const fblt_cross_desc *d, void *stre
     a.head_dim = d->head_dim;
     a.max_q = d->max_q;
     a.max_k = d->max_k;
+    if (d->total_q_rows <= 0x7fffffff && d->total_k_rows <= 0x7fffffff) {
+        a.total_q_rows = (int32_t)d->total_q_rows;
+        a.total_k_rows = (int32_t)d->total_k_rows;
+    }
     a.impl = FBLT_IMPL_AUTO;
     a.precision = d->precision;
     a.cu_q = d->cu_q;

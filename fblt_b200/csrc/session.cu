@@ -254,6 +254,8 @@ static int fblt::session_forward_impl(fblt_session *s, const fblt_attn_desc *hd,
     d.out = s->d_out;
     d.q_stride = d.k_stride = d.v_stride = dstride;
     d.out_stride = E;
+    d.total_q_rows = tq <= 0x7fffffff ? (int32_t)tq : 0; // the staged tensors end here
+    d.total_k_rows = tk <= 0x7fffffff ? (int32_t)tk : 0;
     // the previous non-blocking call's rows must have left d_out before this kernel overwrites them
     if (s->fwd_pending) FBLT_CUDA_TRY(cudaStreamWaitEvent(s->stream, s->ev_fwd_out, 0));
     int st = fblt_attn_forward(&d, s->stream);

@@ -390,6 +390,8 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
 
 int gemm5_take_error(); // gemm5_kernel.cu
 int gemm5_take_error_on(cudaStream_t s);
+int unit5_take_error(); // unit5_kernel.cu
+int unit5_take_error_on(cudaStream_t s);
 
 // The same report for a caller that has just synchronised its own streams: reads (and, when set,
 // clears) the two error words in order with `s` and waits for `s` only -- other streams of the
@@ -403,7 +405,8 @@ int tcgen05_error_on_stream(cudaStream_t s) {
         cudaStreamSynchronize(s);
     }
     const int g = gemm5_take_error_on(s);
-    return v ? (int)v : g;
+    const int u5 = unit5_take_error_on(s);
+    return v ? (int)v : (u5 ? u5 : g);
 }
 
 bool tile5_kernel_supports(const fblt_attn_desc &d, const char **why) {
@@ -460,5 +463,6 @@ extern "C" int fblt_tcgen05_error(void) {
     if (cudaMemcpyFromSymbol(&v, fblt::g_t5_error, sizeof(v)) != cudaSuccess) return -1;
     if (v) cudaMemcpyToSymbol(fblt::g_t5_error, &zero, sizeof(zero));
     const int g = fblt::gemm5_take_error();
-    return v ? (int)v : g;
+    const int u5 = fblt::unit5_take_error();
+    return v ? (int)v : (u5 ? u5 : g);
 }

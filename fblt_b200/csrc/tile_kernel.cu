@@ -377,10 +377,7 @@ static int launch_tile_s(const fblt_attn_desc &d, cudaStream_t stream) {
 template <int HD, bool X3>
 static int launch_tile_t(const fblt_attn_desc &d, cudaStream_t stream) {
     // at most two key tiles per sequence: occupancy beats intra-CTA prefetch.
-    // d.reserved = 1 / 2 forces the stage count (tuning knob, 0 = choose).
-    bool single = d.max_k <= 2 * kBN;
-    if (d.reserved == 1) single = true;
-    if (d.reserved == 2) single = false;
+    const bool single = d.max_k <= 2 * kBN;
     if (single && HD <= 64) return launch_tile_s<HD, X3, 1>(d, stream);
     return launch_tile_s<HD, X3, 2>(d, stream);
 }

@@ -18,7 +18,7 @@ c_u8_p = C.POINTER(C.c_uint8)
 OK, ERR_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_CAPACITY, ERR_LIMIT, ERR_PEER, ERR_TIMEOUT = range(9)
 BACKEND_CPU, BACKEND_CUDA = 0, 1
 GROUP_NONE, GROUP_PATCH_ENC, GROUP_PATCH_DEC, GROUP_PATCH_LEQ, GROUP_IDS = range(5)
-IMPL_AUTO, IMPL_ROW, IMPL_TILE, IMPL_TCGEN05, IMPL_ROW_QUAD = range(5)
+IMPL_AUTO, IMPL_ROW, IMPL_TILE, IMPL_TCGEN05, IMPL_ROW_QUAD, IMPL_UNIT = range(6)
 PREC_FP32, PREC_TF32 = 0, 1
 
 
@@ -118,13 +118,13 @@ class AttnDesc(C.Structure):
     _fields_ = [
         ("batch", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32),
         ("max_q", C.c_int32), ("max_k", C.c_int32), ("impl", C.c_int32), ("precision", C.c_int32),
-        ("reserved", C.c_int32),
+        ("total_q_rows", C.c_int32),
         ("cu_q", C.c_void_p), ("cu_k", C.c_void_p),
         ("q", C.c_void_p), ("q_stride", C.c_int64),
         ("k", C.c_void_p), ("k_stride", C.c_int64),
         ("v", C.c_void_p), ("v_stride", C.c_int64),
         ("out", C.c_void_p), ("out_stride", C.c_int64),
-        ("scale", C.c_float), ("reserved2", C.c_int32),
+        ("scale", C.c_float), ("total_k_rows", C.c_int32),
         ("mask", MaskDesc),
         ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p), ("rope_q_pos", C.c_void_p), ("rope_k_pos", C.c_void_p),
     ]

@@ -175,6 +175,8 @@ def make_batch(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Ten
     d.max_q = int(np.max(np.diff(cu_q_h))) if batch else 0
     d.max_k = int(np.max(np.diff(cu_k_h))) if batch else 0
     d.impl, d.precision = impl, precision
+    d.total_q_rows = int(cu_q_h[-1]) if batch else 0       # where the tensors end: the TMA-loading kernel needs it
+    d.total_k_rows = int(cu_k_h[-1]) if batch else 0
     keep = []
 
     def dev_i32(a):

@@ -213,7 +213,9 @@ typedef enum {
     FBLT_IMPL_ROW = 1,    /* one warp per (query row, head), fp32 FMA; any head_dim up to 256, any mask */
     FBLT_IMPL_TILE = 2,   /* tensor-core tiles, mma.sync TF32 (head_dim 32/64/128, range masks) */
     FBLT_IMPL_TCGEN05 = 3, /* tensor-core tiles, tcgen05 + TMEM (head_dim 64, range masks) */
-    FBLT_IMPL_ROW_QUAD = 4 /* four lanes per (query row, head), fp32 FMA; head_dim 32/64, range masks, no rotary tables */
+    FBLT_IMPL_ROW_QUAD = 4, /* four lanes per (query row, head), fp32 FMA; head_dim 32/64, range masks, no rotary tables */
+    FBLT_IMPL_UNIT = 5     /* tcgen05 + TMA, one 128 x 128 tile per (sequence, head): head_dim 64, at most 128 rows and
+                            * 128 keys per sequence, range masks, total_q_rows / total_k_rows given */
 } fblt_impl;
 
 typedef enum {
@@ -242,7 +244,8 @@ typedef struct {
     int32_t max_k;
     int32_t impl;      /* fblt_impl */
     int32_t precision; /* fblt_precision */
-    int32_t reserved;
+    int32_t total_q_rows; /* host-known cu_q[batch] (rows of q / out), 0 = not given: needed by the kernels that
+                           * load tiles by TMA (the unit kernel), which must know where the tensors end */
     const int32_t *cu_q; /* device [batch+1] */
     const int32_t *cu_k; /* device [batch+1] */
     const float *q;      /* device */
@@ -254,7 +257,7 @@ typedef struct {
     float *out;
     int64_t out_stride;
     float scale;
-    int32_t reserved2;
+    int32_t total_k_rows; /* host-known cu_k[batch] (rows of k / v), 0 = not given */
     fblt_mask_desc mask;
     /* Optional fused rotary embedding for self-attention prefill (replaces the 2 x heads
      * blt_rope_apply_packed launches of models/attention.c:73-89): device tables

@@ -30,6 +30,10 @@ def check(case: ForwardCase, kernels=KERNELS):
         kernels = KERNELS + T5_KERNELS          # the tcgen05 kernel takes head_dim 64
     if kernels[0][0] == L.IMPL_ROW and case.head_dim in (32, 64) and case.mask.group_rule != L.GROUP_IDS:
         kernels = kernels + [(L.IMPL_ROW_QUAD, L.PREC_FP32)]   # four lanes per row: same shapes, range rules
+    fits_unit = (case.head_dim == 64 and case.mask.group_rule != L.GROUP_IDS and len(case.cu_q) > 1 and
+                 int(np.diff(case.cu_q).max()) <= 128 and int(np.diff(case.cu_k).max()) <= 128)
+    if fits_unit and (L.IMPL_UNIT, L.PREC_FP32) not in kernels:
+        kernels = list(kernels) + [(L.IMPL_UNIT, L.PREC_FP32)]   # one 128 x 128 tcgen05 tile per (sequence, head)
     for impl, prec in kernels:
         got, _ = forward_gpu(case, impl, prec)
         what = f"{case.name} impl={impl} prec={prec}"
@@ -37,7 +41,7 @@ def check(case: ForwardCase, kernels=KERNELS):
             assert_close(got, want, what, atol=TF32_ATOL, rtol=TF32_RTOL)
         else:
             assert_close(got, want, what)
-        if impl == L.IMPL_TCGEN05:
+        if impl in (L.IMPL_TCGEN05, L.IMPL_UNIT):
             assert L.load().fblt_tcgen05_error() == 0, "a tcgen05 CTA gave up on a bounded wait"
     return want
 
