@@ -513,7 +513,7 @@ def main():
     pre_launch_ms = pre_ms / args.steps
     pre_bytes = prefill_bytes(rows)
     pre_flops = 4.0 * HD * H * float(sum(int(n) * (int(n) + 1) // 2 for n in np.diff(cu)))  # allowed pairs only
-    prefill = {"kernel": "tile5_attn_kernel<fp32x3> (tcgen05)", "launch_ms": pre_launch_ms,
+    prefill = {"kernel": "unit5_attn_kernel (tcgen05 + TMA, fp32 by three TF32 passes)", "launch_ms": pre_launch_ms,
                "algorithmic_bytes_per_launch": pre_bytes, "achieved_GBps": pre_bytes / pre_launch_ms / 1e6,
                "frac_of_hbm_peak": pre_bytes / pre_launch_ms / 1e6 / peak,
                "algorithmic_tflops": pre_flops / pre_launch_ms / 1e9}
