@@ -37,6 +37,7 @@
 #include "tc5.cuh"
 
 #include <atomic>
+#include <string.h>
 #include <cuda.h> // CUtensorMap and its enums only; the encoder is looked up at run time
 
 namespace fblt {
@@ -53,6 +54,21 @@ constexpr int kGRawBytes = kGM * kGK * 4;      // 16 KB: one raw fp32 tile of a 
 constexpr int kGOffRaw = kGStages * kGStageBytes;
 constexpr int kGSmem = kGOffRaw + kGStages * kGRawBytes;
 constexpr uint32_t kGColSmall = 128, kGColA = 256, kGCols = 512;
+
+// Epilogue of the QKV projection of a cache-aware decode step (infer/kv_cache.c:338-366): instead of
+// storing the [rows, 3E] product, column section 0 (Q) is rotated and stored to q_out, sections 1 and 2
+// (K, V) go straight to the cache rows of their positions, K rotated. Row = sequence b * n_new + r,
+// position = base_len[b] + base_add + r. A 32-column chunk never straddles a section or a head
+// (E and head_dim are multiples of 32). enabled == 0: the plain store.
+struct QkvScatter {
+    int enabled, E, HD, n_new, base_add;
+    const int32_t *base_len;
+    float *q_out;
+    int64_t q_stride;
+    float *kc, *vc;
+    int64_t seq_stride, row_stride;
+    const float *rope_cos, *rope_sin; // [positions, HD / 2] or NULL
+};
 
 __device__ unsigned int g_gemm_error; // 0 = ok; otherwise (code << 24) | low bits of blockIdx.x
 
@@ -83,7 +99,8 @@ __global__ void __launch_bounds__(256) gemm5_pack_kernel(const float *b, int64_t
 template <bool X3>
 __global__ void __launch_bounds__(kGThreads, 1)
     gemm5_kernel(const __grid_constant__ CUtensorMap a_map, const uint8_t *__restrict__ packed, const float *bias,
-                 float *__restrict__ out, int64_t ldo, int M, int N, int ksteps, int ntn, int tiles, int vec_out) {
+                 float *__restrict__ out, int64_t ldo, int M, int N, int ksteps, int ntn, int tiles, int vec_out,
+                 const QkvScatter sc) {
     constexpr int S = kGStages;
     extern __shared__ __align__(1024) uint8_t smem[];
     // bar_full: A operand in TMEM (4 warp arrivals) and weight tile landed (1 arrival + bytes);
@@ -208,7 +225,32 @@ __global__ void __launch_bounds__(kGThreads, 1)
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bar_acc_free);
                 }
-                if (row < M) {
+                if (row < M && sc.enabled) {
+                    const int col0 = nt * kGN + q * 32;
+                    if (col0 < N) {
+                        const int section = col0 / sc.E, ce = col0 - section * sc.E, dcol = ce % sc.HD;
+                        const int b = row / sc.n_new, r = row - b * sc.n_new;
+                        const int pos = sc.base_len[b] + sc.base_add + r;
+                        if (section < 2 && sc.rope_cos) { // interleaved pairs, products and sums rounded separately
+                            const int half = sc.HD / 2;
+                            const float *cs = sc.rope_cos + (int64_t)pos * half + dcol / 2;
+                            const float *sn = sc.rope_sin + (int64_t)pos * half + dcol / 2;
+#pragma unroll
+                            for (int pr = 0; pr < 16; pr += 2) {
+                                const float2 c2 = __ldg(reinterpret_cast<const float2 *>(cs + pr));
+                                const float2 s2 = __ldg(reinterpret_cast<const float2 *>(sn + pr));
+                                rope_rotate(v[2 * pr], v[2 * pr + 1], c2.x, s2.x);
+                                rope_rotate(v[2 * pr + 2], v[2 * pr + 3], c2.y, s2.y);
+                            }
+                        }
+                        float *dst = section == 0 ? sc.q_out + (int64_t)row * sc.q_stride + ce
+                                                  : (section == 1 ? sc.kc : sc.vc) + (int64_t)b * sc.seq_stride +
+                                                        (int64_t)pos * sc.row_stride + ce;
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<float4 *>(dst + c * 4) = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+                    }
+                } else if (row < M) {
                     const int col0 = nt * kGN + q * 32;
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
@@ -429,11 +471,10 @@ extern "C" int fblt_matmul_pack_weights(const float *b, int64_t ldb, int64_t K, 
     return check_launch("gemm5_pack_kernel");
 }
 
-extern "C" int fblt_matmul(const float *a, int64_t lda, const void *packed_b, const float *bias, float *out,
-                           int64_t ldo, int64_t M, int64_t K, int64_t N, int32_t precision, void *stream) {
-    fblt::NvtxRange nvtx_range("fblt_matmul");
-    using namespace fblt;
-    if (M < 0 || K <= 0 || N <= 0 || lda < K || ldo < N) return fail(FBLT_ERR_ARG, "matmul: bad shape or stride");
+namespace fblt {
+static int matmul_impl(const float *a, int64_t lda, const void *packed_b, const float *bias, float *out, int64_t ldo,
+                       int64_t M, int64_t K, int64_t N, int32_t precision, void *stream, const QkvScatter &sc) {
+    if (M < 0 || K <= 0 || N <= 0 || lda < K || (!sc.enabled && ldo < N)) return fail(FBLT_ERR_ARG, "matmul: bad shape or stride");
     if (M == 0) return FBLT_OK;
     if (!a || !packed_b || !out) return fail(FBLT_ERR_ARG, "matmul: buffers must not be NULL");
     if ((K & 3) || (lda & 3) || ((uintptr_t)a & 15))
@@ -455,10 +496,48 @@ extern "C" int fblt_matmul(const float *a, int64_t lda, const void *packed_b, co
     const unsigned grid = (unsigned)(tiles < sms ? tiles : sms); // one persistent CTA per SM
     if (precision != FBLT_PREC_TF32)
         gemm5_kernel<true><<<grid, kGThreads, kGSmem, (cudaStream_t)stream>>>(
-            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, (int)tiles, vec_out);
+            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, (int)tiles, vec_out, sc);
     else
         gemm5_kernel<false><<<grid, kGThreads, kGSmem, (cudaStream_t)stream>>>(
-            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, (int)tiles, vec_out);
+            a_map, (const uint8_t *)packed_b, bias, out, ldo, (int)M, (int)N, ksteps, ntn, (int)tiles, vec_out, sc);
     count_launch();
     return check_launch("gemm5_kernel");
+}
+
+// The QKV projection of a decode step with the scatter epilogue: rotated Q rows to q_out, rotated K and
+// V rows straight into the cache (see QkvScatter). E and head_dim must be multiples of 32.
+int matmul_qkv_to_cache(const float *a, int64_t lda, const void *packed_qkv, int64_t rows, int64_t E, int32_t head_dim,
+                        int32_t n_new, const int32_t *base_len, int32_t base_add, float *q_out, int64_t q_stride,
+                        float *kc, float *vc, int64_t seq_stride, int64_t row_stride, const float *rope_cos,
+                        const float *rope_sin, int32_t precision, void *stream) {
+    if ((E & 31) || (head_dim & 31) || head_dim <= 0 || E % head_dim)
+        return fail(FBLT_ERR_UNSUPPORTED, "qkv scatter: embed_dim and head_dim must be multiples of 32");
+    if (((uintptr_t)q_out | (uintptr_t)kc | (uintptr_t)vc) & 15 || ((q_stride | seq_stride | row_stride) & 3))
+        return fail(FBLT_ERR_ARG, "qkv scatter: destinations must be 16-byte aligned with strides in multiples of 4");
+    if (((uintptr_t)rope_cos | (uintptr_t)rope_sin) & 7) return fail(FBLT_ERR_ARG, "qkv scatter: rotary tables must be 8-byte aligned");
+    QkvScatter sc;
+    sc.enabled = 1;
+    sc.E = (int)E;
+    sc.HD = head_dim;
+    sc.n_new = n_new;
+    sc.base_add = base_add;
+    sc.base_len = base_len;
+    sc.q_out = q_out;
+    sc.q_stride = q_stride;
+    sc.kc = kc;
+    sc.vc = vc;
+    sc.seq_stride = seq_stride;
+    sc.row_stride = row_stride;
+    sc.rope_cos = rope_cos;
+    sc.rope_sin = rope_sin;
+    return matmul_impl(a, lda, packed_qkv, nullptr, q_out, q_stride, rows, E, 3 * E, precision, stream, sc);
+}
+} // namespace fblt
+
+extern "C" int fblt_matmul(const float *a, int64_t lda, const void *packed_b, const float *bias, float *out,
+                           int64_t ldo, int64_t M, int64_t K, int64_t N, int32_t precision, void *stream) {
+    fblt::NvtxRange nvtx_range("fblt_matmul");
+    fblt::QkvScatter none;
+    memset(&none, 0, sizeof(none));
+    return fblt::matmul_impl(a, lda, packed_b, bias, out, ldo, M, K, N, precision, stream, none);
 }

@@ -111,7 +111,15 @@ extern "C" int fblt_cross_attention_forward(const fblt_cross_desc *d, void *stre
 // cache at rows base .. base + n; attention of the n new rows over the cache; output projection.
 // The reference does this per layer with 5 strided copies and 2 rotary launches per head and one
 // operator launch per head; here it is the matmul, the decode kernel (rotation and write-through
-// fused) and the matmul again.
+// fused) and the matmul again; with embed_dim and head_dim multiples of 32 the first matmul's epilogue
+// does the rotation and the write-through itself (attention.c:156 + kv_cache.c:347-366 in one launch).
+namespace fblt {
+int matmul_qkv_to_cache(const float *a, int64_t lda, const void *packed_qkv, int64_t rows, int64_t E, int32_t head_dim,
+                        int32_t n_new, const int32_t *base_len, int32_t base_add, float *q_out, int64_t q_stride,
+                        float *kc, float *vc, int64_t seq_stride, int64_t row_stride, const float *rope_cos,
+                        const float *rope_sin, int32_t precision, void *stream); // gemm5_kernel.cu
+}
+
 extern "C" int fblt_kv_self_attention_step(const fblt_kv_step_desc *d, void *stream) {
     fblt::NvtxRange nvtx_range("fblt_kv_self_attention_step");
     using namespace fblt;
@@ -124,7 +132,17 @@ extern "C" int fblt_kv_self_attention_step(const fblt_kv_step_desc *d, void *str
         return fail(FBLT_ERR_ARG, "kv step: buffers must not be NULL");
     if (d->input_stride < E || d->output_stride < E) return fail(FBLT_ERR_ARG, "kv step: row strides below embed_dim");
 
-    int st = fblt_matmul(d->input, d->input_stride, d->packed_qkv, nullptr, d->qkv_work, 3 * E, rows, E, 3 * E, d->precision,
+    // Projection with the scatter epilogue where the shape allows (embed and head_dim multiples of 32):
+    // the rotated K rows and the V rows go straight from the matmul's accumulators into the cache, the
+    // rotated Q rows into the first E columns' worth of qkv_work; [rows, 3E] never exists in memory.
+    const bool scatter = !(E & 31) && !(d->head_dim & 31);
+    int st;
+    if (scatter)
+        st = matmul_qkv_to_cache(d->input, d->input_stride, d->packed_qkv, rows, E, d->head_dim, d->n_new, d->base_len, 0,
+                                 d->qkv_work, E, d->k_cache, d->v_cache, d->cache_seq_stride, d->cache_row_stride,
+                                 d->rope_cos, d->rope_sin, d->precision, stream);
+    else
+        st = fblt_matmul(d->input, d->input_stride, d->packed_qkv, nullptr, d->qkv_work, 3 * E, rows, E, 3 * E, d->precision,
                          stream);
     if (st != FBLT_OK) return st;
 
@@ -143,15 +161,19 @@ extern "C" int fblt_kv_self_attention_step(const fblt_kv_step_desc *d, void *str
     a.cache_seq_stride = d->cache_seq_stride;
     a.cache_row_stride = d->cache_row_stride;
     a.q = d->qkv_work;
-    a.q_stride = 3 * E;
-    a.k_new = d->qkv_work + E;
-    a.v_new = d->qkv_work + 2 * E;
-    a.kv_new_stride = 3 * E;
     a.out = d->combined_work;
     a.out_stride = E;
     a.scale = 1.0f / sqrtf((float)d->head_dim); // infer/kv_cache.c:258
-    a.rope_cos = d->rope_cos;
-    a.rope_sin = d->rope_sin;
+    if (scatter) { // rows already rotated and in place: the kernel reads the appended rows from the cache
+        a.q_stride = E;
+    } else {
+        a.q_stride = 3 * E;
+        a.k_new = d->qkv_work + E;
+        a.v_new = d->qkv_work + 2 * E;
+        a.kv_new_stride = 3 * E;
+        a.rope_cos = d->rope_cos;
+        a.rope_sin = d->rope_sin;
+    }
     const size_t need = fblt_attn_decode_workspace(&a);
     if (need > d->workspace_bytes) a.splits = 1; // no room for split-K partials: one pass per (sequence, head)
     st = fblt_attn_decode(&a, d->workspace, d->workspace_bytes, stream);
