@@ -53,7 +53,7 @@ __device__ __forceinline__ uint32_t t5_round_in(float x) {
 template <bool X3>
 __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_desc d) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    __shared__ __align__(8) uint64_t bar_s, bar_o;
+    __shared__ __align__(8) uint64_t bar_s, bar_o, bar_fin; // bar_fin: used once, on the failure path
     __shared__ uint32_t tmem_slot;
     __shared__ int s_lo[4], s_hi[4]; // per-warp minimum / maximum of the rows' key ranges
 
@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
     if (tid == 0) {
         mbar_init(&bar_s, 1);
         mbar_init(&bar_o, 1);
+        mbar_init(&bar_fin, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -361,7 +362,13 @@ __global__ void __launch_bounds__(kT5Threads, 2) tile5_attn_kernel(fblt_attn_des
         tc_fence_after();
     }
     if (failed) {
-        if (tid == 0) atomicCAS(&g_t5_error, 0u, (1u << 24) | (blockIdx.x & 0xffffffu));
+        if (tid == 0) {
+            atomicCAS(&g_t5_error, 0u, (1u << 24) | (blockIdx.x & 0xffffffu));
+            // MMAs this thread issued may still be running: one more bounded wait for all of them
+            // before the TMEM they write is given back
+            tc_commit(&bar_fin);
+            mbar_wait(&bar_fin, 0);
+        }
     } else {
         float *orow = d.out + (int64_t)(q0 + (i < nq ? i : 0)) * d.out_stride + (int64_t)h * kT5HD;
 #pragma unroll

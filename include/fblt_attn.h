@@ -745,9 +745,13 @@ int fblt_session_cache_reset(fblt_session *s);
 int fblt_session_cache_lens(fblt_session *s, int32_t *lens_out, int32_t batch);
 
 /*
- * The tcgen05 kernels (attention tile, matmul) bound every mbarrier wait; a CTA whose wait runs out records a code,
- * frees its TMEM and returns without writing its rows. This call synchronises the device,
- * returns that code (0 = none, -1 = CUDA error) and clears it.
+ * The tcgen05 kernels (attention tile and unit kernels, matmul) bound every mbarrier wait; a CTA whose wait runs
+ * out records a code, waits (bounded) for what it has in flight, frees its TMEM and returns without writing its
+ * rows -- the launching call has long returned FBLT_OK by then. A caller that launches fblt_attn_forward,
+ * fblt_mha_forward, fblt_cross_attention_forward, fblt_kv_self_attention_step or fblt_matmul on its own stream
+ * therefore polls this word where it synchronises anyway (the session entry points do it in
+ * fblt_session_wait). This call synchronises the device, returns that code (0 = none, -1 = CUDA error) and
+ * clears it.
  */
 int fblt_tcgen05_error(void);
 
