@@ -45,12 +45,12 @@ constexpr int kU5OffQ = 0, kU5OffK = 4 * kU5Atom, kU5OffV = 8 * kU5Atom, kU5OffS
 constexpr int kU5StageWarp = 2048;    // 32 rows x 64 bytes per worker warp
 constexpr int kU5Smem = 14 * kU5Atom; // + < 3 KB of static shared memory: the 227 KB of an SM
 // TMEM columns
-constexpr uint32_t kU5ColS = 0, kU5ColPlo = 128, kU5ColO = 256, kU5Cols = 512;
+constexpr uint32_t kU5ColS = 0, kU5ColPhi = 128, kU5ColPlo = 256, kU5ColO = 384, kU5Cols = 512;
 
 __device__ unsigned int g_u5_error; // 0 = ok; otherwise (code << 24) | blockIdx.x of the first CTA that gave up
 
 struct U5Bars {
-    uint64_t qk_full, v_full, qk_conv, v_conv, s_done, p_ready, o_done, o_free[2], fin;
+    uint64_t qk_full, v_full, qk_conv, v_conv, s_done, p_ready, o_done, fin;
 };
 
 // Shared-memory matrix descriptor for the 128-byte-swizzled layouts a tiled TMA load produces
@@ -118,8 +118,6 @@ __global__ void __launch_bounds__(kU5Threads, 1)
         mbar_init(&bars.s_done, 1);
         mbar_init(&bars.p_ready, kU5Workers);
         mbar_init(&bars.o_done, 1);
-        mbar_init(&bars.o_free[0], kU5Workers);
-        mbar_init(&bars.o_free[1], kU5Workers);
         mbar_init(&bars.fin, 1);
         abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -179,36 +177,27 @@ __global__ void __launch_bounds__(kU5Threads, 1)
         if (lane == 0) {
             constexpr uint32_t kIdS = t5_idesc(kU5Rows, 128, 0);
             constexpr uint32_t kIdO128 = t5_idesc(kU5Rows, 128, 1), kIdO64 = t5_idesc(kU5Rows, 64, 1);
-            int k = 0;
-            for (int u = blockIdx.x; u < units && !*abortp; u += gridDim.x) {
-                const U5Unit t = u5_unit(d, u);
-                if (t.nq <= 0 || t.nk <= 0) continue;
-                U5_T0();
-                // ---- S = Q K^T into columns [0, 128): the two small products first, then the main one ----
-                if (!mbar_wait_abort(&bars.qk_conv, k & 1, abortp)) {
+            // S = Q K^T of unit number kk of this CTA into columns [0, 128): the two small products first,
+            // then the main one. The columns are free: the workers copied the previous scores out before
+            // they signalled p_ready, which the caller has seen.
+            auto issue_scores = [&](int kk) -> bool {
+                if (!mbar_wait_abort(&bars.qk_conv, kk & 1, abortp)) {
                     give_up(0x21);
-                    break;
+                    return false;
                 }
-                U5_ACC(0, 0);
-                // the score columns still hold the previous unit's probabilities until its P V is done
-                if (k > 0 && !mbar_wait_abort(&bars.o_done, (k - 1) & 1, abortp)) {
-                    give_up(0x22);
-                    break;
-                }
-                U5_ACC(0, 1);
                 tc_fence_after();
 #pragma unroll
                 for (int pass = 0; pass < 2; ++pass) {
 #pragma unroll
                     for (int a = 0; a < 2; ++a) {
 #pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const uint32_t qa = sbase + kU5OffQ + a * 2 * kU5Atom + kk * 32;
-                            const uint32_t ka = sbase + kU5OffK + a * 2 * kU5Atom + kk * 32;
+                        for (int kq = 0; kq < 4; ++kq) {
+                            const uint32_t qa = sbase + kU5OffQ + a * 2 * kU5Atom + kq * 32;
+                            const uint32_t ka = sbase + kU5OffK + a * 2 * kU5Atom + kq * 32;
                             const uint64_t q_hi = u5_desc_sw128(qa, 16, 1024), q_lo = u5_desc_sw128(qa + kU5Atom, 16, 1024);
                             const uint64_t k_hi = u5_desc_sw128(ka, 16, 1024), k_lo = u5_desc_sw128(ka + kU5Atom, 16, 1024);
                             if (pass == 0) {
-                                mma_ss(tmem + kU5ColS, q_hi, k_lo, kIdS, (a | kk) ? 1u : 0u);
+                                mma_ss(tmem + kU5ColS, q_hi, k_lo, kIdS, (a | kq) ? 1u : 0u);
                                 mma_ss(tmem + kU5ColS, q_lo, k_hi, kIdS, 1u);
                             } else {
                                 mma_ss(tmem + kU5ColS, q_hi, k_hi, kIdS, 1u);
@@ -217,8 +206,22 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                     }
                 }
                 tc_commit(&bars.s_done);
-                U5_ACC(0, 2);
-                // ---- O = P V: main terms in 64 columns, small terms in the next 64 ----
+                return true;
+            };
+            auto next_unit = [&](int u) {
+                for (; u < units; u += gridDim.x) {
+                    const U5Unit t = u5_unit(d, u);
+                    if (t.nq > 0 && t.nk > 0) break;
+                }
+                return u;
+            };
+            int k = 0;
+            int u = next_unit(blockIdx.x);
+            bool ok = u < units ? issue_scores(0) : true;
+            while (ok && u < units && !*abortp) {
+                U5_T0();
+                // ---- O = P V: main terms in 64 columns, small terms in the next 64. The accumulator is
+                // free: every worker read the previous output before it signalled this unit's p_ready. ----
                 if (!mbar_wait_abort(&bars.v_conv, k & 1, abortp)) {
                     give_up(0x23);
                     break;
@@ -229,28 +232,22 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                     break;
                 }
                 U5_ACC(0, 4);
-                if (k >= 2 && !mbar_wait_abort(&bars.o_free[k & 1], ((k - 2) >> 1) & 1, abortp)) {
-                    give_up(0x25);
-                    break;
-                }
                 tc_fence_after();
-                const uint32_t ocol = tmem + kU5ColO + (uint32_t)(k & 1) * 128;
 #pragma unroll
                 for (int ks = 0; ks < 16; ++ks) {
                     // 8 keys per step = 8 rows of 128 bytes; N runs over the four 32-column blocks
                     // V_hi[0:32] V_hi[32:64] V_lo[0:32] V_lo[32:64], one atom apart
-#ifdef U5_DEBUG
-                    const uint64_t v_wide = u5_desc_mn32(sbase + kU5OffV + ks * 1024, g_u5_knob[0] ? g_u5_knob[0] : kU5Atom,
-                                                         g_u5_knob[1] ? g_u5_knob[1] : 512);
-#else
                     const uint64_t v_wide = u5_desc_mn32(sbase + kU5OffV + ks * 1024, kU5Atom, 512);
-#endif
-                    mma_ts(ocol, tmem + kU5ColS + ks * 8, v_wide, kIdO128, ks ? 1u : 0u);
-                    mma_ts(ocol + 64, tmem + kU5ColPlo + ks * 8, v_wide, kIdO64, 1u);
+                    mma_ts(tmem + kU5ColO, tmem + kU5ColPhi + ks * 8, v_wide, kIdO128, ks ? 1u : 0u);
+                    mma_ts(tmem + kU5ColO + 64, tmem + kU5ColPlo + ks * 8, v_wide, kIdO64, 1u);
                 }
                 tc_commit(&bars.o_done);
                 U5_ACC(0, 5);
+                // ---- the next unit's scores queue up right behind: they run while the workers store this output ----
+                u = next_unit(u + gridDim.x);
                 ++k;
+                if (u < units) ok = issue_scores(k);
+                U5_ACC(0, 2);
             }
             // whatever was issued has completed before the TMEM is given back
             tc_commit(&bars.fin);
@@ -279,21 +276,21 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             }
             return u;
         };
-        // One 16-byte piece: hi = value rounded to TF32 (written back in place), lo = value - hi. Both
+        // One 16-byte piece: the raw fp32 bits stay where they are as the hi operand (a TF32 MMA reads the
+        // upper 19 bits of each word), lo = value - (value with the low 13 mantissa bits cleared). Both
         // swizzles permute pieces inside a 128-byte row only, so an elementwise pass needs no address
         // arithmetic beyond the plane offset.
         auto split_piece = [&](uint8_t *hi_at, uint8_t *lo_at, bool keep) {
             float4 x = *reinterpret_cast<const float4 *>(hi_at);
-            if (!keep) x = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float e[4] = {x.x, x.y, x.z, x.w};
-            uint4 hi4, lo4;
-            uint32_t *hp = &hi4.x, *lp = &lo4.x;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                hp[c] = t5_tf32_finite(e[c]);
-                lp[c] = __float_as_uint(e[c] - __uint_as_float(hp[c]));
+            if (!keep) {
+                x = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(hi_at) = x;
             }
-            *reinterpret_cast<uint4 *>(hi_at) = hi4;
+            const float e[4] = {x.x, x.y, x.z, x.w};
+            uint4 lo4;
+            uint32_t *lp = &lo4.x;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) lp[c] = __float_as_uint(e[c] - __uint_as_float(__float_as_uint(e[c]) & 0xFFFFE000u));
             *reinterpret_cast<uint4 *>(lo_at) = lo4;
         };
         // Q and K of unit number kk of this CTA: four atoms of 1024 pieces
@@ -412,14 +409,14 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                     for (int c = 0; c < 16; ++c) {
                         const float p = t5_ex2(sc[pc * 16 + c] - ref); // masked entries are -inf: 0
                         l += p;
-                        ph[c] = t5_tf32_finite(p);
-                        pl[c] = __float_as_uint(p - __uint_as_float(ph[c]));
+                        ph[c] = __float_as_uint(p);
+                        pl[c] = __float_as_uint(p - __uint_as_float(ph[c] & 0xFFFFE000u));
                     }
                 } else { // columns past the row group's range: the MMA still reads them
 #pragma unroll
                     for (int c = 0; c < 16; ++c) ph[c] = pl[c] = 0u;
                 }
-                tmem_st16(trow + kU5ColS + qt * 32 + pc * 16, ph);
+                tmem_st16(trow + kU5ColPhi + qt * 32 + pc * 16, ph);
                 tmem_st16(trow + kU5ColPlo + qt * 32 + pc * 16, pl);
             }
             xsum[qt][row] = l;
@@ -444,7 +441,7 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             l = (xsum[0][row] + xsum[1][row]) + (xsum[2][row] + xsum[3][row]);
             const float inv = l > 0.0f ? 1.0f / l : 0.0f; // rows without keys give zeros
             {
-                const uint32_t ocol = trow + kU5ColO + (uint32_t)(k & 1) * 128 + qt * 16;
+                const uint32_t ocol = trow + kU5ColO + qt * 16;
                 float a[16], b[16];
                 tmem_ld16(ocol, a);
                 tmem_ld16(ocol + 64, b);
@@ -467,13 +464,13 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                 for (int j = 0; j < 4; ++j) {
                     const int rr = j * 8 + pr; // row inside this warp's 32
                     const float4 v4 = *reinterpret_cast<const float4 *>(stage + rr * 64 + ((pc ^ ((rr >> 1) & 3)) << 4));
+#ifdef U5_DEBUG
+                    if (g_u5_knob[3]) continue;
+#endif
                     if (rg * 32 + rr < t.nq) *reinterpret_cast<float4 *>(obase + (int64_t)(rg * 32 + rr) * d.out_stride) = v4;
                 }
                 __syncwarp(); // the staged rows have been read back before the next unit's are written
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.o_free[k & 1]);
             if (tid == 96) U5_ACC(1, 6);
             u = un;
             ++k;
