@@ -180,6 +180,24 @@ __device__ __forceinline__ void bulk_load(void *smem_dst, const void *gmem_src, 
                  : "memory");
 }
 
+// Tiled 2-D TMA store from this CTA's shared memory, in the issuing thread's bulk group.
+__device__ __forceinline__ void tma_store_2d(const void *tensor_map, int x, int y, const void *smem_src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tensor_map), "r"(x),
+                 "r"(y), "r"(smem_u32(smem_src))
+                 : "memory");
+}
+// Shared memory -> global memory bulk copy (16-byte aligned addresses, size a multiple of 16) in the
+// issuing thread's bulk group; the waits cover that thread's groups only.
+__device__ __forceinline__ void bulk_store(void *gmem_dst, const void *smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// every committed group of this thread has finished READING its shared-memory source
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// every committed group of this thread has completed
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Tiled 2-D TMA load (tensor map in kernel parameter space) into this CTA's shared memory;
 // x is the innermost coordinate (x * element size must be a multiple of 16 bytes). No multicast.
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const void *tensor_map, int x, int y, uint64_t *bar) {

@@ -37,12 +37,11 @@ namespace fblt {
 
 constexpr int kU5Rows = 128, kU5HD = 64;
 constexpr int kU5Workers = 16;                       // worker warps: conversion, softmax, output
-constexpr int kU5Threads = 32 * (kU5Workers + 2);    // + warp 16 issuer, warp 17 loader
+constexpr int kU5Threads = 32 * (kU5Workers + 3);    // + warp 16 issuer, warp 17 loader, warp 18 output storer
 constexpr int kU5Atom = 16384;                       // one 128-row x 32-column fp32 box (rows of 128 bytes)
 // shared memory map (bytes). Q and K: per 32-column atom the raw / hi plane followed by the lo plane.
 // V: both raw / hi atoms, then both lo atoms, so that [V_hi | V_lo] is four 32-column blocks at one stride.
 constexpr int kU5OffQ = 0, kU5OffK = 4 * kU5Atom, kU5OffV = 8 * kU5Atom, kU5OffStage = 12 * kU5Atom;
-constexpr int kU5StageWarp = 2048;    // 32 rows x 64 bytes per worker warp
 constexpr int kU5Smem = 14 * kU5Atom; // + < 3 KB of static shared memory: the 227 KB of an SM
 // TMEM columns
 constexpr uint32_t kU5ColS = 0, kU5ColPhi = 128, kU5ColPlo = 256, kU5ColO = 384, kU5Cols = 512;
@@ -50,7 +49,7 @@ constexpr uint32_t kU5ColS = 0, kU5ColPhi = 128, kU5ColPlo = 256, kU5ColO = 384,
 __device__ unsigned int g_u5_error; // 0 = ok; otherwise (code << 24) | blockIdx.x of the first CTA that gave up
 
 struct U5Bars {
-    uint64_t qk_full, v_full, qk_conv, v_conv, s_done, p_ready, o_done, fin;
+    uint64_t qk_full, v_full, qk_conv, v_conv, s_done, p_ready, o_done, out_full, out_free, fin;
 };
 
 // Shared-memory matrix descriptor for the 128-byte-swizzled layouts a tiled TMA load produces
@@ -86,6 +85,15 @@ __device__ int g_u5_knob[4];
 struct U5Unit {
     int b, h, q0, nq, k0, nk;
 };
+// What the loader publishes for each unit it loads (u < 0: no more units for this CTA).
+struct U5Geo {
+    int u, b, h, q0, nq, k0, nk, pad;
+};
+// Output maps: boxes of 128, 64, ... 1 rows x 32 columns, so that a unit's nq rows go out as one store
+// per set bit of nq and column half, without touching the next sequence's rows.
+struct U5OutMaps {
+    CUtensorMap m[8];
+};
 
 // Unit `u` of the launch, or nq == 0 for units with nothing to do (skipped by every role alike).
 __device__ __forceinline__ U5Unit u5_unit(const fblt_attn_desc &d, int u) {
@@ -101,9 +109,10 @@ __device__ __forceinline__ U5Unit u5_unit(const fblt_attn_desc &d, int u) {
 
 __global__ void __launch_bounds__(kU5Threads, 1)
     unit5_attn_kernel(fblt_attn_desc d, const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                      const __grid_constant__ CUtensorMap v_map, int units) {
+                      const __grid_constant__ CUtensorMap v_map, const __grid_constant__ U5OutMaps out_maps, int units) {
     extern __shared__ __align__(1024) uint8_t smem[]; // swizzle atoms: 1 KB alignment
     __shared__ __align__(8) U5Bars bars;
+    __shared__ __align__(16) U5Geo geo[4];
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_word;
     __shared__ float xsum[4][kU5Rows]; // the four quarters of a row trade their sums here, their maxima through the staging area
@@ -118,6 +127,8 @@ __global__ void __launch_bounds__(kU5Threads, 1)
         mbar_init(&bars.s_done, 1);
         mbar_init(&bars.p_ready, kU5Workers);
         mbar_init(&bars.o_done, 1);
+        mbar_init(&bars.out_full, kU5Workers);
+        mbar_init(&bars.out_free, 1);
         mbar_init(&bars.fin, 1);
         abort_word = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -142,12 +153,21 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             int k = 0; // processed units of this CTA
             for (int u = blockIdx.x; u < units && !*abortp; u += gridDim.x) {
                 const U5Unit t = u5_unit(d, u);
-                if (t.nq <= 0 || t.nk <= 0) continue;
+                if (t.nq <= 0) continue;
+                if (t.nk <= 0) { // a sequence without keys: its rows are zeros, and no other role sees the unit
+                    for (int i = 0; i < t.nq * (kU5HD / 4); ++i)
+                        *reinterpret_cast<float4 *>(d.out + (int64_t)(t.q0 + i / (kU5HD / 4)) * d.out_stride +
+                                                    (int64_t)t.h * kU5HD + (i % (kU5HD / 4)) * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                    continue;
+                }
                 // Q / K of the previous unit have been read once its score MMAs completed
                 if (k > 0 && !mbar_wait_abort(&bars.s_done, (k - 1) & 1, abortp)) {
                     give_up(0x11);
                     break;
                 }
+                // the unit's geometry travels with the barrier: whoever has waited for qk_full may read it.
+                // Slot k & 3 was last read for unit k - 4, two score rounds ago.
+                geo[k & 3] = U5Geo{u, t.b, t.h, t.q0, t.nq, t.k0, t.nk, 0};
                 mbar_expect_tx(&bars.qk_full, 4 * kU5Atom);
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
@@ -166,12 +186,46 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                 ++k;
             }
             // copies still in flight must have landed before the CTA's shared memory is given up
-            // (only an aborted run can get here with any outstanding)
+            // (only an aborted run can get here with any outstanding); then the end marker, as one more
+            // phase of qk_full
+            bool landed = true;
             if (k > 0) {
-                mbar_wait(&bars.qk_full, (k - 1) & 1);
-                if (!*abortp) mbar_wait(&bars.v_full, (k - 1) & 1);
+                landed = mbar_wait(&bars.qk_full, (k - 1) & 1);
+                if (!*abortp) landed = mbar_wait(&bars.v_full, (k - 1) & 1) && landed;
+            }
+            if (landed && !*abortp) {
+                geo[k & 3].u = -1;
+                mbar_arrive(&bars.qk_full);
             }
         }
+    } else if (warp == kU5Workers + 2) {
+        // ================= output storer =================
+        // Lane 2 b + a sends the 2^(7-b) rows that bit (7 - b) of nq stands for (they start at nq with that
+        // bit and the lower ones cleared), column half a: the staged tile leaves as at most 14 tiled TMA stores.
+        // After the last unit the workers arrive once more, with the loader's end marker in the slot. (This
+        // warp runs a unit behind the others, so it must not wait on qk_full itself: that barrier may by
+        // then be two phases on, which a parity wait cannot tell from none.)
+        for (int k = 0; !*abortp; ++k) {
+            if (!mbar_wait_abort(&bars.out_full, k & 1, abortp)) {
+                if (lane == 0) give_up(0x52);
+                break;
+            }
+            const U5Geo g = geo[k & 3];
+            if (g.u < 0) break;
+            if (lane < 16) {
+                const int bit = 7 - (lane >> 1), a = lane & 1, r = 1 << bit;
+                if (g.nq & r) {
+                    const int r0 = g.nq & ~(2 * r - 1);
+                    tma_store_2d(&out_maps.m[lane >> 1], g.h * kU5HD + a * 32, g.q0 + r0,
+                                 smem + kU5OffStage + a * kU5Atom + r0 * 128);
+                }
+                bulk_commit();
+                bulk_wait_read(); // the staging tile may be written again
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.out_free);
+        }
+        bulk_wait_all(); // the stores have completed before the CTA's shared memory goes away
     } else if (warp == kU5Workers) {
         // ================= MMA issuer =================
         if (lane == 0) {
@@ -263,19 +317,6 @@ __global__ void __launch_bounds__(kU5Threads, 1)
         const uint32_t trow = tmem + ((uint32_t)(rg * 32) << 16);
         const float qscale = d.scale * kLog2e;
         auto group_sync = [&]() { asm volatile("bar.sync %0, 128;" ::"r"(1 + rg) : "memory"); };
-        // next unit at or after u that every role processes; rows of sequences without keys get their zeros here
-        auto next_unit = [&](int u) {
-            for (; u < units; u += gridDim.x) {
-                const U5Unit t = u5_unit(d, u);
-                if (t.nq > 0 && t.nk > 0) break;
-                if (t.nq > 0 && row < t.nq) {
-                    float *o = d.out + (int64_t)(t.q0 + row) * d.out_stride + (int64_t)t.h * kU5HD + qt * 16;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) *reinterpret_cast<float4 *>(o + c * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-            }
-            return u;
-        };
         // One 16-byte piece: the raw fp32 bits stay where they are as the hi operand (a TF32 MMA reads the
         // upper 19 bits of each word), lo = value - (value with the low 13 mantissa bits cleared). Both
         // swizzles permute pieces inside a 128-byte row only, so an elementwise pass needs no address
@@ -293,11 +334,26 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             for (int c = 0; c < 4; ++c) lp[c] = __float_as_uint(e[c] - __uint_as_float(__float_as_uint(e[c]) & 0xFFFFE000u));
             *reinterpret_cast<uint4 *>(lo_at) = lo4;
         };
-        // Q and K of unit number kk of this CTA: four atoms of 1024 pieces
-        auto convert_qk = [&](int kk) -> bool {
+        // Geometry of this CTA's unit number kk and this thread's key range in it, then the split of its
+        // Q and K (four atoms of 1024 pieces). g.u < 0: no such unit (or the wait gave up).
+        struct Work {
+            U5Geo g;
+            int lo, hi;
+        };
+        auto fetch_and_convert = [&](int kk) -> Work {
+            Work w;
+            w.lo = w.hi = 0;
             if (!mbar_wait_abort(&bars.qk_full, kk & 1, abortp)) {
                 give_up(0x31);
-                return false;
+                w.g.u = -1;
+                return w;
+            }
+            w.g = geo[kk & 3];
+            if (w.g.u < 0) return w;
+            if (row < w.g.nq) {
+                const SeqMask sm = resolve_mask(d.mask, w.g.b, w.g.q0, w.g.k0, w.g.nq, w.g.nk);
+                row_range(sm, row, w.lo, w.hi);
+                if (w.hi <= w.lo) w.lo = w.hi = 0;
             }
 #pragma unroll
             for (int op = 0; op < 2; ++op) {
@@ -314,15 +370,19 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             fence_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.qk_conv);
-            return true;
+            return w;
         };
+        // This thread's 16 output columns in the staging tile: two 128-row x 128-byte atoms with the
+        // 128-byte swizzle of the output maps; the first word of the first piece carries the thread's
+        // maximum during the softmax.
+        uint8_t *const srow = smem + kU5OffStage + row * 128;
+        auto piece_at = [&](int q, int c) { return srow + (q >> 1) * kU5Atom + ((((q & 1) * 4 + c) ^ (row & 7)) << 4); };
 
         int k = 0;
-        int u = next_unit(blockIdx.x);
-        bool ok = true;
-        if (u < units) ok = convert_qk(0);
-        while (ok && u < units && !*abortp) {
-            const U5Unit t = u5_unit(d, u);
+        Work w = fetch_and_convert(0);
+        while (w.g.u >= 0 && !*abortp) {
+            const U5Geo t = w.g;
+            const int lo = w.lo, hi = w.hi;
             U5_T0();
             // ---- (1) V of this unit, in place. Rows at and past the sequence's last key belong to the
             // next sequence (or are the load's zero fill) and are cleared: their probabilities are
@@ -346,12 +406,6 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             if (lane == 0) mbar_arrive(&bars.v_conv);
             if (tid == 96) U5_ACC(1, 1);
             // ---- (2) scores -> probabilities, this thread's key chunk of its row ----
-            int lo = 0, hi = 0;
-            if (row < t.nq) {
-                const SeqMask sm = resolve_mask(d.mask, t.b, t.q0, t.k0, t.nq, t.nk);
-                row_range(sm, row, lo, hi);
-                if (hi <= lo) lo = hi = 0;
-            }
             int whi = hi; // 32-key chunks the row group has to look at: up to the largest key any row may see
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) whi = max(whi, __shfl_xor_sync(0xffffffffu, whi, o));
@@ -387,18 +441,16 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                 }
             }
             if (tid == 96) U5_ACC(1, 9);
-            // The maxima travel through the first 128 bytes of each warp's own staging area: its owner
-            // wrote rows there last (program order), and writes rows there again only after the second
-            // group barrier of this unit, when every partner has read.
-            *reinterpret_cast<float *>(smem + kU5OffStage + warp * kU5StageWarp + lane * 4) = mx;
+            // the staging tile is free again once the previous unit's stores have read it
+            if (k > 0 && !mbar_wait_abort(&bars.out_free, (k - 1) & 1, abortp)) {
+                give_up(0x43);
+                break;
+            }
+            *reinterpret_cast<float *>(piece_at(qt, 0)) = mx;
             group_sync();
             if (tid == 96) U5_ACC(1, 10);
-            {
-                const uint8_t *xm = smem + kU5OffStage + rg * kU5StageWarp + lane * 4;
-                mx = fmaxf(fmaxf(*reinterpret_cast<const float *>(xm), *reinterpret_cast<const float *>(xm + 4 * kU5StageWarp)),
-                           fmaxf(*reinterpret_cast<const float *>(xm + 8 * kU5StageWarp),
-                                 *reinterpret_cast<const float *>(xm + 12 * kU5StageWarp)));
-            }
+            mx = fmaxf(fmaxf(*reinterpret_cast<const float *>(piece_at(0, 0)), *reinterpret_cast<const float *>(piece_at(1, 0))),
+                       fmaxf(*reinterpret_cast<const float *>(piece_at(2, 0)), *reinterpret_cast<const float *>(piece_at(3, 0))));
             const float ref = mx == -INFINITY ? 0.0f : mx;
             float l = 0.0f;
 #pragma unroll
@@ -425,9 +477,8 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.p_ready);
             if (tid == 96) U5_ACC(1, 3);
-            // ---- (3) the next unit's Q / K planes, while this unit's P V runs ----
-            const int un = next_unit(u + gridDim.x);
-            if (un < units && !convert_qk(k + 1)) break;
+            // ---- (3) the next unit's geometry and Q / K planes, while this unit's P V runs ----
+            w = fetch_and_convert(k + 1);
             if (tid == 96) U5_ACC(1, 4);
             // ---- (4) output: (main + small) / row sum, this thread's 16 columns ----
             if (!mbar_wait_abort(&bars.o_done, k & 1, abortp)) {
@@ -436,44 +487,34 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             }
             if (tid == 96) U5_ACC(1, 5);
             tc_fence_after();
-            group_sync(); // the partners' sums are there; and their reads of this round's maxima are over
-            if (tid == 96) U5_ACC(1, 7);
-            l = (xsum[0][row] + xsum[1][row]) + (xsum[2][row] + xsum[3][row]);
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f; // rows without keys give zeros
             {
-                const uint32_t ocol = trow + kU5ColO + qt * 16;
                 float a[16], b[16];
-                tmem_ld16(ocol, a);
-                tmem_ld16(ocol + 64, b);
+                tmem_ld16(trow + kU5ColO + qt * 16, a);
+                tmem_ld16(trow + kU5ColO + 64 + qt * 16, b);
+                group_sync(); // the partners' sums are there; and their reads of this round's maxima are over
+                if (tid == 96) U5_ACC(1, 7);
+                l = (xsum[0][row] + xsum[1][row]) + (xsum[2][row] + xsum[3][row]);
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f; // rows without keys give zeros
                 tc_wait_ld();
                 if (tid == 96) U5_ACC(1, 8);
-                // A thread holds 64 contiguous bytes of one row; stored as they are, a warp's store would
-                // touch 32 rows with 16 bytes each. The warp trades them through its own 2 KB of shared
-                // memory (pieces XOR-swizzled by row pair so that both passes are conflict-free) and then
-                // writes eight whole 64-byte row pieces per instruction.
-                uint8_t *stage = smem + kU5OffStage + warp * kU5StageWarp;
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
-                    *reinterpret_cast<float4 *>(stage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) =
+                    *reinterpret_cast<float4 *>(piece_at(qt, c)) =
                         make_float4((a[c * 4] + b[c * 4]) * inv, (a[c * 4 + 1] + b[c * 4 + 1]) * inv,
                                     (a[c * 4 + 2] + b[c * 4 + 2]) * inv, (a[c * 4 + 3] + b[c * 4 + 3]) * inv);
-                __syncwarp();
-                const int pr = lane >> 2, pc = lane & 3;
-                float *obase = d.out + (int64_t)t.q0 * d.out_stride + (int64_t)t.h * kU5HD + qt * 16 + pc * 4;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int rr = j * 8 + pr; // row inside this warp's 32
-                    const float4 v4 = *reinterpret_cast<const float4 *>(stage + rr * 64 + ((pc ^ ((rr >> 1) & 3)) << 4));
-#ifdef U5_DEBUG
-                    if (g_u5_knob[3]) continue;
-#endif
-                    if (rg * 32 + rr < t.nq) *reinterpret_cast<float4 *>(obase + (int64_t)(rg * 32 + rr) * d.out_stride) = v4;
-                }
-                __syncwarp(); // the staged rows have been read back before the next unit's are written
             }
+            // the storer warp sends the tile out by TMA: the stores leave the workers' instruction streams
+            fence_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.out_full);
             if (tid == 96) U5_ACC(1, 6);
-            u = un;
             ++k;
+        }
+        // end of this CTA's units: wake the storer with the end marker in its slot
+        if (w.g.u < 0 && !*abortp) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.out_full);
         }
     }
     tc_fence_before();
@@ -559,12 +600,13 @@ static U5EncodeTiledFn u5_encoder() {
 // Map of the head columns of a [rows, row stride] fp32 tensor for 128-row x 32-column boxes with one of
 // the 128-byte swizzles (16-byte chunks for K-major operands, 32-byte chunks for the MN-major one);
 // rows past `rows` read as zeros and are never touched in memory.
-static int u5_make_map(CUtensorMap *map, const float *base, int64_t stride, int64_t rows, int64_t cols, CUtensorMapSwizzle swz) {
+static int u5_make_map(CUtensorMap *map, const float *base, int64_t stride, int64_t rows, int64_t cols, CUtensorMapSwizzle swz,
+                       int box_rows = kU5Rows) {
     U5EncodeTiledFn enc = u5_encoder();
     if (!enc) return fail(FBLT_ERR_CUDA, "attn: cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)stride * sizeof(float)};
-    const cuuint32_t box[2] = {32, (cuuint32_t)kU5Rows};
+    const cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr,
                            CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -587,15 +629,37 @@ int launch_unit5_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
         configured.fetch_or(bit, std::memory_order_release);
     }
     const int64_t cols = (int64_t)d.num_heads * kU5HD;
-    CUtensorMap qm, km, vm;
-    int st = u5_make_map(&qm, d.q, d.q_stride, d.total_q_rows, cols, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (st == FBLT_OK) st = u5_make_map(&km, d.k, d.k_stride, d.total_k_rows, cols, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (st == FBLT_OK) st = u5_make_map(&vm, d.v, d.v_stride, d.total_k_rows, cols, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-    if (st != FBLT_OK) return st;
+    // The eleven tensor maps depend on the tensors only; a host loop that launches over the same buffers
+    // again (a decode loop, a benchmark) reuses the last set of its thread.
+    struct MapSet {
+        const float *q, *k, *v;
+        float *out;
+        int64_t qs, ks, vs, os, cols;
+        int32_t tq, tk;
+        CUtensorMap qm, km, vm;
+        U5OutMaps om;
+        bool valid;
+    };
+    static thread_local MapSet ms = {};
+    if (!(ms.valid && ms.q == d.q && ms.k == d.k && ms.v == d.v && ms.out == d.out && ms.qs == d.q_stride &&
+          ms.ks == d.k_stride && ms.vs == d.v_stride && ms.os == d.out_stride && ms.cols == cols &&
+          ms.tq == d.total_q_rows && ms.tk == d.total_k_rows)) {
+        ms.valid = false;
+        int st = u5_make_map(&ms.qm, d.q, d.q_stride, d.total_q_rows, cols, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st == FBLT_OK) st = u5_make_map(&ms.km, d.k, d.k_stride, d.total_k_rows, cols, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st == FBLT_OK) st = u5_make_map(&ms.vm, d.v, d.v_stride, d.total_k_rows, cols, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+        for (int b = 0; b < 8 && st == FBLT_OK; ++b)
+            st = u5_make_map(&ms.om.m[b], d.out, d.out_stride, d.total_q_rows, cols, CU_TENSOR_MAP_SWIZZLE_128B, kU5Rows >> b);
+        if (st != FBLT_OK) return st;
+        ms.q = d.q, ms.k = d.k, ms.v = d.v, ms.out = d.out;
+        ms.qs = d.q_stride, ms.ks = d.k_stride, ms.vs = d.v_stride, ms.os = d.out_stride, ms.cols = cols;
+        ms.tq = d.total_q_rows, ms.tk = d.total_k_rows;
+        ms.valid = true;
+    }
     const int units = d.batch * d.num_heads;
     const int sms = sm_count[dev & 63].load(std::memory_order_relaxed);
     const int grid = units < sms ? units : sms;
-    unit5_attn_kernel<<<grid, kU5Threads, kU5Smem, stream>>>(d, qm, km, vm, units);
+    unit5_attn_kernel<<<grid, kU5Threads, kU5Smem, stream>>>(d, ms.qm, ms.km, ms.vm, ms.om, units);
     count_launch();
     return check_launch("unit5_attn_kernel");
 }
