@@ -186,14 +186,16 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                 ++k;
             }
             // copies still in flight must have landed before the CTA's shared memory is given up
-            // (only an aborted run can get here with any outstanding); then the end marker, as one more
-            // phase of qk_full
+            // (only an aborted run can get here with any outstanding)
             bool landed = true;
             if (k > 0) {
                 landed = mbar_wait(&bars.qk_full, (k - 1) & 1);
                 if (!*abortp) landed = mbar_wait(&bars.v_full, (k - 1) & 1) && landed;
             }
-            if (landed && !*abortp) {
+            // The end marker is one more phase of qk_full. It must not complete before the workers have
+            // seen the last load's phase (a parity wait cannot tell two phases on from none): the last
+            // unit's score MMAs, issued after the workers split its Q / K, have completed by then.
+            if (landed && !*abortp && (k == 0 || mbar_wait_abort(&bars.s_done, (k - 1) & 1, abortp))) {
                 geo[k & 3].u = -1;
                 mbar_arrive(&bars.qk_full);
             }
@@ -512,7 +514,8 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             ++k;
         }
         // end of this CTA's units: wake the storer with the end marker in its slot
-        if (w.g.u < 0 && !*abortp) {
+        // (once it has taken the last tile: two phases of out_full must not complete unseen)
+        if (w.g.u < 0 && !*abortp && (k == 0 || mbar_wait_abort(&bars.out_free, (k - 1) & 1, abortp))) {
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.out_full);
         }
