@@ -418,29 +418,39 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             }
             if (tid == 96) U5_ACC(1, 2);
             tc_fence_after();
+            // The scores stay unscaled in registers: scale > 0 keeps the order, and the scale folds into the
+            // exponent's multiply-add. Non-finite scores count as masked; whether there is one is found by
+            // one multiply-add per score (x * 0 is NaN for them), the per-score test runs only then.
             float sc[32];
-            float mx = -INFINITY;
+            float mx = -INFINITY, qs = qscale;
             if (live) {
                 tmem_ld32(trow + kU5ColS + qt * 32, sc);
                 tc_wait_ld();
-                // a chunk that every row of the warp sees whole needs no per-key range test
-                const bool whole = __all_sync(0xffffffffu, lo <= qt * 32 && hi >= qt * 32 + 32);
-                if (whole) {
+                float odd = 0.0f;
+#pragma unroll
+                for (int c = 0; c < 32; ++c) odd = fmaf(sc[c], 0.0f, odd);
+                if (odd != odd || !(qscale > 0.0f)) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const float sv = sc[c] * qscale;
                         sc[c] = finite_f(sv) ? sv : -INFINITY;
-                        mx = fmaxf(mx, sc[c]);
                     }
+                    qs = 1.0f;
+                }
+                // a chunk that every row of the warp sees whole needs no per-key range test
+                const bool whole = __all_sync(0xffffffffu, lo <= qt * 32 && hi >= qt * 32 + 32);
+                if (whole) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, sc[c]);
                 } else {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
                         const int j = qt * 32 + c;
-                        const float sv = sc[c] * qscale;
-                        sc[c] = (j >= lo && j < hi && finite_f(sv)) ? sv : -INFINITY;
+                        sc[c] = (j >= lo && j < hi) ? sc[c] : -INFINITY;
                         mx = fmaxf(mx, sc[c]);
                     }
                 }
+                mx *= qs; // the four quarters of a row trade their maxima in the scaled domain
             }
             if (tid == 96) U5_ACC(1, 9);
             // the staging tile is free again once the previous unit's stores have read it
@@ -461,7 +471,7 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                 if (live) {
 #pragma unroll
                     for (int c = 0; c < 16; ++c) {
-                        const float p = t5_ex2(sc[pc * 16 + c] - ref); // masked entries are -inf: 0
+                        const float p = t5_ex2(fmaf(sc[pc * 16 + c], qs, -ref)); // masked entries are -inf: 0
                         l += p;
                         ph[c] = __float_as_uint(p);
                         pl[c] = __float_as_uint(p - __uint_as_float(ph[c] & 0xFFFFE000u));
