@@ -61,8 +61,9 @@ constexpr uint32_t kGColSmall = 128, kGColA = 256, kGCols = 512;
 // position = base_len[b] + base_add + r. A 32-column chunk never straddles a section or a head
 // (E and head_dim are multiples of 32). enabled == 0: the plain store.
 struct QkvScatter {
-    int enabled, E, HD, n_new, base_add;
-    const int32_t *base_len;
+    int enabled; // 0 plain store, 1 decode step (scatter into the cache), 2 prefill (rotate Q / K, store in place)
+    int E, HD, n_new, base_add;
+    const int32_t *base_len; // mode 2: cu_rows [batch + 1] of the packed sequences, batch in n_new
     float *q_out;
     int64_t q_stride;
     float *kc, *vc;
@@ -207,6 +208,7 @@ __global__ void __launch_bounds__(kGThreads, 1)
             tc_fence_after();
             const int row = mt * kGM + quarter * 32 + lane;
             float *orow = out + (int64_t)(row < M ? row : 0) * ldo;
+            int pos_row = -1;
 #pragma unroll
             for (int q = 0; q < kGN / 32; ++q) {
                 float v[32];
@@ -225,7 +227,37 @@ __global__ void __launch_bounds__(kGThreads, 1)
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&bar_acc_free);
                 }
-                if (row < M && sc.enabled) {
+                if (row < M && sc.enabled == 2) {
+                    // prefill: position = row index inside the packed sequence that holds the row
+                    const int col0 = nt * kGN + q * 32;
+                    if (col0 < N) {
+                        const int section = col0 / sc.E, dcol = (col0 - section * sc.E) % sc.HD;
+                        if (section < 2) {
+                            if (q == 0 || pos_row < 0) { // upper bound of row in cu_rows, once per tile
+                                int lo = 0, hi = sc.n_new;
+                                while (hi - lo > 1) {
+                                    const int mid = (lo + hi) >> 1;
+                                    if (__ldg(sc.base_len + mid) <= row) lo = mid;
+                                    else hi = mid;
+                                }
+                                pos_row = row - __ldg(sc.base_len + lo);
+                            }
+                            const int half = sc.HD / 2;
+                            const float *cs = sc.rope_cos + (int64_t)pos_row * half + dcol / 2;
+                            const float *sn = sc.rope_sin + (int64_t)pos_row * half + dcol / 2;
+#pragma unroll
+                            for (int pr = 0; pr < 16; pr += 2) {
+                                const float2 c2 = __ldg(reinterpret_cast<const float2 *>(cs + pr));
+                                const float2 s2 = __ldg(reinterpret_cast<const float2 *>(sn + pr));
+                                rope_rotate(v[2 * pr], v[2 * pr + 1], c2.x, s2.x);
+                                rope_rotate(v[2 * pr + 2], v[2 * pr + 3], c2.y, s2.y);
+                            }
+                        }
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<float4 *>(orow + col0 + c * 4) = make_float4(v[c * 4], v[c * 4 + 1], v[c * 4 + 2], v[c * 4 + 3]);
+                    }
+                } else if (row < M && sc.enabled) {
                     const int col0 = nt * kGN + q * 32;
                     if (col0 < N) {
                         const int section = col0 / sc.E, ce = col0 - section * sc.E, dcol = ce % sc.HD;
@@ -474,7 +506,7 @@ extern "C" int fblt_matmul_pack_weights(const float *b, int64_t ldb, int64_t K, 
 namespace fblt {
 static int matmul_impl(const float *a, int64_t lda, const void *packed_b, const float *bias, float *out, int64_t ldo,
                        int64_t M, int64_t K, int64_t N, int32_t precision, void *stream, const QkvScatter &sc) {
-    if (M < 0 || K <= 0 || N <= 0 || lda < K || (!sc.enabled && ldo < N)) return fail(FBLT_ERR_ARG, "matmul: bad shape or stride");
+    if (M < 0 || K <= 0 || N <= 0 || lda < K || (sc.enabled != 1 && ldo < N)) return fail(FBLT_ERR_ARG, "matmul: bad shape or stride");
     if (M == 0) return FBLT_OK;
     if (!a || !packed_b || !out) return fail(FBLT_ERR_ARG, "matmul: buffers must not be NULL");
     if ((K & 3) || (lda & 3) || ((uintptr_t)a & 15))
@@ -531,6 +563,30 @@ int matmul_qkv_to_cache(const float *a, int64_t lda, const void *packed_qkv, int
     sc.rope_cos = rope_cos;
     sc.rope_sin = rope_sin;
     return matmul_impl(a, lda, packed_qkv, nullptr, q_out, q_stride, rows, E, 3 * E, precision, stream, sc);
+}
+
+// The QKV projection of a self-attention prefill with the rotation in the epilogue: out [rows, 3E] holds
+// Q and K rotated with each row's position inside its packed sequence (cu_rows [batch + 1]) and V as it is
+// (models/attention.c:156-160 in one launch). E and head_dim multiples of 32, out 16-byte aligned, ldo % 4 == 0.
+int matmul_qkv_rotated(const float *a, int64_t lda, const void *packed_qkv, int64_t rows, int64_t E, int32_t head_dim,
+                       const int32_t *cu_rows, int32_t batch, float *out, int64_t ldo, const float *rope_cos,
+                       const float *rope_sin, int32_t precision, void *stream) {
+    if ((E & 31) || (head_dim & 31) || head_dim <= 0 || E % head_dim)
+        return fail(FBLT_ERR_UNSUPPORTED, "qkv rotation: embed_dim and head_dim must be multiples of 32");
+    if (((uintptr_t)out & 15) || (ldo & 3) || ldo < 3 * E)
+        return fail(FBLT_ERR_ARG, "qkv rotation: out must be 16-byte aligned with a row stride >= 3E in multiples of 4");
+    if (!cu_rows || batch < 1 || !rope_cos || !rope_sin) return fail(FBLT_ERR_ARG, "qkv rotation: tables must not be NULL");
+    if (((uintptr_t)rope_cos | (uintptr_t)rope_sin) & 7) return fail(FBLT_ERR_ARG, "qkv rotation: rotary tables must be 8-byte aligned");
+    QkvScatter sc;
+    memset(&sc, 0, sizeof(sc));
+    sc.enabled = 2;
+    sc.E = (int)E;
+    sc.HD = head_dim;
+    sc.n_new = batch;
+    sc.base_len = cu_rows;
+    sc.rope_cos = rope_cos;
+    sc.rope_sin = rope_sin;
+    return matmul_impl(a, lda, packed_qkv, nullptr, out, ldo, rows, E, 3 * E, precision, stream, sc);
 }
 } // namespace fblt
 

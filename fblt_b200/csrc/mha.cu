@@ -1,12 +1,19 @@
 // Multi-head self-attention block over a batch of packed sequences: the work of
 // blt_multihead_attention (models/attention.c:130-207) -- QKV projection, rotary embedding of
 // Q and K, per-head masked attention, output projection -- as three launches: the tcgen05
-// matmul, the batched attention kernel with the rotation fused into its loads and the mask
-// evaluated from the descriptor, and the matmul again. The reference runs, per sequence and
+// matmul with the rotation in its epilogue (or, for odd shapes, fused into the attention
+// kernel's loads), the batched attention kernel with the mask evaluated from the descriptor,
+// and the matmul again. The reference runs, per sequence and
 // layer, two GEMMs, 2 x heads rotary launches, a mask build and one attention launch per head.
 #include "common.cuh"
 
 #include <math.h>
+
+namespace fblt {
+int matmul_qkv_rotated(const float *a, int64_t lda, const void *packed_qkv, int64_t rows, int64_t E, int32_t head_dim,
+                       const int32_t *cu_rows, int32_t batch, float *out, int64_t ldo, const float *rope_cos,
+                       const float *rope_sin, int32_t precision, void *stream); // gemm5_kernel.cu
+}
 
 extern "C" int fblt_mha_forward(const fblt_mha_desc *d, void *stream) {
     fblt::NvtxRange nvtx_range("fblt_mha_forward");
@@ -20,7 +27,17 @@ extern "C" int fblt_mha_forward(const fblt_mha_desc *d, void *stream) {
         return fail(FBLT_ERR_ARG, "mha: buffers must not be NULL");
     if (d->input_stride < E || d->output_stride < E) return fail(FBLT_ERR_ARG, "mha: row strides below embed_dim");
 
-    int st = fblt_matmul(d->input, d->input_stride, d->packed_qkv, nullptr, d->qkv_work, 3 * E, d->total_rows, E, 3 * E,
+    // With embed_dim and head_dim multiples of 32 the projection's epilogue rotates Q and K itself (query and
+    // key positions coincide in a self-attention block unless the mask shifts the queries), and the attention
+    // kernels, the TMA-fed one included, read rotated rows.
+    const bool rotate_in_epilogue = d->rope_cos && d->rope_sin && !(E & 31) && !(d->head_dim & 31) && !d->mask.causal_offset &&
+                                    !(((uintptr_t)d->qkv_work) & 15);
+    int st;
+    if (rotate_in_epilogue)
+        st = matmul_qkv_rotated(d->input, d->input_stride, d->packed_qkv, d->total_rows, E, d->head_dim, d->cu_rows, d->batch,
+                                d->qkv_work, 3 * E, d->rope_cos, d->rope_sin, d->precision, stream);
+    else
+        st = fblt_matmul(d->input, d->input_stride, d->packed_qkv, nullptr, d->qkv_work, 3 * E, d->total_rows, E, 3 * E,
                          d->precision, stream);
     if (st != FBLT_OK) return st;
 
@@ -42,8 +59,10 @@ extern "C" int fblt_mha_forward(const fblt_mha_desc *d, void *stream) {
     a.out_stride = E;
     a.scale = 1.0f / sqrtf((float)d->head_dim); // models/attention.c:137
     a.mask = d->mask;
-    a.rope_cos = d->rope_cos;
-    a.rope_sin = d->rope_sin;
+    if (!rotate_in_epilogue) {
+        a.rope_cos = d->rope_cos;
+        a.rope_sin = d->rope_sin;
+    }
     st = fblt_attn_forward(&a, stream);
     if (st != FBLT_OK) return st;
 

@@ -572,7 +572,11 @@ int fblt_matmul(const float *a, int64_t lda, const void *packed_b, const float *
  * with scale 1/sqrt(head_dim); output = combined * weight_proj. Weights are the
  * fblt_matmul_pack_weights images of weight_qkv [E, 3E] and weight_proj [E, E].
  * qkv_work [total_rows, 3E] and combined_work [total_rows, E] are caller-provided
- * scratch (qkv_work holds the un-rotated projection afterwards). Three launches.
+ * scratch. Three launches: with embed_dim and head_dim multiples of 32 (and no
+ * causal_offset in the mask) the first matmul's epilogue rotates Q and K, so qkv_work
+ * holds the rotated projection afterwards and every attention kernel, the TMA-fed one
+ * for sequences of at most 128 rows included, takes the rows as they are; otherwise
+ * qkv_work holds the un-rotated projection and the attention kernel rotates as it loads.
  * total_rows is the host copy of cu_rows[batch]; max_len bounds the sequence
  * lengths. All pointers device.
  */

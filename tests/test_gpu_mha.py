@@ -49,6 +49,14 @@ def test_mha_block_matches_reference(cuda_lib):
     got, want = run_case(256, 4, [150, 64], 3, use_rope=False,
                          docs=[np.array([40, 90]), np.array([], dtype=np.int64)])
     assert_close(got, want, "mha documents")
+    # patch-transformer shape: sequences of at most 128 rows, head_dim 64 -- the projection's epilogue rotates
+    # Q / K and the TMA-fed unit kernel does the attention
+    got, want = run_case(512, 8, [128, 77, 1, 0, 100, 128], 5, use_rope=True)
+    assert_close(got, want, "mha rope, unit kernel")
+    got, want = run_case(256, 4, [64, 128], 6, use_rope=True, window=32)
+    assert_close(got, want, "mha rope window, unit kernel")
+    got, want = run_case(96, 3, [50, 20], 7, use_rope=True)                   # embed not a multiple of 32: rotation in the loads
+    assert_close(got, want, "mha rope, head_dim 32, odd embed")
 
 
 def test_mha_block_tf32_mode(cuda_lib):
