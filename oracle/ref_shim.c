@@ -54,7 +54,7 @@ static void *ref_worker(void *p) {
         blt_attention_head_args a = c->jobs[idx];
         if (!a.weights_out && !a.scores_scratch) {
             size_t need = a.nq * a.nk;
-            if (need > cap) {
+            if (need > cap || !scratch) { /* a job without keys (need == 0) still wants a non-NULL pointer */
                 free(scratch);
                 scratch = (float *)malloc(need * sizeof(float) + 16);
                 cap = need;

@@ -133,6 +133,34 @@ def test_small_lengths_at_every_edge(cuda_lib, hd):
     check(random_case(302 + hd, cu_q, cu, 3, hd, MaskConfig()), kernels=kernels)
 
 
+def test_unit_kernel_many_units_per_cta(cuda_lib):
+    """The persistent unit kernel with more units than CTAs: 700 sequences x 4 heads on one CTA per SM, lengths
+    0 .. 128 (empty sequences and full tiles included), so every CTA walks a queue of loads, conversions,
+    MMAs and TMA stores of different row counts; then a cross shape with sequences that have queries but
+    no keys (zeros, written by the loader) and keys but no queries. Repeated launches must agree bit
+    for bit (the roles meet on barriers only)."""
+    rng = np.random.default_rng(77)
+    lens = rng.integers(0, 129, 700)
+    lens[::50] = 128
+    lens[7::90] = 0
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    unit = [(L.IMPL_UNIT, L.PREC_FP32)]
+    case = random_case(70, cu, cu, 4, 64, MaskConfig(is_causal=True))
+    check(case, kernels=unit)
+    first, _ = forward_gpu(case, L.IMPL_UNIT)
+    for _ in range(3):
+        again, _ = forward_gpu(case, L.IMPL_UNIT)
+        assert np.array_equal(first, again)
+    check(random_case(71, cu, cu, 4, 64, MaskConfig(is_causal=True, sliding_window=20)), kernels=unit)
+    qlens = rng.integers(0, 129, 300)
+    klens = rng.integers(0, 129, 300)
+    klens[3::17] = 0
+    qlens[5::19] = 0
+    cu_q, cu_k = np.concatenate([[0], np.cumsum(qlens)]), np.concatenate([[0], np.cumsum(klens)])
+    check(random_case(72, cu_q, cu_k, 2, 64, MaskConfig()), kernels=unit)
+    assert L.load().fblt_tcgen05_error() == 0
+
+
 def test_docs_offsets_and_block_infer(cuda_lib):
     cu = np.array([0, 150, 150 + 97])
     docs = [np.array([40, 41, 120]), np.array([64])]
