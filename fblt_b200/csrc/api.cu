@@ -151,7 +151,7 @@ extern "C" int fblt_attn_forward(const fblt_attn_desc *desc, void *stream) {
     case FBLT_IMPL_AUTO:
         // short per-row key ranges (a patch's own bytes, one latent) stay on the row kernel
         if ((d->mask.group_rule == FBLT_GROUP_NONE || d->mask.group_rule == FBLT_GROUP_PATCH_LEQ) && d->max_k >= 32) {
-            // whole sequences of up to 128 rows and keys: one tcgen05 tile per (sequence, head), persistent
+            // sequences of up to 128 keys: one tcgen05 tile per (sequence, head, 128 query rows), persistent
             if (d->max_q >= 32 && unit5_kernel_supports(*d, &why)) return launch_unit5_kernel(*d, s);
             // 128-row tcgen05 tiles once sequences fill most of a tile; 64-row mma.sync tiles otherwise
             if (d->max_q >= 96 && tile5_kernel_supports(*d, &why)) return launch_tile5_kernel(*d, s);

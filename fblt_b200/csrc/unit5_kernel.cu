@@ -1,6 +1,6 @@
-// L1 tcgen05 kernel for short sequences (head_dim 64, at most 128 query rows and 128 keys per
-// sequence: the patch-transformer shapes): one (sequence, head) unit = one 128 x 128 score tile,
-// so the softmax is a single pass with no running maximum and no rescale of the output.
+// L1 tcgen05 kernel for sequences of at most 128 keys (head_dim 64: the patch-transformer shapes, and byte
+// queries over a sequence's patches): one (sequence, head, 128 query rows) unit = one 128 x 128 score
+// tile, so the softmax is a single pass with no running maximum and no rescale of the output.
 //
 // Persistent, one CTA per SM, roles that meet only on mbarriers:
 //   loader (1 thread)   raw fp32 Q, K, V tiles of the NEXT unit by tiled TMA (no multicast, this
@@ -82,12 +82,14 @@ __device__ int g_u5_knob[4];
 #define U5_ACC(role, slot) do { } while (0)
 #endif
 
+// One unit: 128 query rows (tile number qrow0 / 128 of sequence b) of head h over all keys of the sequence.
+// q0 / nq are the tile's first packed row and row count, sq0 / snq the sequence's.
 struct U5Unit {
-    int b, h, q0, nq, k0, nk;
+    int b, h, q0, nq, k0, nk, qrow0, sq0, snq;
 };
 // What the loader publishes for each unit it loads (u < 0: no more units for this CTA).
 struct U5Geo {
-    int u, b, h, q0, nq, k0, nk, pad;
+    int u, b, h, q0, nq, k0, nk, qrow0, sq0, snq, pad0, pad1;
 };
 // Output maps: boxes of 128, 64, ... 1 rows x 32 columns, so that a unit's nq rows go out as one store
 // per set bit of nq and column half, without touching the next sequence's rows.
@@ -95,13 +97,19 @@ struct U5OutMaps {
     CUtensorMap m[8];
 };
 
-// Unit `u` of the launch, or nq == 0 for units with nothing to do (skipped by every role alike).
-__device__ __forceinline__ U5Unit u5_unit(const fblt_attn_desc &d, int u) {
+// Unit `u` of the launch (heads fastest, then query tiles, then sequences), or nq <= 0 for units with
+// nothing to do (skipped by every role alike).
+__device__ __forceinline__ U5Unit u5_unit(const fblt_attn_desc &d, int u, int qtiles) {
     U5Unit t;
-    t.b = u / d.num_heads;
-    t.h = u - t.b * d.num_heads;
-    t.q0 = d.cu_q[t.b];
-    t.nq = d.cu_q[t.b + 1] - t.q0;
+    const int per_seq = d.num_heads * qtiles;
+    t.b = u / per_seq;
+    const int rem = u - t.b * per_seq, qt = rem / d.num_heads;
+    t.h = rem - qt * d.num_heads;
+    t.sq0 = d.cu_q[t.b];
+    t.snq = d.cu_q[t.b + 1] - t.sq0;
+    t.qrow0 = qt * kU5Rows;
+    t.q0 = t.sq0 + t.qrow0;
+    t.nq = min(kU5Rows, t.snq - t.qrow0);
     t.k0 = d.cu_k[t.b];
     t.nk = d.cu_k[t.b + 1] - t.k0;
     return t;
@@ -109,7 +117,7 @@ __device__ __forceinline__ U5Unit u5_unit(const fblt_attn_desc &d, int u) {
 
 __global__ void __launch_bounds__(kU5Threads, 1)
     unit5_attn_kernel(fblt_attn_desc d, const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                      const __grid_constant__ CUtensorMap v_map, const __grid_constant__ U5OutMaps out_maps, int units) {
+                      const __grid_constant__ CUtensorMap v_map, const __grid_constant__ U5OutMaps out_maps, int units, int qtiles) {
     extern __shared__ __align__(1024) uint8_t smem[]; // swizzle atoms: 1 KB alignment
     __shared__ __align__(8) U5Bars bars;
     __shared__ __align__(16) U5Geo geo[4];
@@ -152,7 +160,7 @@ __global__ void __launch_bounds__(kU5Threads, 1)
         if (lane == 0) {
             int k = 0; // processed units of this CTA
             for (int u = blockIdx.x; u < units && !*abortp; u += gridDim.x) {
-                const U5Unit t = u5_unit(d, u);
+                const U5Unit t = u5_unit(d, u, qtiles);
                 if (t.nq <= 0) continue;
                 if (t.nk <= 0) { // a sequence without keys: its rows are zeros, and no other role sees the unit
                     for (int i = 0; i < t.nq * (kU5HD / 4); ++i)
@@ -167,7 +175,7 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                 }
                 // the unit's geometry travels with the barrier: whoever has waited for qk_full may read it.
                 // Slot k & 3 was last read for unit k - 4, two score rounds ago.
-                geo[k & 3] = U5Geo{u, t.b, t.h, t.q0, t.nq, t.k0, t.nk, 0};
+                geo[k & 3] = U5Geo{u, t.b, t.h, t.q0, t.nq, t.k0, t.nk, t.qrow0, t.sq0, t.snq, 0, 0};
                 mbar_expect_tx(&bars.qk_full, 4 * kU5Atom);
 #pragma unroll
                 for (int a = 0; a < 2; ++a) {
@@ -266,7 +274,7 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             };
             auto next_unit = [&](int u) {
                 for (; u < units; u += gridDim.x) {
-                    const U5Unit t = u5_unit(d, u);
+                    const U5Unit t = u5_unit(d, u, qtiles);
                     if (t.nq > 0 && t.nk > 0) break;
                 }
                 return u;
@@ -353,8 +361,8 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             w.g = geo[kk & 3];
             if (w.g.u < 0) return w;
             if (row < w.g.nq) {
-                const SeqMask sm = resolve_mask(d.mask, w.g.b, w.g.q0, w.g.k0, w.g.nq, w.g.nk);
-                row_range(sm, row, w.lo, w.hi);
+                const SeqMask sm = resolve_mask(d.mask, w.g.b, w.g.sq0, w.g.k0, w.g.snq, w.g.nk);
+                row_range(sm, w.g.qrow0 + row, w.lo, w.hi);
                 if (w.hi <= w.lo) w.lo = w.hi = 0;
             }
 #pragma unroll
@@ -560,8 +568,8 @@ bool unit5_kernel_supports(const fblt_attn_desc &d, const char **why) {
         *why = "unit kernel: head_dim must be 64";
         return false;
     }
-    if (d.max_q > kU5Rows || d.max_k > kU5Rows) {
-        *why = "unit kernel: at most 128 query rows and 128 keys per sequence";
+    if (d.max_k > kU5Rows || d.max_q < 1 || d.max_q > 64 * kU5Rows) {
+        *why = "unit kernel: at most 128 keys per sequence (and 8192 query rows)";
         return false;
     }
     if (d.total_q_rows <= 0 || d.total_k_rows <= 0) {
@@ -584,7 +592,7 @@ bool unit5_kernel_supports(const fblt_attn_desc &d, const char **why) {
         *why = "q/k/v/out must be 16-byte aligned";
         return false;
     }
-    if ((int64_t)d.batch * d.num_heads > 0x7fffffff) {
+    if ((int64_t)d.batch * d.num_heads * ((d.max_q + kU5Rows - 1) / kU5Rows) > 0x7fffffff) {
         *why = "batch * heads beyond int32";
         return false;
     }
@@ -669,10 +677,11 @@ int launch_unit5_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
         ms.tq = d.total_q_rows, ms.tk = d.total_k_rows;
         ms.valid = true;
     }
-    const int units = d.batch * d.num_heads;
+    const int qtiles = (d.max_q + kU5Rows - 1) / kU5Rows; // query tiles per sequence; all of them read the sequence's keys
+    const int units = d.batch * d.num_heads * qtiles;
     const int sms = sm_count[dev & 63].load(std::memory_order_relaxed);
     const int grid = units < sms ? units : sms;
-    unit5_attn_kernel<<<grid, kU5Threads, kU5Smem, stream>>>(d, ms.qm, ms.km, ms.vm, ms.om, units);
+    unit5_attn_kernel<<<grid, kU5Threads, kU5Smem, stream>>>(d, ms.qm, ms.km, ms.vm, ms.om, units, qtiles);
     count_launch();
     return check_launch("unit5_attn_kernel");
 }

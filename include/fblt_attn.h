@@ -214,8 +214,8 @@ typedef enum {
     FBLT_IMPL_TILE = 2,   /* tensor-core tiles, mma.sync TF32 (head_dim 32/64/128, range masks) */
     FBLT_IMPL_TCGEN05 = 3, /* tensor-core tiles, tcgen05 + TMEM (head_dim 64, range masks) */
     FBLT_IMPL_ROW_QUAD = 4, /* four lanes per (query row, head), fp32 FMA; head_dim 32/64, range masks, no rotary tables */
-    FBLT_IMPL_UNIT = 5     /* tcgen05 + TMA, one 128 x 128 tile per (sequence, head): head_dim 64, at most 128 rows and
-                            * 128 keys per sequence, range masks, total_q_rows / total_k_rows given */
+    FBLT_IMPL_UNIT = 5     /* tcgen05 + TMA, one 128 x 128 tile per (sequence, head, 128 query rows): head_dim 64, at
+                            * most 128 keys per sequence, range masks, total_q_rows / total_k_rows given */
 } fblt_impl;
 
 typedef enum {
@@ -575,7 +575,7 @@ int fblt_matmul(const float *a, int64_t lda, const void *packed_b, const float *
  * scratch. Three launches: with embed_dim and head_dim multiples of 32 (and no
  * causal_offset in the mask) the first matmul's epilogue rotates Q and K, so qkv_work
  * holds the rotated projection afterwards and every attention kernel, the TMA-fed one
- * for sequences of at most 128 rows included, takes the rows as they are; otherwise
+ * for sequences of at most 128 keys included, takes the rows as they are; otherwise
  * qkv_work holds the un-rotated projection and the attention kernel rotates as it loads.
  * total_rows is the host copy of cu_rows[batch]; max_len bounds the sequence
  * lengths. All pointers device.

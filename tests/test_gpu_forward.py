@@ -31,7 +31,7 @@ def check(case: ForwardCase, kernels=KERNELS):
     if kernels[0][0] == L.IMPL_ROW and case.head_dim in (32, 64) and case.mask.group_rule != L.GROUP_IDS:
         kernels = kernels + [(L.IMPL_ROW_QUAD, L.PREC_FP32)]   # four lanes per row: same shapes, range rules
     fits_unit = (case.head_dim == 64 and case.mask.group_rule != L.GROUP_IDS and len(case.cu_q) > 1 and
-                 int(np.diff(case.cu_q).max()) <= 128 and int(np.diff(case.cu_k).max()) <= 128)
+                 int(np.diff(case.cu_q).max()) >= 1 and int(np.diff(case.cu_k).max()) <= 128)
     if fits_unit and (L.IMPL_UNIT, L.PREC_FP32) not in kernels:
         kernels = list(kernels) + [(L.IMPL_UNIT, L.PREC_FP32)]   # one 128 x 128 tcgen05 tile per (sequence, head)
     for impl, prec in kernels:
@@ -158,6 +158,13 @@ def test_unit_kernel_many_units_per_cta(cuda_lib):
     qlens[5::19] = 0
     cu_q, cu_k = np.concatenate([[0], np.cumsum(qlens)]), np.concatenate([[0], np.cumsum(klens)])
     check(random_case(72, cu_q, cu_k, 2, 64, MaskConfig()), kernels=unit)
+    # several 128-row query tiles over one sequence's keys (byte rows over a sequence's patches)
+    qlens = np.array([700, 1, 128, 129, 0, 300, 513])
+    klens = np.array([128, 5, 100, 128, 7, 0, 31])
+    cu_q, cu_k = np.concatenate([[0], np.cumsum(qlens)]), np.concatenate([[0], np.cumsum(klens)])
+    check(random_case(73, cu_q, cu_k, 4, 64, MaskConfig()), kernels=unit)
+    check(random_case(74, cu_q, cu_k, 4, 64, MaskConfig(is_causal=True, causal_offset=[0, 2, 5, 0, 3, 0, 10])),
+          kernels=unit)
     assert L.load().fblt_tcgen05_error() == 0
 
 
