@@ -46,6 +46,11 @@ struct DecodeParams {
 };
 
 __device__ __forceinline__ float4 ld4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+// 16 bytes global -> shared, bypassing L1, in the calling thread's current cp.async group
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const float *gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+                 : "memory");
+}
 __device__ __forceinline__ float dot4(const float4 &a, const float4 &b) {
     return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
 }
@@ -113,10 +118,27 @@ __host__ __device__ constexpr int dec_partial_floats() {
 }
 
 // Shared memory of one CTA: the warps' partial states meet here.
+// Keys per lane group and chunk of the unmasked stream: as many as fit "one score per lane", at most 8.
 template <int HD, int NQ>
+__host__ __device__ constexpr int dec_chunk_u() {
+    return ((HD / 4) / NQ) > 8 ? 8 : (((HD / 4) / NQ) < 1 ? 1 : ((HD / 4) / NQ));
+}
+// Whether the grid form stages the stream through shared memory (see DecShared::ring): the shapes whose
+// two-stage ring stays small enough for five CTAs per SM.
+template <int HD, int NQ>
+__host__ __device__ constexpr bool dec_ring_ok() {
+    return dec_chunk_u<HD, NQ>() <= 4 && HD <= 64;
+}
+
+template <int HD, int NQ, bool RING>
 struct DecShared {
     float4 acc[kDecWarps][NQ][HD / 4];
     float m[kDecWarps][NQ], l[kDecWarps][NQ];
+    // RING: per warp two stages of one chunk (U key pieces + U value pieces per lane). Every lane copies its
+    // own 16-byte pieces with cp.async and reads the same slots back, so a stage is in flight while the
+    // previous one is consumed, at no cost in registers and with no synchronisation beyond the lane's own
+    // wait_group.
+    float4 ring[RING ? kDecWarps : 1][2][RING ? 2 * dec_chunk_u<HD, NQ>() : 1][RING ? 32 : 1];
 };
 
 // Key range a query group may attend to, over all of its rows: [lo_min, hi_max).
@@ -129,8 +151,8 @@ __device__ __forceinline__ void dec_group_range(const DecodeParams &p, int base,
 // One piece of work: query group qg of (sequence b, head h) over the keys [k0, k1) (already inside
 // the group's range). The result goes to the output rows (direct) or, as (acc, m, l) partials, to
 // wdst + q * wrow floats for row q of the group.
-template <int HD, int NQ>
-__device__ __forceinline__ void decode_piece(const DecodeParams &p, DecShared<HD, NQ> &sh, int b, int h, int qg, int base,
+template <int HD, int NQ, bool RING>
+__device__ __forceinline__ void decode_piece(const DecodeParams &p, DecShared<HD, NQ, RING> &sh, int b, int h, int qg, int base,
                                              int k0, int k1, bool direct, float *wdst, int64_t wrow,
                                              bool write_through) {
     constexpr int LPK = HD / 4;   // lanes per key row
@@ -216,12 +238,40 @@ __device__ __forceinline__ void decode_piece(const DecodeParams &p, DecShared<HD
         const int64_t ustep = (int64_t)KPW * p.row_stride, cstep = (int64_t)kDecWarps * CH * p.row_stride;
         const float *kp = kc + (int64_t)(F0 + warp * CH + grp) * p.row_stride;
         const float *vp = vc + (int64_t)(F0 + warp * CH + grp) * p.row_stride;
+        // RING: the chunk after this one is already on its way into the warp's other stage
+        auto stage_in = [&](const float *kq, const float *vq, int slot) {
+            if constexpr (RING) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    cp_async_16(&sh.ring[warp][slot][u][lane], kq + u * ustep);
+                    cp_async_16(&sh.ring[warp][slot][U + u][lane], vq + u * ustep);
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
+        };
+        if (RING && warp < nchunks) stage_in(kp, vp, 0);
+        int ri = 0;
         for (int c = warp; c < nchunks; c += kDecWarps, kp += cstep, vp += cstep) {
             float4 kk[U], vv[U];
+            if constexpr (RING) {
+                if (c + kDecWarps < nchunks) {
+                    stage_in(kp + cstep, vp + cstep, (ri + 1) & 1);
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                } else {
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                kk[u] = ld4(kp + u * ustep);
-                vv[u] = ld4(vp + u * ustep);
+                for (int u = 0; u < U; ++u) {
+                    kk[u] = sh.ring[warp][ri & 1][u][lane];
+                    vv[u] = sh.ring[warp][ri & 1][U + u][lane];
+                }
+                ++ri;
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    kk[u] = ld4(kp + u * ustep);
+                    vv[u] = ld4(vp + u * ustep);
+                }
             }
             float s[V];
 #pragma unroll
@@ -411,7 +461,8 @@ __host__ __device__ constexpr int dec_chunk_keys() { // keys per warp per chunk 
 template <int HD, int NQ>
 __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p) {
     constexpr int CH = dec_chunk_keys<HD, NQ>();
-    __shared__ DecShared<HD, NQ> sh;
+    constexpr bool RING = dec_ring_ok<HD, NQ>();
+    __shared__ DecShared<HD, NQ, RING> sh;
     const int h = blockIdx.x, sp = blockIdx.y;
     const int b = blockIdx.z / p.qgroups, qg = blockIdx.z - b * p.qgroups;
     const int base = p.base_len[b] + p.base_add;
@@ -424,7 +475,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(DecodeParams p
     const int k0 = min(hi_max, lo_min + sp * per);
     const int k1 = min(hi_max, k0 + per);
     float *w = p.ws + ((((int64_t)b * p.H + h) * p.n_new + r0) * p.splits + sp) * dec_partial_floats<HD>();
-    decode_piece<HD, NQ>(p, sh, b, h, qg, base, k0, k1, p.splits == 1, w, (int64_t)p.splits * dec_partial_floats<HD>(),
+    decode_piece<HD, NQ, RING>(p, sh, b, h, qg, base, k0, k1, p.splits == 1, w, (int64_t)p.splits * dec_partial_floats<HD>(),
                          p.kn != nullptr && sp == p.splits - 1 && qg == 0);
 }
 
@@ -457,7 +508,7 @@ __global__ void __launch_bounds__(kDecThreads, NQ <= 4 ? 5 : 3) decode_stream_ke
     constexpr int A = dec_chunk_keys<HD, NQ>() * kDecWarps; // keys per block: one chunk for every warp
     constexpr int PF = dec_partial_floats<HD>();
     extern __shared__ int s_pref[]; // [batch + 1]: blocks before sequence b
-    __shared__ DecShared<HD, NQ> sh;
+    __shared__ DecShared<HD, NQ, false> sh; // no ring here: the prefix sum already takes the dynamic shared memory
     __shared__ int s_warp_sum[kDecWarps];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int units_per_seq = p.H * p.qgroups;
@@ -527,7 +578,7 @@ __global__ void __launch_bounds__(kDecThreads, NQ <= 4 ? 5 : 3) decode_stream_ke
         const int slot = g * 2 + (first ? 0 : 1);
         if (!whole && tid == 0)
             desc[slot] = make_int2(b * units_per_seq + ul, kPieceValid | (head ? kPieceHead : 0) | (tail ? kPieceTail : 0));
-        decode_piece<HD, NQ>(p, sh, b, h, qg, base, k0, k1, whole, part + (int64_t)slot * NQ * PF, PF,
+        decode_piece<HD, NQ, false>(p, sh, b, h, qg, base, k0, k1, whole, part + (int64_t)slot * NQ * PF, PF,
                              p.kn != nullptr && tail && qg == 0);
         __syncthreads(); // the warps' shared state is reused by the next piece
         x += blk1 - blk0;
