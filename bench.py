@@ -517,6 +517,23 @@ def main():
                "algorithmic_bytes_per_launch": pre_bytes, "achieved_GBps": pre_bytes / pre_launch_ms / 1e6,
                "frac_of_hbm_peak": pre_bytes / pre_launch_ms / 1e6 / peak,
                "algorithmic_tflops": pre_flops / pre_launch_ms / 1e9}
+    # The same launch timed alone (L2 flushed before each of 10 launches, median): launch_ms above is taken
+    # inside the step, right after 64 decode launches that hold the GPU at its power cap, and this kernel,
+    # unlike the HBM-bound decode stream, runs with the SM clock.
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    alone = []
+    for _ in range(10):
+        flush.zero_()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(main_stream)
+        ops.attn_forward(pre, main_stream)
+        a1.record(main_stream)
+        a1.synchronize()
+        alone.append(a0.elapsed_time(a1))
+    del flush
+    alone_ms = sorted(alone)[len(alone) // 2]
+    prefill["launch_ms_alone"] = alone_ms
+    prefill["frac_of_hbm_peak_alone"] = pre_bytes / alone_ms / 1e6 / peak
 
     # ---- host-buffer leg (sessions): copies inside the timed region -------------
     e2e = None
