@@ -118,10 +118,11 @@ __host__ __device__ constexpr int dec_partial_floats() {
 }
 
 // Shared memory of one CTA: the warps' partial states meet here.
-// Keys per lane group and chunk of the unmasked stream: as many as fit "one score per lane", at most 8.
+constexpr int kDecMaxU = 8; // (4, which would give the single-row decode a ring too, loses 2 % on long caches)
+// Keys per lane group and chunk of the unmasked stream: as many as fit "one score per lane", at most kDecMaxU.
 template <int HD, int NQ>
 __host__ __device__ constexpr int dec_chunk_u() {
-    return ((HD / 4) / NQ) > 8 ? 8 : (((HD / 4) / NQ) < 1 ? 1 : ((HD / 4) / NQ));
+    return ((HD / 4) / NQ) > kDecMaxU ? kDecMaxU : (((HD / 4) / NQ) < 1 ? 1 : ((HD / 4) / NQ));
 }
 // Whether the grid form stages the stream through shared memory (see DecShared::ring): the shapes whose
 // two-stage ring stays small enough for five CTAs per SM.
@@ -158,7 +159,7 @@ __device__ __forceinline__ void decode_piece(const DecodeParams &p, DecShared<HD
     constexpr int LPK = HD / 4;   // lanes per key row
     constexpr int KPW = 32 / LPK; // key rows per warp load
     // keys per lane group and chunk: as many as fit "one score per lane", at most 8
-    constexpr int U = (LPK / NQ) > 8 ? 8 : ((LPK / NQ) < 1 ? 1 : (LPK / NQ));
+    constexpr int U = dec_chunk_u<HD, NQ>();
     constexpr int CH = KPW * U; // keys per warp per chunk
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -453,8 +454,7 @@ __device__ __forceinline__ void decode_piece(const DecodeParams &p, DecShared<HD
 template <int HD, int NQ>
 __host__ __device__ constexpr int dec_chunk_keys() { // keys per warp per chunk of the unmasked stream (CH above)
     constexpr int LPK = HD / 4, KPW = 32 / LPK;
-    constexpr int U = (LPK / NQ) > 8 ? 8 : ((LPK / NQ) < 1 ? 1 : (LPK / NQ));
-    return KPW * U;
+    return KPW * dec_chunk_u<HD, NQ>();
 }
 
 // Grid form: CTA = (head, key-range split, sequence x query group).
@@ -772,7 +772,7 @@ static int stream_slots(int hd, int nq, int *slots) {
 static int chunk_keys(int hd, int nq) { // dec_chunk_keys<HD, NQ>() for run-time values
     const int lpk = hd / 4, kpw = 32 / lpk;
     int u = lpk / nq;
-    u = u > 8 ? 8 : (u < 1 ? 1 : u);
+    u = u > kDecMaxU ? kDecMaxU : (u < 1 ? 1 : u);
     return kpw * u;
 }
 
