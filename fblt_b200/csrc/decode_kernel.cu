@@ -51,14 +51,18 @@ __device__ __forceinline__ void cp_async_16(void *smem_dst, const float *gmem_sr
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
                  : "memory");
 }
+// Packed fp32 pairs (one instruction for two multiply-adds): the stream is issue-bound once the power cap
+// has pulled the SM clock down, and these two helpers are most of its arithmetic.
 __device__ __forceinline__ float dot4(const float4 &a, const float4 &b) {
-    return a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    float2 t = __fmul2_rn(make_float2(a.x, a.y), make_float2(b.x, b.y));
+    t = __ffma2_rn(make_float2(a.z, a.w), make_float2(b.z, b.w), t);
+    return t.x + t.y;
 }
 __device__ __forceinline__ void fma4(float4 &acc, float p, const float4 &v) {
-    acc.x += p * v.x;
-    acc.y += p * v.y;
-    acc.z += p * v.z;
-    acc.w += p * v.w;
+    const float2 pp = make_float2(p, p);
+    const float2 lo = __ffma2_rn(pp, make_float2(v.x, v.y), make_float2(acc.x, acc.y));
+    const float2 hi = __ffma2_rn(pp, make_float2(v.z, v.w), make_float2(acc.z, acc.w));
+    acc = make_float4(lo.x, lo.y, hi.x, hi.y);
 }
 __device__ __forceinline__ void scale4(float4 &a, float c) {
     a.x *= c;
