@@ -926,7 +926,7 @@ def run_blocks(args):
 # dram__bytes_read + dram__bytes_write per algorithmic byte of the decode kernel, from an ncu capture
 # of a 256-sequence launch; the traffic of a full launch is scaled from it by the rows processed
 # (traffic grows in proportion: every cache row is read once).
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.010
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.009
 
 
 def measure_host_link(torch, dev, barrier, world: int):
