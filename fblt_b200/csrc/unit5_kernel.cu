@@ -341,7 +341,13 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             uint4 lo4;
             uint32_t *lp = &lo4.x;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) lp[c] = __float_as_uint(e[c] - __uint_as_float(__float_as_uint(e[c]) & 0xFFFFE000u));
+            for (int c = 0; c < 4; c += 2) { // x - trunc(x) for two words per instruction (packed fp32 multiply-add)
+                const float2 t = make_float2(__uint_as_float(__float_as_uint(e[c]) & 0xFFFFE000u),
+                                             __uint_as_float(__float_as_uint(e[c + 1]) & 0xFFFFE000u));
+                const float2 r = __ffma2_rn(t, make_float2(-1.0f, -1.0f), make_float2(e[c], e[c + 1]));
+                lp[c] = __float_as_uint(r.x);
+                lp[c + 1] = __float_as_uint(r.y);
+            }
             *reinterpret_cast<uint4 *>(lo_at) = lo4;
         };
         // Geometry of this CTA's unit number kk and this thread's key range in it, then the split of its
@@ -434,9 +440,10 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             if (live) {
                 tmem_ld32(trow + kU5ColS + qt * 32, sc);
                 tc_wait_ld();
-                float odd = 0.0f;
+                float2 odd2 = make_float2(0.0f, 0.0f);
 #pragma unroll
-                for (int c = 0; c < 32; ++c) odd = fmaf(sc[c], 0.0f, odd);
+                for (int c = 0; c < 32; c += 2) odd2 = __ffma2_rn(make_float2(sc[c], sc[c + 1]), make_float2(0.0f, 0.0f), odd2);
+                const float odd = odd2.x + odd2.y;
                 if (odd != odd || !(qscale > 0.0f)) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c) {
@@ -472,17 +479,23 @@ __global__ void __launch_bounds__(kU5Threads, 1)
             mx = fmaxf(fmaxf(*reinterpret_cast<const float *>(piece_at(0, 0)), *reinterpret_cast<const float *>(piece_at(1, 0))),
                        fmaxf(*reinterpret_cast<const float *>(piece_at(2, 0)), *reinterpret_cast<const float *>(piece_at(3, 0))));
             const float ref = mx == -INFINITY ? 0.0f : mx;
-            float l = 0.0f;
+            float2 l2 = make_float2(0.0f, 0.0f);
 #pragma unroll
             for (int pc = 0; pc < 2; ++pc) {
                 uint32_t ph[16], pl[16];
                 if (live) {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const float p = t5_ex2(fmaf(sc[pc * 16 + c], qs, -ref)); // masked entries are -inf: 0
-                        l += p;
-                        ph[c] = __float_as_uint(p);
-                        pl[c] = __float_as_uint(p - __uint_as_float(ph[c] & 0xFFFFE000u));
+                    for (int c = 0; c < 16; c += 2) { // two scores per packed instruction; masked entries are -inf: 0
+                        const float2 x = __ffma2_rn(make_float2(sc[pc * 16 + c], sc[pc * 16 + c + 1]), make_float2(qs, qs),
+                                                    make_float2(-ref, -ref));
+                        const float2 pp = make_float2(t5_ex2(x.x), t5_ex2(x.y));
+                        l2 = __fadd2_rn(l2, pp);
+                        ph[c] = __float_as_uint(pp.x);
+                        ph[c + 1] = __float_as_uint(pp.y);
+                        const float2 lo2 = __ffma2_rn(make_float2(__uint_as_float(ph[c] & 0xFFFFE000u), __uint_as_float(ph[c + 1] & 0xFFFFE000u)),
+                                                      make_float2(-1.0f, -1.0f), pp);
+                        pl[c] = __float_as_uint(lo2.x);
+                        pl[c + 1] = __float_as_uint(lo2.y);
                     }
                 } else { // columns past the row group's range: the MMA still reads them
 #pragma unroll
@@ -491,6 +504,7 @@ __global__ void __launch_bounds__(kU5Threads, 1)
                 tmem_st16(trow + kU5ColPhi + qt * 32 + pc * 16, ph);
                 tmem_st16(trow + kU5ColPlo + qt * 32 + pc * 16, pl);
             }
+            float l = l2.x + l2.y;
             xsum[qt][row] = l;
             tc_wait_st();
             tc_fence_before();
