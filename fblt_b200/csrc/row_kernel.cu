@@ -6,6 +6,8 @@
 // shapes the tile kernel does not take.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace fblt {
 
 constexpr int kRowWarps = 4;
@@ -145,6 +147,14 @@ __global__ void __launch_bounds__(kRowWarps * 32) row_attn_kernel(fblt_attn_desc
 constexpr int kQuadRows = 32;     // rows per CTA of 128 threads
 constexpr int kQuadLongRow = 16;  // rows with more keys than this are walked by the whole warp
 
+// 16 bytes global -> shared in the calling thread's cp.async group; `valid` false copies nothing and
+// fills the destination with zeros.
+__device__ __forceinline__ void cp_async_16_zfill(void *smem_dst, const float *gmem_src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+                 "l"(gmem_src), "r"(valid ? 16 : 0)
+                 : "memory");
+}
+
 // Running softmax state of one row (or of one quad's share of a long row).
 template <int NV>
 struct QuadState {
@@ -204,6 +214,67 @@ __device__ __forceinline__ void quad_key_pair(QuadState<NV> &st, const float4 (&
     if (two) st.take(s1, vc);
 }
 
+// The same walk over `trips` key pairs (keys j0 + it * jstep and the one after it), with the pieces of the
+// next pair already on their way: every lane copies its own 16-byte pieces with cp.async into its slots of a
+// two-stage ring in shared memory (slots [stage][piece][thread]: conflict-free, private to the lane, so
+// the lane's own wait_group is all the synchronisation there is) and reads them back a trip later. A walk
+// of n trips then waits for memory about once instead of n times. Keys at or past hi are zero-filled by
+// the copy itself (source size 0) and fold nothing into the state.
+template <int NV>
+__device__ __forceinline__ void quad_walk_ring(QuadState<NV> &st, const float4 (&qv)[NV], const float *kb, const float *vb,
+                                               int64_t k_stride, int64_t v_stride, int j0, int jstep, int trips, int hi,
+                                               float4 *ring) {
+    constexpr int PIECES = 4 * NV; // K and V pieces of two keys
+    const int nthreads = blockDim.x, tid = threadIdx.x;
+    auto stage_in = [&](int it) {
+        const int j = j0 + it * jstep;
+        const bool one = j < hi, two = j + 1 < hi;
+        const float *k0p = kb + (int64_t)(one ? j : 0) * k_stride, *v0p = vb + (int64_t)(one ? j : 0) * v_stride;
+        const float *k1p = k0p + (two ? k_stride : 0), *v1p = v0p + (two ? v_stride : 0);
+        float4 *slot = ring + (size_t)(it & 1) * PIECES * nthreads + tid;
+#pragma unroll
+        for (int t = 0; t < NV; ++t) {
+            cp_async_16_zfill(slot + (0 * NV + t) * nthreads, k0p + t * 16, one);
+            cp_async_16_zfill(slot + (1 * NV + t) * nthreads, v0p + t * 16, one);
+            cp_async_16_zfill(slot + (2 * NV + t) * nthreads, k1p + t * 16, two);
+            cp_async_16_zfill(slot + (3 * NV + t) * nthreads, v1p + t * 16, two);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (trips > 0) stage_in(0);
+    for (int it = 0; it < trips; ++it) {
+        if (it + 1 < trips) {
+            stage_in(it + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        const int j = j0 + it * jstep;
+        const bool one = j < hi, two = j + 1 < hi;
+        const float4 *slot = ring + (size_t)(it & 1) * PIECES * nthreads + tid;
+        float4 ka[NV], va[NV], kc[NV], vc[NV];
+#pragma unroll
+        for (int t = 0; t < NV; ++t) {
+            ka[t] = slot[(0 * NV + t) * nthreads];
+            va[t] = slot[(1 * NV + t) * nthreads];
+            kc[t] = slot[(2 * NV + t) * nthreads];
+            vc[t] = slot[(3 * NV + t) * nthreads];
+        }
+        float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+        for (int t = 0; t < NV; ++t) {
+            s0 += qv[t].x * ka[t].x + qv[t].y * ka[t].y + qv[t].z * ka[t].z + qv[t].w * ka[t].w;
+            s1 += qv[t].x * kc[t].x + qv[t].y * kc[t].y + qv[t].z * kc[t].z + qv[t].w * kc[t].w;
+        }
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+        s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
+        if (one) st.take(s0, va);
+        if (two) st.take(s1, vc);
+    }
+}
+
 // LONG = false drops the long-row pass (and its registers) for rules whose ranges cannot be long.
 template <int HD, bool LONG>
 __global__ void __launch_bounds__(kQuadRows * 4) rowq_attn_kernel(fblt_attn_desc d) {
@@ -242,7 +313,12 @@ __global__ void __launch_bounds__(kQuadRows * 4) rowq_attn_kernel(fblt_attn_desc
     // into eight serial strands.
     const bool long_row = LONG && hi - lo > kQuadLongRow;
     const int trips = warp_max(long_row ? 0 : (hi - lo + 1) >> 1);
-    for (int it = 0; it < trips; ++it) quad_key_pair<NV>(st, qv, kb, vb, d.k_stride, d.v_stride, lo + 2 * it, long_row ? lo : hi);
+    extern __shared__ float4 quad_ring[]; // LONG only: 2 stages x 4 NV pieces x 128 threads
+    if constexpr (LONG) {
+        quad_walk_ring<NV>(st, qv, kb, vb, d.k_stride, d.v_stride, lo, 2, trips, long_row ? lo : hi, quad_ring);
+    } else {
+        for (int it = 0; it < trips; ++it) quad_key_pair<NV>(st, qv, kb, vb, d.k_stride, d.v_stride, lo + 2 * it, hi);
+    }
 
     // Long rows (a patch that absorbed the rest of its sequence): one at a time, the eight quads
     // of the warp take every eighth key pair, then their partial softmax states are merged.
@@ -262,8 +338,7 @@ __global__ void __launch_bounds__(kQuadRows * 4) rowq_attn_kernel(fblt_attn_desc
         QuadState<NV> part;
         part.reset();
         const int trips8 = (rhi - rlo + 15) >> 4; // the same for every lane: 16 keys per warp trip
-        for (int it = 0; it < trips8; ++it)
-            quad_key_pair<NV>(part, rq, kb, vb, d.k_stride, d.v_stride, rlo + 16 * it + 2 * qd, rhi);
+        quad_walk_ring<NV>(part, rq, kb, vb, d.k_stride, d.v_stride, rlo + 2 * qd, 16, trips8, rhi, quad_ring);
         // merge the eight partial states (each step pairs quads 1, 2 and 4 apart); afterwards every
         // quad holds the row's state
 #pragma unroll
@@ -327,11 +402,24 @@ int launch_rowq_kernel(const fblt_attn_desc &d, cudaStream_t stream) {
     dim3 grid((d.max_q + kQuadRows - 1) / kQuadRows, d.num_heads, d.batch);
     // the decoder's one-latent rule gives every row at most `subtokens` keys
     const bool may_be_long = !(d.mask.group_rule == FBLT_GROUP_PATCH_DEC && d.mask.subtokens <= kQuadLongRow);
+    // the LONG variants stage their key walk through a two-stage ring: 2 x (4 * head_dim / 16) pieces per thread
+    const size_t ring32 = (size_t)2 * 4 * 2 * kQuadRows * 4 * sizeof(float4), ring64 = 2 * ring32;
+    if (may_be_long) {
+        static std::atomic<uint64_t> configured{0}; // one bit per device ordinal: 64 KB of dynamic shared memory needs the opt-in
+        int dev = 0;
+        FBLT_CUDA_TRY(cudaGetDevice(&dev));
+        const uint64_t bit = 1ull << (dev & 63);
+        if (!(configured.load(std::memory_order_acquire) & bit)) {
+            FBLT_CUDA_TRY(cudaFuncSetAttribute(rowq_attn_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring64));
+            FBLT_CUDA_TRY(cudaFuncSetAttribute(rowq_attn_kernel<32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ring32));
+            configured.fetch_or(bit, std::memory_order_release);
+        }
+    }
     if (d.head_dim == 32) {
-        if (may_be_long) rowq_attn_kernel<32, true><<<grid, kQuadRows * 4, 0, stream>>>(d);
+        if (may_be_long) rowq_attn_kernel<32, true><<<grid, kQuadRows * 4, ring32, stream>>>(d);
         else rowq_attn_kernel<32, false><<<grid, kQuadRows * 4, 0, stream>>>(d);
     } else {
-        if (may_be_long) rowq_attn_kernel<64, true><<<grid, kQuadRows * 4, 0, stream>>>(d);
+        if (may_be_long) rowq_attn_kernel<64, true><<<grid, kQuadRows * 4, ring64, stream>>>(d);
         else rowq_attn_kernel<64, false><<<grid, kQuadRows * 4, 0, stream>>>(d);
     }
     count_launch();
